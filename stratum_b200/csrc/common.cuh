@@ -1,0 +1,58 @@
+// Shared helpers for the sm_100a kernels: element types, status codes, reductions.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+// Launchers return 0 on success, a positive cudaError_t from the launch, or one of these.
+#define STRATUM_ERR_DTYPE (-1)   // dtype code is neither 0 (float32) nor 1 (bfloat16)
+#define STRATUM_ERR_SHAPE (-2)   // a size the kernel does not take
+#define STRATUM_ERR_ALIGN (-3)   // a pointer or stride is not aligned as the kernel needs
+#define STRATUM_ERR_LIMIT (-4)   // beyond a stated maximum
+
+#define STRATUM_DT_F32 0
+#define STRATUM_DT_BF16 1
+
+#define STRATUM_EXPORT extern "C" __attribute__((visibility("default")))
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_float<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The order of
+// additions depends only on the block size, never on what else runs.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = (lane < n_warps) ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+static inline int launch_status() {
+  cudaError_t e = cudaGetLastError();
+  return (int)e;
+}

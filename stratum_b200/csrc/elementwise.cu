@@ -1,0 +1,227 @@
+// Embedding gather, RMSNorm, SwiGLU and rotary position encoding fused with the cache write.
+//
+// The residual stream is float32 on every path; T is the dtype of weights, of the
+// normed activations that feed matrix products, and of the cache (float or bfloat16).
+// Every reduction's order depends only on the row it belongs to, so a row's result does
+// not depend on what else is in the step.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding gather
+// out[t][:] = table[ids[t]][:]   (stratum/native/stratum_arch_llama.inc.c:564-593: a row copy, no scaling)
+template <typename T>
+__global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                    float* __restrict__ out, int hidden, int vocab) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;   // ids are range-checked on the host before a step; never trust twice
+  const T* row = table + (size_t)id * hidden;
+  float* o = out + (size_t)t * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(row[i]);
+}
+
+STRATUM_EXPORT int stratum_embed_gather(const void* table, int dtype, const int* ids, float* out,
+                                        int n_tokens, int hidden, int vocab, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (dtype == STRATUM_DT_F32)
+    embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, hidden, vocab);
+  else if (dtype == STRATUM_DT_BF16)
+    embed_gather_kernel<bf16><<<n_tokens, threads, 0, stream>>>((const bf16*)table, ids, out, hidden, vocab);
+  else
+    return STRATUM_ERR_DTYPE;
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// y = x * (1/sqrt(mean(x^2) + eps)) * gain     (stratum/native/stratum_arch_llama.inc.c:45-76)
+// x float32 [*, hidden]; row r of the output reads row rows[r] of x when rows != nullptr
+// (the final norm runs only on the rows whose logits are wanted).
+template <typename T>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
+                               const int* __restrict__ rows, T* __restrict__ out, int hidden, float eps) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  const float* xr = x + (size_t)src * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = xr[i];
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+  T* o = out + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<T>(xr[i] * scale * gain[i]);
+}
+
+STRATUM_EXPORT int stratum_rmsnorm(const float* x, const float* gain, const int* rows, void* out, int out_dtype,
+                                   int n_rows, int hidden, float eps, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  if (out_dtype == STRATUM_DT_F32)
+    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, gain, rows, (float*)out, hidden, eps);
+  else if (out_dtype == STRATUM_DT_BF16)
+    rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, gain, rows, (bf16*)out, hidden, eps);
+  else
+    return STRATUM_ERR_DTYPE;
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- SwiGLU
+// a[j] = silu(g[j]) * u[j], silu(z) = z / (1 + exp(-z))   (stratum/native/stratum_engine.h:373-391)
+// gu holds gate and up interleaved: gu[r][2j] = g_j, gu[r][2j+1] = u_j.
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, size_t total) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t r = i / inter;
+  const int j = (int)(i - r * inter);
+  const T* p = gu + r * (size_t)(2 * inter) + 2 * j;
+  const float g = to_float(p[0]), u = to_float(p[1]);
+  out[i] = from_float<T>(g / (1.0f + expf(-g)) * u);
+}
+
+STRATUM_EXPORT int stratum_swiglu(const void* gu, void* out, int dtype, int n_rows, int inter, cudaStream_t stream) {
+  const size_t total = (size_t)n_rows * inter;
+  if (total == 0) return 0;
+  const int threads = 256;
+  const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+  if (dtype == STRATUM_DT_F32)
+    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, inter, total);
+  else if (dtype == STRATUM_DT_BF16)
+    swiglu_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, inter, total);
+  else
+    return STRATUM_ERR_DTYPE;
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- rotary encoding + cache write
+// qkv: [tokens][(Nq + 2 Nk) * Hd], the fused projection's output: q heads, then k heads, then v heads.
+// For every token: rotate each q head in place; rotate each k head and store it, and store each v head,
+// into the token's row of the paged cache.  angle = (float)pos * inv_freq[k]; pair (x0,x1) <-
+// (x0 c - x1 s, x0 s + x1 c), with c and s scaled by `mscale`
+// (stratum/native/stratum_arch_llama.inc.c:132-159).  Pairs are (2k, 2k+1) when interleaved, else
+// (k, k + n_pairs).  Dims at and beyond 2*n_pairs pass through unrotated.
+// Cache layout: [pages][Nk][page_tokens][Hd]; page of a position = block_table[seq][pos / page_tokens].
+// A token whose sequence index is negative (padding) is skipped entirely.
+template <typename T>
+__global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ token_pos,
+                                  const int* __restrict__ token_seq, const int* __restrict__ block_table,
+                                  int bt_stride, const float* __restrict__ inv_freq, int n_pairs,
+                                  int interleaved, float mscale, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                  int n_q, int n_kv, int head_dim, int page_tokens, int write_cache) {
+  extern __shared__ float cs[];   // cos[n_pairs], sin[n_pairs]
+  const int t = blockIdx.x;
+  const int seq = token_seq[t];
+  if (seq < 0) return;
+  const int pos = token_pos[t];
+  for (int k = threadIdx.x; k < n_pairs; k += blockDim.x) {
+    const float angle = (float)pos * inv_freq[k];
+    float s, c;
+    sincosf(angle, &s, &c);
+    cs[k] = c * mscale;
+    cs[n_pairs + k] = s * mscale;
+  }
+  __syncthreads();
+  const int row_elems = (n_q + 2 * n_kv) * head_dim;
+  T* row = qkv + (size_t)t * row_elems;
+  const int half = head_dim / 2;          // work items per head: one per pair slot (rotated or not)
+  size_t kv_row_base = 0;
+  if (write_cache) {
+    const int page = block_table[(size_t)seq * bt_stride + pos / page_tokens];
+    kv_row_base = ((size_t)page * n_kv * page_tokens + (pos % page_tokens)) * (size_t)head_dim;
+  }
+  const size_t head_stride = (size_t)page_tokens * head_dim;   // between kv heads inside a page
+  // q and k heads: item = (head, slot); slot < n_pairs rotates a pair, slot >= n_pairs copies two plain dims
+  const int n_rot_heads = n_q + (write_cache ? n_kv : 0);
+  for (int item = threadIdx.x; item < n_rot_heads * half; item += blockDim.x) {
+    const int h = item / half, slot = item - h * half;
+    T* hp = row + (size_t)h * head_dim;
+    int i0, i1;
+    float y0, y1;
+    if (slot < n_pairs) {
+      if (interleaved) { i0 = 2 * slot; i1 = i0 + 1; } else { i0 = slot; i1 = slot + n_pairs; }
+      const float x0 = to_float(hp[i0]), x1 = to_float(hp[i1]);
+      const float c = cs[slot], s = cs[n_pairs + slot];
+      y0 = x0 * c - x1 * s;
+      y1 = x0 * s + x1 * c;
+    } else {
+      i0 = 2 * n_pairs + 2 * (slot - n_pairs); i1 = i0 + 1;
+      y0 = to_float(hp[i0]); y1 = to_float(hp[i1]);
+    }
+    if (h < n_q) {
+      hp[i0] = from_float<T>(y0);
+      hp[i1] = from_float<T>(y1);
+    } else {
+      T* dst = k_cache + kv_row_base + (size_t)(h - n_q) * head_stride;
+      dst[i0] = from_float<T>(y0);
+      dst[i1] = from_float<T>(y1);
+    }
+  }
+  if (write_cache) {
+    const T* vsrc = row + (size_t)(n_q + n_kv) * head_dim;
+    for (int item = threadIdx.x; item < n_kv * head_dim; item += blockDim.x) {
+      const int h = item / head_dim, d = item - h * head_dim;
+      v_cache[kv_row_base + (size_t)h * head_stride + d] = vsrc[item];
+    }
+  }
+}
+
+STRATUM_EXPORT int stratum_rope_store(void* qkv, int dtype, const int* token_pos, const int* token_seq,
+                                      const int* block_table, int bt_stride, const float* inv_freq, int n_pairs,
+                                      int interleaved, float mscale, void* k_cache, void* v_cache, int n_tokens,
+                                      int n_q, int n_kv, int head_dim, int page_tokens, int write_cache,
+                                      cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (head_dim % 2 != 0 || 2 * n_pairs > head_dim || n_pairs < 0) return STRATUM_ERR_SHAPE;
+  const int threads = 256;
+  const size_t smem = (size_t)2 * n_pairs * sizeof(float);
+  if (dtype == STRATUM_DT_F32)
+    rope_store_kernel<float><<<n_tokens, threads, smem, stream>>>(
+        (float*)qkv, token_pos, token_seq, block_table, bt_stride, inv_freq, n_pairs, interleaved, mscale,
+        (float*)k_cache, (float*)v_cache, n_q, n_kv, head_dim, page_tokens, write_cache);
+  else if (dtype == STRATUM_DT_BF16)
+    rope_store_kernel<bf16><<<n_tokens, threads, smem, stream>>>(
+        (bf16*)qkv, token_pos, token_seq, block_table, bt_stride, inv_freq, n_pairs, interleaved, mscale,
+        (bf16*)k_cache, (bf16*)v_cache, n_q, n_kv, head_dim, page_tokens, write_cache);
+  else
+    return STRATUM_ERR_DTYPE;
+  return launch_status();
+}
+
+// ---------------------------------------------------------------- seeded fill (random weights on the device)
+// value = std * z, z standard normal from a counter-based hash of (seed, element index): Box-Muller over
+// two 24-bit uniforms.  Filling a tensor in pieces or whole gives the same values.
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+  z += 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+template <typename T>
+__global__ void fill_normal_kernel(T* __restrict__ out, size_t n, uint64_t seed, float std_dev) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    const uint64_t r = mix64(seed ^ mix64(i));
+    const float u1 = ((float)((r >> 40) & 0xFFFFFF) + 1.0f) * (1.0f / 16777216.0f);   // (0, 1]
+    const float u2 = (float)((r >> 8) & 0xFFFFFF) * (1.0f / 16777216.0f);             // [0, 1)
+    const float z = sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
+    out[i] = from_float<T>(std_dev * z);
+  }
+}
+
+STRATUM_EXPORT int stratum_fill_normal(void* out, int dtype, size_t n, uint64_t seed, float std_dev,
+                                       cudaStream_t stream) {
+  if (n == 0) return 0;
+  const int threads = 256;
+  size_t want = (n + threads - 1) / threads;
+  const unsigned blocks = (unsigned)(want > 148 * 16 ? 148 * 16 : want);
+  if (dtype == STRATUM_DT_F32)
+    fill_normal_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, n, seed, std_dev);
+  else if (dtype == STRATUM_DT_BF16)
+    fill_normal_kernel<bf16><<<blocks, threads, 0, stream>>>((bf16*)out, n, seed, std_dev);
+  else
+    return STRATUM_ERR_DTYPE;
+  return launch_status();
+}

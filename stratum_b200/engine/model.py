@@ -1,0 +1,162 @@
+"""A model built from a ModelSpec: parts, their weights, and the forward pass over one step.
+
+The model class is chosen by config.json through the architecture registry; from there on
+everything is generic: the spec names parts, the part registry builds them, the schedule says
+in which order layers run and whose cache each stop uses.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Mapping, Optional, Tuple
+
+import torch
+
+from .. import architectures  # noqa: F401  (registers the built-in architectures)
+from ..cache.store import CacheSpec
+from ..config.base import ModelConfig, read_config_json
+from ..config.registry import find_architecture
+from ..parts import find_part
+from ..parts.base import Runtime
+from ..parts.spec import LayerSpec, ModelSpec, TensorSpec
+from ..weights.loader import check_tensors, load_weights, place
+
+
+class Layer:
+    """The parts of one decoder layer, built from its LayerSpec."""
+
+    def __init__(self, spec: LayerSpec, runtime: Optional[Runtime]):
+        self.spec = spec
+        self.prefix = spec.prefix
+        self.arrangement = find_part("arrangement", spec.arrangement)()
+        self.mixer = find_part("mixer", spec.mixer.kind)(spec.mixer, runtime)
+        self.mixer_norm = find_part("norm", spec.mixer_norm.kind)(spec.mixer_norm, runtime)
+        self.feed_forward = find_part("feed_forward", spec.feed_forward.kind)(spec.feed_forward, runtime)
+        self.feed_forward_norm = find_part("norm", spec.feed_forward_norm.kind)(spec.feed_forward_norm, runtime)
+
+    def parts(self):
+        return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        out: Dict[str, TensorSpec] = {}
+        for p in self.parts():
+            for name, ts in p.tensors().items():
+                out[self.prefix + name] = ts
+        return out
+
+    def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
+        n = len(self.prefix)
+        local = {k[n:]: v for k, v in weights.items() if k.startswith(self.prefix)}
+        for p in self.parts():
+            p.bind(local)
+
+
+class Model:
+    """Parts of a whole model.  Without a runtime it only describes (tensor list, cache needs)."""
+
+    def __init__(self, spec: ModelSpec, runtime: Optional[Runtime]):
+        spec.check()
+        self.spec = spec
+        self.runtime = runtime
+        self.embedding = find_part("embedding", spec.embedding.kind)(spec.embedding, runtime)
+        self.layers: List[Layer] = [Layer(ls, runtime) for ls in spec.layers]
+        self.final_norm = find_part("norm", spec.final_norm.kind)(spec.final_norm, runtime)
+        self.head = find_part("head", spec.head.kind)(spec.head, runtime)
+        self.schedule = spec.schedule
+        self.hidden, self.vocab = spec.hidden, spec.vocab
+
+    # ------------------------------------------------------------------ description
+    def tensors(self) -> Dict[str, TensorSpec]:
+        out: Dict[str, TensorSpec] = {}
+        out.update(self.embedding.tensors())
+        for layer in self.layers:
+            out.update(layer.tensors())
+        out.update(self.final_norm.tensors())
+        out.update(self.head.tensors())
+        return out
+
+    def cache_specs(self) -> List[Optional[CacheSpec]]:
+        """Per layer: what its mixer keeps per sequence (None if nothing, or if no stop owns its cache)."""
+        owners = {e.layer for e in self.schedule if e.cache_of is None}
+        owners |= {e.cache_of for e in self.schedule if e.cache_of is not None}
+        return [layer.mixer.cache_spec() if i in owners else None for i, layer in enumerate(self.layers)]
+
+    # ------------------------------------------------------------------ weights
+    def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
+        self.embedding.bind(weights)
+        for layer in self.layers:
+            layer.bind(weights)
+        self.final_norm.bind(weights)
+        self.head.bind_with_embedding(weights, self.embedding.table())
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, step, cache) -> torch.Tensor:
+        """Run the tokens of one step through every stop of the schedule; float32 logits at the wanted rows."""
+        x = self.embedding.forward(step.token_ids)
+        for entry in self.schedule:
+            layer = self.layers[entry.layer]
+            owner = entry.layer if entry.cache_of is None else entry.cache_of
+            view = cache.layer_view(owner, entry.cache_of is None, step.block_tables)
+            layer.arrangement.forward(layer, x, step, view)
+        if step.want_rows.numel() == 0:
+            return torch.empty((0, self.vocab), dtype=torch.float32, device=x.device)
+        xn = self.final_norm.forward(x, rows=step.want_rows)
+        return self.head.forward(xn)
+
+
+def config_from_dir(model_dir: str) -> Tuple[ModelConfig, object]:
+    raw = read_config_json(model_dir)
+    arch = find_architecture(raw)
+    return arch.config_class.from_dict(raw), arch
+
+
+def expected_tensors(config: ModelConfig) -> Dict[str, TensorSpec]:
+    """Every tensor a model of this configuration expects; needs no GPU."""
+    arch = find_architecture(config.architecture)
+    return Model(arch.describe_model(config), None).tensors()
+
+
+def load_model(model_dir: str, dtype: torch.dtype, device="cuda") -> Tuple[Model, ModelConfig]:
+    """config.json picks the architecture; weights are bound by name."""
+    config, arch = config_from_dir(model_dir)
+    runtime = Runtime(dtype, device)
+    model = Model(arch.describe_model(config), runtime)
+    weights = load_weights(model_dir, model.tensors(), dtype, runtime.device)
+    model.bind(weights)
+    return model, config
+
+
+def model_from_tensors(config: ModelConfig, tensors: Mapping[str, torch.Tensor], dtype: torch.dtype,
+                       device="cuda") -> Model:
+    """Build from tensors already in memory (checked like a file's)."""
+    arch = find_architecture(config.architecture)
+    runtime = Runtime(dtype, device)
+    model = Model(arch.describe_model(config), runtime)
+    expected = model.tensors()
+    check_tensors("tensors in memory", expected, tensors)
+    placed = {n: place(tensors[n], s, dtype, runtime.device) for n, s in expected.items() if n in tensors}
+    model.bind(placed)
+    return model
+
+
+def random_model_on_device(config: ModelConfig, seed: int, dtype: torch.dtype, device="cuda",
+                           std: float = 0.02) -> Model:
+    """Random weights made on the device by the seeded fill kernel (no files): for measurements."""
+    from .. import kernels as K
+    arch = find_architecture(config.architecture)
+    runtime = Runtime(dtype, device)
+    model = Model(arch.describe_model(config), runtime)
+    weights: Dict[str, torch.Tensor] = {}
+    for i, (name, ts) in enumerate(model.tensors().items()):
+        if ts.optional:
+            continue
+        dt = torch.float32 if ts.role in ("vector", "keep") else dtype
+        t = torch.empty(ts.shape, dtype=dt, device=runtime.device)
+        if ts.init == "ones":
+            t.fill_(1.0)
+        elif ts.init == "zeros":
+            t.zero_()
+        else:
+            K.fill_normal(t, (seed << 20) + i, std)
+        weights[name] = t
+    model.bind(weights)
+    return model

@@ -1,0 +1,197 @@
+"""Python launchers of the hand-written CUDA kernels (ctypes over the libraries csrc/build.py makes).
+
+Tensors are torch tensors used as plain device memory: every launcher checks device, dtype and
+layout, passes raw pointers and the current CUDA stream, and turns a non-zero status into a
+`KernelError`.  Nothing here computes: if a library cannot be built or loaded the call raises;
+there is no CPU or library-op fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_size_t, c_uint64, c_void_p
+from typing import Optional
+
+import torch
+
+from .csrc import build
+
+DT_F32, DT_BF16 = 0, 1
+_STATUS = {-1: "unsupported dtype", -2: "unsupported shape", -3: "misaligned pointer or stride",
+           -4: "size beyond the kernel's limit", -5: "device-side wait ran out"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status < 0:
+        raise KernelError(f"{what}: {_STATUS.get(status, f'status {status}')}")
+    raise KernelError(f"{what}: CUDA error {status} (cudaError_t)")
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return DT_F32
+    if dt == torch.bfloat16:
+        return DT_BF16
+    raise KernelError(f"kernels take float32 or bfloat16, not {dt}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must live on a CUDA device (no CPU path exists)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, is {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+
+
+_sigs_done = set()
+
+
+def _fn(libname: str, fname: str, argtypes):
+    lib = build.load(libname)
+    f = getattr(lib, fname)
+    key = (libname, fname)
+    if key not in _sigs_done:
+        f.argtypes = argtypes
+        f.restype = c_int
+        _sigs_done.add(key)
+    return f
+
+
+# ------------------------------------------------------------------ elementwise
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = table[ids[t]] as float32.  table [V,H] float32|bfloat16, ids int32 [T], out float32 [T,H]."""
+    _need(table, "table"); _need(ids, "ids", torch.int32); _need(out, "out", torch.float32)
+    f = _fn("elementwise", "stratum_embed_gather",
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), ids.numel(), table.shape[1],
+             table.shape[0], _stream()), "embed_gather")
+
+
+def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = rmsnorm(x[rows[r]] or x[r]) * gain.  x float32 [*,H], gain float32 [H]."""
+    _need(x, "x", torch.float32); _need(gain, "gain", torch.float32); _need(out, "out")
+    n_rows = out.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        if rows.numel() != n_rows:
+            raise KernelError("rmsnorm: rows and out disagree")
+    elif x.shape[0] != n_rows:
+        raise KernelError("rmsnorm: x and out disagree")
+    f = _fn("elementwise", "stratum_rmsnorm",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(_ptr(x), _ptr(gain), _ptr(rows), _ptr(out), dtype_code(out.dtype), n_rows, x.shape[-1],
+             c_float(eps), _stream()), "rmsnorm")
+
+
+def swiglu(gu: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r][j] = silu(gu[r][2j]) * gu[r][2j+1]."""
+    _need(gu, "gu"); _need(out, "out", gu.dtype)
+    f = _fn("elementwise", "stratum_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(gu), _ptr(out), dtype_code(gu.dtype), out.shape[0], out.shape[1], _stream()), "swiglu")
+
+
+def rope_store(qkv: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tensor,
+               block_table: Optional[torch.Tensor], inv_freq: Optional[torch.Tensor], interleaved: bool,
+               mscale: float, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+               n_q: int, n_kv: int, head_dim: int, page_tokens: int, write_cache: bool) -> None:
+    """Rotate q (in place) and k, and store k and v into the paged cache."""
+    _need(qkv, "qkv"); _need(token_pos, "token_pos", torch.int32); _need(token_seq, "token_seq", torch.int32)
+    n_pairs = 0 if inv_freq is None else inv_freq.numel()
+    if inv_freq is not None:
+        _need(inv_freq, "inv_freq", torch.float32)
+    if write_cache:
+        _need(k_cache, "k_cache", qkv.dtype); _need(v_cache, "v_cache", qkv.dtype)
+        _need(block_table, "block_table", torch.int32)
+    if qkv.shape[-1] != (n_q + 2 * n_kv) * head_dim:
+        raise KernelError("rope_store: qkv width is not (n_q + 2 n_kv) * head_dim")
+    f = _fn("elementwise", "stratum_rope_store",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(qkv), dtype_code(qkv.dtype), _ptr(token_pos), _ptr(token_seq), _ptr(block_table),
+             0 if block_table is None else block_table.stride(0), _ptr(inv_freq), n_pairs, int(interleaved),
+             c_float(mscale), _ptr(k_cache), _ptr(v_cache), qkv.shape[0], n_q, n_kv, head_dim, page_tokens,
+             int(write_cache), _stream()), "rope_store")
+
+
+def fill_normal(out: torch.Tensor, seed: int, std: float) -> None:
+    """Fill with std * N(0,1) from a counter-based generator keyed by (seed, element index)."""
+    _need(out, "out")
+    f = _fn("elementwise", "stratum_fill_normal", [c_void_p, c_int, c_size_t, c_uint64, c_float, c_void_p])
+    _check(f(_ptr(out), dtype_code(out.dtype), out.numel(), c_uint64(seed & (2**64 - 1)), c_float(std),
+             _stream()), "fill_normal")
+
+
+# ------------------------------------------------------------------ linear (any shape, CUDA cores)
+EPI_STORE, EPI_ADD_F32, EPI_STORE_F32 = 0, 1, 2
+
+
+def linear_simple(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                  epilogue: int) -> None:
+    """out (=|+=) x @ w.T + bias.  x [M,K] and w [N,K] of one dtype; bias float32; see EPI_*."""
+    _need(x, "x", contiguous=False); _need(w, "w", x.dtype); _need(out, "out", contiguous=False)
+    if x.stride(-1) != 1 or out.stride(-1) != 1:
+        raise KernelError("linear: rows must be contiguous")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N:
+        raise KernelError(f"linear: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} disagree")
+    want = x.dtype if epilogue == EPI_STORE else torch.float32
+    if out.dtype != want:
+        raise KernelError(f"linear: epilogue {epilogue} writes {want}, out is {out.dtype}")
+    f = _fn("linear_simple", "stratum_linear_simple",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), dtype_code(x.dtype), epilogue, M, N, K, x.stride(0),
+             out.stride(0), _stream()), "linear_simple")
+
+
+# ------------------------------------------------------------------ attention (any sizes, CUDA cores)
+def attention_simple(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, token_pos: torch.Tensor,
+                     token_seq: torch.Tensor, block_table: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int,
+                     head_dim: int, page_tokens: int, window: int, scale: float) -> None:
+    """Causal GQA attention of every token of the step over its sequence's cached keys."""
+    _need(qkv, "qkv"); _need(k_cache, "k_cache", qkv.dtype); _need(v_cache, "v_cache", qkv.dtype)
+    _need(out, "out", qkv.dtype); _need(block_table, "block_table", torch.int32)
+    f = _fn("attention_simple", "stratum_attention_simple",
+            [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(_ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), dtype_code(qkv.dtype), _ptr(token_pos),
+             _ptr(token_seq), _ptr(block_table), block_table.stride(0), _ptr(out), out.stride(0), qkv.shape[0],
+             n_q, n_kv, head_dim, page_tokens, window, c_float(scale), _stream()), "attention_simple")
+
+
+# ------------------------------------------------------------------ sampling
+def argmax(logits: torch.Tensor, ids: torch.Tensor, values: Optional[torch.Tensor] = None) -> None:
+    _need(logits, "logits", torch.float32, contiguous=False); _need(ids, "ids", torch.int32)
+    if values is not None:
+        _need(values, "values", torch.float32)
+    f = _fn("sampling", "stratum_argmax", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(ids), _ptr(values),
+             _stream()), "argmax")
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           uniform: torch.Tensor, ids: torch.Tensor, values: Optional[torch.Tensor] = None) -> None:
+    _need(logits, "logits", torch.float32, contiguous=False); _need(ids, "ids", torch.int32)
+    _need(temperature, "temperature", torch.float32); _need(top_k, "top_k", torch.int32)
+    _need(top_p, "top_p", torch.float32); _need(uniform, "uniform", torch.float32)
+    f = _fn("sampling", "stratum_sample",
+            [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(temperature), _ptr(top_k),
+             _ptr(top_p), _ptr(uniform), _ptr(ids), _ptr(values), _stream()), "sample")

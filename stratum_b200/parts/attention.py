@@ -1,0 +1,87 @@
+"""Grouped-query attention over the paged cache.
+
+q = Wq xn, k = Wk xn, v = Wv xn (+ biases); rotate q and k; append k and v to the cache at the
+token's position; score_t = (q_h . K_t[kv(h)]) * scale for the keys the token may see; softmax;
+o_h = sum_t p_t V_t[kv(h)]; residual += Wo o.  kv(h) = h / (n_heads / n_kv_heads).
+(stratum/native/stratum_arch_llama.inc.c:398-524.)  The three projections run as one matrix
+product over a weight made by stacking their rows (the reference fuses them at dispatch time,
+stratum/native/stratum_linear.h:1086-1121).
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from .. import kernels as K
+from ..cache.pages import PAGE_TOKENS
+from ..cache.store import KVSpec, LayerCache
+from .base import Mixer
+from .linear import ADD_TO_F32, STORE, Linear
+from .registry import find_part, register_part
+from .spec import PartSpec, TensorSpec
+
+
+@register_part("mixer", "gqa_attention")
+class GQAAttention(Mixer):
+    """params: hidden, n_heads, n_kv_heads, head_dim, bias, window (0 = all keys), scale (None =
+    1/sqrt(head_dim)), position (PartSpec of a position encoding, or None), prefix."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.hidden = int(spec["hidden"])
+        self.n_heads = int(spec["n_heads"])
+        self.n_kv_heads = int(spec["n_kv_heads"])
+        self.head_dim = int(spec["head_dim"])
+        self.bias = bool(spec.get("bias", False))
+        self.window = int(spec.get("window", 0) or 0)
+        scale = spec.get("scale")
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
+        if self.n_heads % self.n_kv_heads:
+            raise ValueError(f"attention: {self.n_heads} heads are not a multiple of {self.n_kv_heads} kv heads")
+        if self.head_dim % 2:
+            raise ValueError(f"attention: head_dim {self.head_dim} must be even")
+        pos: Optional[PartSpec] = spec.get("position")
+        self.position = find_part("position", pos.kind)(pos, runtime) if pos is not None else None
+        self.qkv: Optional[Linear] = None
+        self.o: Optional[Linear] = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        p, H, D = self.prefix, self.hidden, self.head_dim
+        t = {p + "q_proj.weight": TensorSpec((self.n_heads * D, H)),
+             p + "k_proj.weight": TensorSpec((self.n_kv_heads * D, H)),
+             p + "v_proj.weight": TensorSpec((self.n_kv_heads * D, H)),
+             p + "o_proj.weight": TensorSpec((H, self.n_heads * D))}
+        if self.bias:
+            t.update({p + "q_proj.bias": TensorSpec((self.n_heads * D,), role="vector"),
+                      p + "k_proj.bias": TensorSpec((self.n_kv_heads * D,), role="vector"),
+                      p + "v_proj.bias": TensorSpec((self.n_kv_heads * D,), role="vector"),
+                      p + "o_proj.bias": TensorSpec((H,), role="vector")})
+        return t
+
+    def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
+        p = self.prefix
+        w = torch.cat([weights[p + "q_proj.weight"], weights[p + "k_proj.weight"],
+                       weights[p + "v_proj.weight"]], dim=0).contiguous()
+        b = None
+        if self.bias:
+            b = torch.cat([weights[p + "q_proj.bias"], weights[p + "k_proj.bias"],
+                           weights[p + "v_proj.bias"]]).contiguous()
+        self.qkv = Linear(self.runtime, w, b)
+        self.o = Linear(self.runtime, weights[p + "o_proj.weight"], weights.get(p + "o_proj.bias"))
+
+    def cache_spec(self) -> KVSpec:
+        return KVSpec(self.n_kv_heads, self.head_dim, self.window)
+
+    def forward(self, xn: torch.Tensor, residual: torch.Tensor, step, cache: LayerCache) -> None:
+        qkv = self.qkv(xn, mode=STORE)
+        rot = self.position.rotary() if self.position is not None else None
+        K.rope_store(qkv, step.token_pos, step.token_seq, cache.block_table,
+                     None if rot is None else rot.inv_freq, bool(rot and rot.interleaved),
+                     1.0 if rot is None else rot.magnitude, cache.k, cache.v,
+                     self.n_heads, self.n_kv_heads, self.head_dim, PAGE_TOKENS, cache.writes)
+        out = self.runtime.empty(xn.shape[0], self.n_heads * self.head_dim)
+        from . import attention_dispatch
+        attention_dispatch.run(self, qkv, cache, step, out)
+        self.o(out, out=residual, mode=ADD_TO_F32)

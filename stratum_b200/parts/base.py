@@ -1,0 +1,116 @@
+"""Interfaces of the parts a decoder layer is put together from.
+
+A part is built from the sizes and constants in its `PartSpec` and from
+nothing else: it does not know which model or which layer it is in.  It
+declares the weight tensors it expects (`tensors()`), receives them
+(`bind()`), and computes (`forward`).  Constructing a part allocates nothing
+on a device, so a model's tensor list can be made on a machine without a GPU.
+
+Data conventions during a step:
+  * the residual stream `x` is float32 [tokens, hidden];
+  * norms turn it into the compute dtype (`runtime.dtype`) for the matrix products;
+  * a mixer or feed-forward adds its output into the residual stream in place.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, Mapping, Optional
+
+import torch
+
+from ..cache.store import CacheSpec, LayerCache
+from .spec import PartSpec, TensorSpec
+
+
+class Runtime:
+    """Where and in which dtype a model computes."""
+
+    def __init__(self, dtype: torch.dtype, device):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"compute dtype must be float32 or bfloat16, not {dtype}")
+        self.dtype = dtype
+        self.device = torch.device(device)
+
+    def empty(self, *shape: int, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
+
+
+class Part:
+    kind = ""
+
+    def __init__(self, spec: PartSpec, runtime: Optional[Runtime]):
+        self.spec = spec
+        self.runtime = runtime
+        self.prefix: str = spec.get("prefix", "")
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        """Expected weights, by name relative to the layer (the part's own prefix included)."""
+        return {}
+
+    def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
+        """Receive the tensors named by `tensors()` (optional ones may be absent)."""
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """float32 [T, hidden] -> compute dtype [T or len(rows), hidden]."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def rotary(self) -> Optional["RotaryTable"]:
+        """Frequencies for a mixer that rotates queries and keys, or None if this encoding does not rotate."""
+        return None
+
+    def add_to_embedding(self, x: torch.Tensor, step) -> None:
+        """Hook for encodings that act on the embedded tokens; the default does nothing."""
+
+
+class RotaryTable:
+    """inv_freq: float32 [n_pairs] on the device; pairs (2k,2k+1) if interleaved else (k, k+n_pairs)."""
+
+    def __init__(self, inv_freq: torch.Tensor, interleaved: bool, magnitude: float = 1.0):
+        self.inv_freq = inv_freq
+        self.interleaved = interleaved
+        self.magnitude = magnitude
+
+
+class Mixer(Part):
+    def cache_spec(self) -> Optional[CacheSpec]:
+        """What this mixer keeps per sequence between steps (keys and values, fixed-size state, nothing)."""
+        return None
+
+    def forward(self, xn: torch.Tensor, residual: torch.Tensor, step, cache: LayerCache) -> None:
+        """residual += mix(xn).  xn: compute dtype [T, hidden]; residual: float32 [T, hidden]."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, xn: torch.Tensor, residual: torch.Tensor, step) -> None:
+        """residual += ffn(xn)."""
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        """int32 [T] -> float32 [T, hidden]."""
+        raise NotImplementedError
+
+    def table(self) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Head(Part):
+    def bind_with_embedding(self, weights: Mapping[str, torch.Tensor], table: torch.Tensor) -> None:
+        self.bind(weights)
+
+    def forward(self, xn: torch.Tensor) -> torch.Tensor:
+        """compute dtype [n, hidden] -> float32 logits [n, vocab]."""
+        raise NotImplementedError
+
+
+class Arrangement:
+    """How a layer's norms, mixer and feed-forward are wired around the residual stream."""
+    kind = ""
+
+    def forward(self, layer, x: torch.Tensor, step, cache: LayerCache) -> None:
+        raise NotImplementedError

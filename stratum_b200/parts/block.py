@@ -1,0 +1,20 @@
+"""Arrangements: how a layer's parts are wired around the residual stream."""
+from __future__ import annotations
+
+import torch
+
+from ..cache.store import LayerCache
+from .base import Arrangement
+from .registry import register_part
+
+
+@register_part("arrangement", "prenorm_residual")
+class PreNormResidual(Arrangement):
+    """x += mixer(norm_a(x)); x += feed_forward(norm_b(x)): each norm stands before its part, on the
+    residual stream (stratum/native/stratum_arch_llama.inc.c:392-396, :524-532, :555)."""
+
+    def forward(self, layer, x: torch.Tensor, step, cache: LayerCache) -> None:
+        xn = layer.mixer_norm.forward(x)
+        layer.mixer.forward(xn, x, step, cache)
+        xn = layer.feed_forward_norm.forward(x)
+        layer.feed_forward.forward(xn, x, step)

@@ -1,0 +1,34 @@
+"""RMSNorm: y = x / sqrt(mean(x^2) + eps) * gain  (stratum/native/stratum_arch_llama.inc.c:45-76)."""
+from __future__ import annotations
+
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from .. import kernels as K
+from .base import Norm
+from .registry import register_part
+from .spec import TensorSpec
+
+
+@register_part("norm", "rmsnorm")
+class RMSNorm(Norm):
+    """params: size, eps, prefix (e.g. "input_layernorm.")."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.size = int(spec["size"])
+        self.eps = float(spec["eps"])
+        self.gain: Optional[torch.Tensor] = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        return {self.prefix + "weight": TensorSpec((self.size,), role="vector", init="ones")}
+
+    def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
+        self.gain = weights[self.prefix + "weight"]
+
+    def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        n = x.shape[0] if rows is None else rows.numel()
+        out = self.runtime.empty(n, self.size)
+        K.rmsnorm(x, self.gain, self.eps, out, rows)
+        return out

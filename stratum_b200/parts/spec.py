@@ -1,0 +1,91 @@
+"""Data that describes a model: which parts, with which sizes, in which order.
+
+An architecture turns its typed configuration into a `ModelSpec`; the engine
+builds the parts named there from the part registry.  Nothing in a spec is
+code: a layer names its mixer, feed-forward, norms and arrangement by kind,
+with their sizes and constants as parameters, so two layers of one model may
+use different kinds; and the order in which layers run is a list of its own.
+
+The reference classifies layers per index from its configuration
+(stratum/native/stratum_arch.h:82-105: full attention / SSM / next-token
+layers); this is the same idea with open-ended kinds.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, Mapping, Optional, Tuple
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    """One part: its registered kind and its sizes and constants."""
+    kind: str
+    params: Mapping[str, Any] = field(default_factory=dict)
+
+    def __getitem__(self, key: str) -> Any:
+        return self.params[key]
+
+    def get(self, key: str, default: Any = None) -> Any:
+        return self.params.get(key, default)
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    """One decoder layer: a mixer and a feed-forward, each behind a norm, in an arrangement."""
+    arrangement: str                 # registered arrangement kind, e.g. "prenorm_residual"
+    mixer: PartSpec
+    mixer_norm: PartSpec
+    feed_forward: PartSpec
+    feed_forward_norm: PartSpec
+    prefix: str                      # tensor-name prefix of this layer's weights
+
+
+@dataclass(frozen=True)
+class ScheduleEntry:
+    """One stop of the forward pass.
+
+    `layer` indexes ModelSpec.layers (a layer may appear more than once).
+    `cache_of`: the layer whose cache this stop reads; None means its own.  A stop
+    that reads another layer's cache does not write keys or state of its own.
+    """
+    layer: int
+    cache_of: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class ModelSpec:
+    hidden: int
+    vocab: int
+    embedding: PartSpec
+    layers: Tuple[LayerSpec, ...]
+    schedule: Tuple[ScheduleEntry, ...]
+    final_norm: PartSpec
+    head: PartSpec
+
+    def check(self) -> None:
+        n = len(self.layers)
+        if not self.schedule:
+            raise ValueError("model spec: empty schedule")
+        for e in self.schedule:
+            if not (0 <= e.layer < n):
+                raise ValueError(f"model spec: schedule names layer {e.layer}, model has {n}")
+            if e.cache_of is not None and not (0 <= e.cache_of < n):
+                raise ValueError(f"model spec: schedule reads the cache of layer {e.cache_of}, model has {n}")
+
+
+@dataclass(frozen=True)
+class TensorSpec:
+    """A weight tensor a part expects: its shape and what it is used as.
+
+    role: "matrix"  - an operand of a matrix product or an embedding table; kept in the
+                      compute dtype (bfloat16 on the bfloat16 path);
+          "vector"  - gains and biases; always held in float32 (exact from bfloat16);
+          "keep"    - held in the dtype the file stores (float32 stays float32);
+          "index"   - integer table, held as int32.
+    init: how random-weights mode fills it: "normal" (std from the caller), "ones", "zeros".
+    optional: absence is not an error (the part then does without it).
+    """
+    shape: Tuple[int, ...]
+    role: str = "matrix"
+    init: str = "normal"
+    optional: bool = False

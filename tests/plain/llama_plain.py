@@ -23,6 +23,11 @@ import numpy as np
 F64 = np.float64
 
 
+def _as_f32(a: np.ndarray) -> np.ndarray:
+    """Round to float32 and return as float64."""
+    return np.asarray(a, dtype=np.float32).astype(F64)
+
+
 # --------------------------------------------------------------------------- parts
 
 def embed(table: np.ndarray, token_ids: Sequence[int]) -> np.ndarray:
@@ -66,6 +71,7 @@ def rope_inv_freq(rope_dim: int, theta: float, scaling: Optional[dict] = None) -
     n_pairs = rope_dim // 2
     k = np.arange(n_pairs, dtype=F64)
     inv = 1.0 / (F64(theta) ** (2.0 * k / F64(rope_dim)))
+    inv = _as_f32(inv)          # the reference keeps the table in float32 (powf)
     if not scaling:
         return inv
     kind = scaling.get("rope_type", scaling.get("type", "default"))
@@ -73,7 +79,7 @@ def rope_inv_freq(rope_dim: int, theta: float, scaling: Optional[dict] = None) -
         return inv
     factor = F64(scaling["factor"])
     if kind == "linear":
-        return inv / factor
+        return _as_f32(inv / factor)
     if kind == "llama3":
         low = F64(scaling["low_freq_factor"])
         high = F64(scaling["high_freq_factor"])
@@ -88,7 +94,7 @@ def rope_inv_freq(rope_dim: int, theta: float, scaling: Optional[dict] = None) -
             else:
                 s = (orig / lam - low) / (high - low)
                 out[i] = (1.0 - s) * f / factor + s * f
-        return out
+        return _as_f32(out)
     raise ValueError(f"plain oracle: unknown rope scaling {kind!r}")
 
 
@@ -101,7 +107,8 @@ def apply_rope(x: np.ndarray, positions: np.ndarray, inv_freq: np.ndarray,
     (x0, x1) <- (x0*c - x1*s, x0*s + x1*c)."""
     x = np.array(x, dtype=F64, copy=True)
     n_pairs = inv_freq.shape[0]
-    ang = np.asarray(positions, dtype=F64)[:, None] * inv_freq[None, :]   # [T, n_pairs]
+    # angle = (float)pos * inv_k in float32, as the reference computes it (:141, :151)
+    ang = (np.asarray(positions, dtype=np.float32)[:, None] * inv_freq.astype(np.float32)[None, :]).astype(F64)
     c = np.cos(ang)[:, None, :]
     s = np.sin(ang)[:, None, :]
     if interleaved:
