@@ -51,9 +51,12 @@ class PagePool:
         return out
 
     def give(self, pages: List[int]) -> None:
-        for p in pages:
-            if not (0 <= p < self.n_pages) or not self._held[p]:
+        seen = set()
+        for p in pages:                       # check everything first: a refused give changes nothing
+            if not (0 <= p < self.n_pages) or not self._held[p] or p in seen:
                 raise CacheMisuse(f"page {p} given back but not held")
+            seen.add(p)
+        for p in pages:
             self._held[p] = False
         # keep the free list sorted descending so that take() stays lowest-first and deterministic
         self._free.extend(pages)

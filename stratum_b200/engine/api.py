@@ -1,0 +1,95 @@
+"""The Python entry point: open a model folder, step it, generate from it.
+
+    from stratum_b200 import Stratum
+    llm = Stratum("/path/to/model_dir", dtype="bfloat16", max_tokens=8192)
+    out = llm.generate([[1, 2, 3], [4, 5]], max_new_tokens=16)      # -> list of GenerationResult
+
+The reference has no library API (everything is static in one translation unit,
+CONTRIBUTING.md:52); the names follow its command line and environment switches.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..config.base import ModelConfig
+from ..sampling import Pcg32, Sampler, SamplingParams
+from .generate import Backend, GenerationResult, generate
+from .model import load_model, random_model_on_device
+from .step import Engine, StepEntry
+
+_DTYPES = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bfloat16, "bf16": torch.bfloat16}
+
+
+class _EngineBackend(Backend):
+    def __init__(self, engine: Engine, sampler: Sampler):
+        self.engine, self.sampler = engine, sampler
+        self.n_pages, self.max_seqs = engine.cache.n_pages, engine.cache.max_seqs
+        self.on_logits = None          # optional hook(logits [n, vocab] on the device, picked ids list)
+
+    def acquire(self) -> int:
+        return self.engine.acquire()
+
+    def release(self, slot: int) -> None:
+        self.engine.release(slot)
+
+    def step_and_pick(self, work, streams, params):
+        logits = self.engine.step([StepEntry(s, toks, [len(toks) - 1]) for s, toks in work])
+        ids, values = self.sampler.pick(logits, params, streams, want_values=True)
+        both = torch.stack([ids.to(torch.float64), values.to(torch.float64)]).cpu()     # one device-to-host copy
+        picked = [int(v) for v in both[0].tolist()]
+        if self.on_logits is not None:
+            self.on_logits(logits, picked)
+        return picked, both[1].tolist()
+
+
+class Stratum:
+    """A loaded model with its cache.  dtype: "bfloat16" (serving kernels) or "float32" (true 32-bit)."""
+
+    def __init__(self, model_dir: Optional[str] = None, dtype: str = "bfloat16", max_tokens: int = 4096,
+                 max_seqs: Optional[int] = None, device: str = "cuda", *, _model=None, _config=None):
+        if dtype not in _DTYPES:
+            raise ValueError(f"dtype {dtype!r} not one of {sorted(_DTYPES)}")
+        if not torch.cuda.is_available():
+            raise RuntimeError("stratum_b200 needs a CUDA device (sm_100a); there is no CPU path")
+        if _model is None:
+            _model, _config = load_model(model_dir, _DTYPES[dtype], device)
+        self.model, self.config = _model, _config
+        self.dtype = dtype
+        self.engine = Engine(self.model, max_tokens=max_tokens, max_seqs=max_seqs)
+        self.sampler = Sampler(self.model.runtime.device)
+        self._backend = _EngineBackend(self.engine, self.sampler)
+
+    @classmethod
+    def from_random(cls, config: ModelConfig, seed: int = 0, dtype: str = "bfloat16", max_tokens: int = 4096,
+                    max_seqs: Optional[int] = None, device: str = "cuda", std: float = 0.02) -> "Stratum":
+        """Random weights made on the device from (config, seed); nothing is read or written."""
+        model = random_model_on_device(config, seed, _DTYPES[dtype], device, std)
+        return cls(None, dtype, max_tokens, max_seqs, device, _model=model, _config=config)
+
+    # -- stepping by hand -----------------------------------------------------
+    def acquire(self) -> int:
+        return self.engine.acquire()
+
+    def release(self, slot: int) -> None:
+        self.engine.release(slot)
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        return self.engine.step(entries)
+
+    # -- generation ---------------------------------------------------------------
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens=16, stop_ids: Optional[Sequence[int]] = None,
+                 sampling: SamplingParams = SamplingParams(), max_batch: Optional[int] = None,
+                 on_token: Optional[Callable] = None, want_values: bool = False,
+                 on_logits: Optional[Callable] = None) -> List[GenerationResult]:
+        """stop_ids None: the configuration's eos ids; () : none.
+        on_logits(logits on the device [live sequences, vocab], picked ids) is called after every step."""
+        if stop_ids is None:
+            stop_ids = tuple(getattr(self.config, "eos_token_ids", ()) or ())
+        self._backend.on_logits = on_logits
+        try:
+            return generate(self._backend, prompts, max_new_tokens, stop_ids, sampling, max_batch, on_token,
+                            want_values)
+        finally:
+            self._backend.on_logits = None
