@@ -1,0 +1,279 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the Llama-3.1-8B shape on one B200, random bf16 weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--context 4096] [--layers L]
+    python bench.py --impl reference        # the reference arm (see below)
+
+Prints ONE JSON line.  `value` is decoded tokens per second at the given batch, with every
+sequence's cache filled to the given context at the end of the timed steps (so the timed steps
+read the longest keys of the run); a "step" is one decode step of the whole batch, timed on the
+device with CUDA events over exactly K steps after W warm-up steps.  `e2e` is the same through
+the Python entry point (`Stratum.generate`): host token ids in, host token ids out, every step's
+inputs copied from pinned host memory and its picked ids read back.  `prefill` times one prompt
+of 2,048 tokens; `roofline` relates the decode step to the bytes it must read (every weight it
+uses once, and the cached keys and values of the live requests); `points` adds batch 1 and 64.
+Weights (15 GB) exceed the 126 MB L2 by two orders of magnitude, so no flush is needed
+between timed steps.  Peaks come from MEASURED_PEAKS.json beside this file when it exists.
+
+Only one GPU is used; `--gpus N` with N > 1 prints a line saying so and exits with 2.
+The reference (shiaho777/stratum) is C11 with NEON/Accelerate/Metal for Apple Silicon, has no
+Python package metadata and no CUDA path, so it cannot be installed or run here: `--impl
+reference` prints {"impl": "reference", "unavailable": ...} and exits 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA_31_8B = {   # the Llama-3.1-8B shape named by the baseline's third configuration
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 32, "hidden_size": 4096, "intermediate_size": 14336,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "vocab_size": 128256,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "max_position_embeddings": 131072,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    "tie_word_embeddings": False, "attention_bias": False, "mlp_bias": False, "hidden_act": "silu",
+    "torch_dtype": "bfloat16",
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+PREFILL_TOKENS = 2048
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            raw = json.load(f)
+        return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]),
+                "source": "measured"}
+    except (OSError, KeyError, ValueError, TypeError):
+        return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def decode_bytes(cfg, n_layers, batch, context):
+    """Bytes one decode step has to read: each weight it uses once, and the live requests' keys and values."""
+    H, F, D = cfg.hidden, cfg.intermediate, cfg.head_dim
+    per_layer = (cfg.n_heads + 2 * cfg.n_kv_heads) * D * H + H * cfg.n_heads * D + 3 * H * F
+    weights = 2 * (n_layers * per_layer + cfg.vocab * H)
+    kv = 2 * batch * context * 2 * cfg.n_kv_heads * D * n_layers
+    return weights + kv
+
+
+def prefill_flops(cfg, n_layers, tokens):
+    H, F, D = cfg.hidden, cfg.intermediate, cfg.head_dim
+    per_layer = (cfg.n_heads + 2 * cfg.n_kv_heads) * D * H + H * cfg.n_heads * D + 3 * H * F
+    linear = 2 * tokens * n_layers * per_layer + 2 * cfg.vocab * H          # the head runs on one row
+    attention = n_layers * 2 * 2 * cfg.n_heads * D * (tokens * (tokens + 1) // 2)
+    return linear + attention
+
+
+def fill_to(llm, slots, n_tokens, vocab, rng, chunk=2048):
+    """Bring every slot's cache to n_tokens with random ids, in steps of at most `chunk` tokens each."""
+    from stratum_b200 import StepEntry
+    done = 0
+    while done < n_tokens:
+        n = min(chunk, n_tokens - done)
+        llm.step([StepEntry(s, rng.integers(0, vocab, size=n).tolist(), []) for s in slots])
+        done += n
+
+
+def time_decode(llm, batch, context, steps, warmup, vocab, rng):
+    """(ms per step, launches per step) for `steps` decode steps ending at `context` tokens per sequence."""
+    import torch
+    from stratum_b200 import StepEntry, kernels
+    slots = [llm.acquire() for _ in range(batch)]
+    try:
+        fill_to(llm, slots, context - steps - warmup, vocab, rng)
+        toks = rng.integers(0, vocab, size=(steps + warmup, batch)).tolist()
+        for i in range(warmup):
+            llm.step([StepEntry(s, [t], [0]) for s, t in zip(slots, toks[i])])
+        torch.cuda.synchronize()
+        l0 = kernels.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(warmup, warmup + steps):
+            llm.step([StepEntry(s, [t], [0]) for s, t in zip(slots, toks[i])])
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps, (kernels.launch_count() - l0) / steps
+    finally:
+        for s in slots:
+            llm.release(s)
+
+
+def time_prefill(llm, tokens, vocab, rng, repeats=3):
+    import torch
+    from stratum_b200 import StepEntry
+    best = None
+    for _ in range(repeats + 1):            # the first run warms up
+        slot = llm.acquire()
+        ids = rng.integers(0, vocab, size=tokens).tolist()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        llm.step([StepEntry(slot, ids, [tokens - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        llm.release(slot)
+        ms = e0.elapsed_time(e1)
+        best = ms if best is None else min(best, ms)
+    return best
+
+
+def time_e2e(llm, batch, context, steps, warmup, vocab, rng):
+    """Decode tokens per second through Stratum.generate: host ids in, host ids out."""
+    import torch
+    prompts = [rng.integers(0, vocab, size=context - steps - warmup).tolist() for _ in range(batch)]
+    marks = {}
+
+    def on_token(req, index, fed, picked, logit):
+        if index == warmup and req == batch - 1:
+            marks["t0"] = time.perf_counter()
+
+    torch.cuda.synchronize()
+    llm.generate(prompts, max_new_tokens=warmup + steps + 1, stop_ids=(), on_token=on_token)
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    return batch * steps / (t1 - marks["t0"])
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0 = all)")
+    ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "shiaho777/stratum is C11 + NEON/Accelerate/Metal for Apple Silicon with no Python "
+                          "package metadata and no CUDA path: it cannot be installed or run on this machine"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import numpy as np
+    import torch
+    from stratum_b200 import Stratum, kernels
+    from stratum_b200.config import LlamaConfig
+
+    raw = dict(LLAMA_31_8B)
+    n_layers_full = raw["num_hidden_layers"]
+    n_layers = args.layers or n_layers_full
+    raw["num_hidden_layers"] = n_layers
+    cfg = LlamaConfig.from_dict(raw)
+    peaks = load_peaks()
+    rng = np.random.default_rng(0)
+    biggest = max(args.batch, 1 if args.no_points else 64)
+    llm = Stratum.from_random(cfg, seed=0, dtype="bfloat16",
+                              max_tokens=biggest * (args.context + 64), max_seqs=biggest)
+    vocab = cfg.vocab
+
+    with ClockSampler() as clocks:
+        ms_step, launches = time_decode(llm, args.batch, args.context, args.steps, args.warmup, vocab, rng)
+    value = args.batch * 1000.0 / ms_step
+    clock_summary = clocks.summary()
+
+    e2e_value = time_e2e(llm, args.batch, args.context, args.steps, args.warmup, vocab, rng)
+    prefill_ms = time_prefill(llm, PREFILL_TOKENS, vocab, rng)
+    pf_flops = prefill_flops(cfg, n_layers, PREFILL_TOKENS)
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            ms_b, _ = time_decode(llm, b, args.context, max(8, args.steps // 2), 3, vocab, rng)
+            points[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 1)
+
+    step_bytes = decode_bytes(cfg, n_layers, args.batch, args.context)
+    achieved = step_bytes / (ms_step * 1e-3) / 1e9
+    meta_bytes = 4 * (7 * args.batch + 1 + args.batch * ((args.context + 63) // 64))
+    line = {
+        "metric": "decode tok/s @ batch 8 (Llama-3.1-8B bf16, context 4096)" if args.batch == 8 and
+                  args.context == 4096 else f"decode tok/s @ batch {args.batch} (Llama-3.1-8B bf16, context {args.context})",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: random-init weights N(0,0.02), uniform random token ids",
+        "config": {
+            "model": "Llama-3.1-8B shape", "layers": n_layers, "layers_full": n_layers_full,
+            "hidden": cfg.hidden, "heads": cfg.n_heads, "kv_heads": cfg.n_kv_heads, "head_dim": cfg.head_dim,
+            "intermediate": cfg.intermediate, "vocab": cfg.vocab, "global_batch": args.batch,
+            "seq_len": args.context, "rope_theta": cfg.rope_theta, "rope_scaling": "llama3 f8 lo1 hi4 orig8192",
+            "rms_eps": cfg.rms_eps, "tied": cfg.tie_embeddings, "cache_dtype": "bf16",
+            "parallelism": "single GPU", "l2": "weights (GBs) far exceed the 126 MB L2; no flush needed",
+            "peaks": peaks["source"]},
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": meta_bytes,
+                "d2h_bytes_per_step": 16 * args.batch},
+        "gpu_launches": int(round(launches * args.steps)),
+        "prefill": {"value": round(PREFILL_TOKENS * 1000.0 / prefill_ms, 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_ms, 3),
+                    "frac": round(pf_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clock_summary,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -24,8 +24,24 @@ class KernelError(RuntimeError):
     pass
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernel launches made through this module since import (launch counting for measurements)."""
+    return _launches
+
+
+def count_launches(n: int) -> None:
+    """Account for launches made on this module's behalf elsewhere (a replayed CUDA graph)."""
+    global _launches
+    _launches += n
+
+
 def _check(status: int, what: str) -> None:
+    global _launches
     if status == 0:
+        _launches += 1
         return
     if status < 0:
         raise KernelError(f"{what}: {_STATUS.get(status, f'status {status}')}")

@@ -1,0 +1,92 @@
+"""The sampling kernels alone against the plain sampling oracle."""
+import numpy as np
+import pytest
+import torch
+
+from plain import llama_plain as P
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(a, dtype):
+    return torch.tensor(a, dtype=dtype, device="cuda")
+
+
+def test_argmax_lowest_index_wins_ties():
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(0)
+    V = 128256 + 3
+    logits = rng.standard_normal((5, V)).astype(np.float32)
+    logits[0, [77, 5000, 120000]] = 9.0
+    logits[1, V - 1] = 11.0
+    logits[2, :] = -3.5                       # all equal: index 0
+    logits[3, 0] = 50.0
+    logits[4, [V - 2, V - 1]] = 12.0
+    ids = torch.empty(5, dtype=torch.int32, device="cuda")
+    vals = torch.empty(5, dtype=torch.float32, device="cuda")
+    K.argmax(_dev(logits, torch.float32), ids, vals)
+    assert ids.tolist() == [P.argmax_lowest(r) for r in logits] == [77, V - 1, 0, 0, V - 2]
+    assert vals.tolist() == [9.0, 11.0, -3.5, 50.0, 12.0]
+
+
+def _pick(logits, temp, top_k, top_p, us):
+    from stratum_b200 import kernels as K
+    n = len(us)
+    L = _dev(np.repeat(logits[None], n, 0), torch.float32)
+    ids = torch.empty(n, dtype=torch.int32, device="cuda")
+    K.sample(L, _dev([temp] * n, torch.float32), _dev([top_k] * n, torch.int32), _dev([top_p] * n, torch.float32),
+             _dev(us, torch.float32), ids)
+    return ids.tolist()
+
+
+@pytest.mark.parametrize("vocab", [320, 5000, 128256])
+def test_temperature_draws_follow_the_inverse_cdf(vocab):
+    rng = np.random.default_rng(vocab)
+    logits = (rng.standard_normal(vocab) * 2.0).astype(np.float32)
+    us = np.concatenate([rng.random(2000), [0.0, 0.999999]]).astype(np.float32)
+    got = _pick(logits, 0.8, 0, 1.0, us)
+    ids, probs = P.filtered_distribution(logits, np.float32(0.8), 0, 1.0)
+    cum = np.cumsum(probs)
+    bad = 0
+    for u, g in zip(us, got):
+        e = P.sample_inverse_cdf(ids, probs, float(u))
+        if g != e:
+            # only where u is within float32 summation noise of a boundary of the cumulative distribution
+            assert np.min(np.abs(cum - u)) < 2e-5, (u, g, e)
+            bad += 1
+    assert bad <= 20
+    # and the draws have the distribution's shape: the most likely token comes up about as often as it should
+    top = int(np.argmax(probs))
+    assert abs(sum(g == top for g in got) / len(got) - probs[top]) < 4 * np.sqrt(probs[top] / len(got)) + 1e-3
+
+
+@pytest.mark.parametrize("top_k, top_p", [(5, 1.0), (0, 0.7), (40, 0.9), (600, 0.95), (1, 1.0)])
+def test_top_k_top_p_candidates(top_k, top_p):
+    rng = np.random.default_rng(7)
+    vocab = 50000
+    logits = (rng.standard_normal(vocab) * 3.0).astype(np.float32)
+    logits[[10, 20, 30]] = logits.max() + 0.5             # a tie at the very top: lower ids come first
+    us = rng.random(600).astype(np.float32)
+    got = _pick(logits, 1.3, top_k, top_p, us)
+    k = top_k if 0 < top_k <= 512 else 512                # a filtered draw keeps at most 512 candidates
+    ids, probs = P.filtered_distribution(logits, np.float32(1.3), k, top_p)
+    cum = np.cumsum(probs)
+    assert set(got) <= set(ids.tolist())
+    for u, g in zip(us, got):
+        e = P.sample_inverse_cdf(ids, probs, float(u))
+        assert g == e or np.min(np.abs(cum - u)) < 2e-5, (u, g, e)
+    if top_k == 1:
+        assert set(got) == {10}
+
+
+def test_greedy_rows_and_sampled_rows_in_one_launch():
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(3)
+    logits = rng.standard_normal((3, 1000)).astype(np.float32)
+    ids = torch.empty(3, dtype=torch.int32, device="cuda")
+    K.sample(_dev(logits, torch.float32), _dev([0.0, 1.0, -1.0], torch.float32), _dev([0, 0, 0], torch.int32),
+             _dev([1.0, 1.0, 1.0], torch.float32), _dev([0.5, 0.5, 0.5], torch.float32), ids)
+    got = ids.tolist()
+    assert got[0] == int(logits[0].argmax()) and got[2] == int(logits[2].argmax())
+    i, p = P.filtered_distribution(logits[1], 1.0, 0, 1.0)
+    assert got[1] == P.sample_inverse_cdf(i, p, 0.5)
