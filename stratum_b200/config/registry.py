@@ -36,6 +36,7 @@ def register_architecture(arch: Architecture, *, replace: bool = False) -> Archi
 
 
 def registered_architectures() -> List[Architecture]:
+    from .. import architectures  # noqa: F401
     return list(_ARCHITECTURES)
 
 
@@ -50,6 +51,7 @@ def architecture_name(raw: Dict[str, Any]) -> str:
 
 
 def find_architecture(raw_or_name) -> Architecture:
+    from .. import architectures  # noqa: F401  (the built-in architectures register themselves on import)
     name = raw_or_name if isinstance(raw_or_name, str) else architecture_name(raw_or_name)
     for arch in _ARCHITECTURES:
         if name in arch.names:

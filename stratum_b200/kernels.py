@@ -153,7 +153,7 @@ def fill_normal(out: torch.Tensor, seed: int, std: float) -> None:
 
 
 # ------------------------------------------------------------------ linear (any shape, CUDA cores)
-EPI_STORE, EPI_ADD_F32, EPI_STORE_F32 = 0, 1, 2
+EPI_STORE, EPI_ADD_F32, EPI_STORE_F32, EPI_SWIGLU = 0, 1, 2, 3
 
 
 def linear_simple(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
@@ -175,6 +175,34 @@ def linear_simple(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(f(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), dtype_code(x.dtype), epilogue, M, N, K, x.stride(0),
              out.stride(0), _stream()), "linear_simple")
+
+
+def _linear_shapes(x, w, bias, out, epilogue, what):
+    _need(x, "x", contiguous=False); _need(w, "w", x.dtype); _need(out, "out", contiguous=False)
+    if x.stride(-1) != 1 or out.stride(-1) != 1:
+        raise KernelError(f"{what}: rows must be contiguous")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    M, Kd = x.shape
+    N = w.shape[0]
+    width = N // 2 if epilogue == EPI_SWIGLU else N
+    if w.shape[1] != Kd or out.shape[0] != M or out.shape[1] != width:
+        raise KernelError(f"{what}: shapes x{tuple(x.shape)} w{tuple(w.shape)} out{tuple(out.shape)} disagree")
+    want = x.dtype if epilogue in (EPI_STORE, EPI_SWIGLU) else torch.float32
+    if out.dtype != want:
+        raise KernelError(f"{what}: epilogue {epilogue} writes {want}, out is {out.dtype}")
+    return M, N, Kd
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                epilogue: int) -> None:
+    """bfloat16, at most 32 rows of x: the weight-streaming tensor-core kernel (see EPI_*)."""
+    M, N, Kd = _linear_shapes(x, w, bias, out, epilogue, "gemm_skinny")
+    _need(x, "x", torch.bfloat16, contiguous=False)
+    f = _fn("gemm_skinny", "stratum_gemm_skinny",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), epilogue, M, N, Kd, x.stride(0), out.stride(0), _stream()),
+           "gemm_skinny")
 
 
 # ------------------------------------------------------------------ attention (any sizes, CUDA cores)

@@ -1,4 +1,10 @@
-"""Which matrix-product kernel serves a given call."""
+"""Which matrix-product kernel serves a given call.
+
+float32 always takes the CUDA-core kernel with the fixed summation order (the true 32-bit
+path).  bfloat16: up to SKINNY_MAX_ROWS rows of x take the weight-streaming kernel (decode
+steps), more rows take the tensor-core tile kernel (prompts), and any shape either refuses
+(rows not 16-byte aligned) falls back to the CUDA-core kernel.
+"""
 from __future__ import annotations
 
 from typing import Optional
@@ -7,6 +13,24 @@ import torch
 
 from .. import kernels as K
 
+STORE, ADD_TO_F32, STORE_F32, SWIGLU = K.EPI_STORE, K.EPI_ADD_F32, K.EPI_STORE_F32, K.EPI_SWIGLU
+SKINNY_MAX_ROWS = 32
+
+
+def _aligned(x: torch.Tensor, w: torch.Tensor) -> bool:
+    k = w.shape[1]
+    return (k % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
 
 def run(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int) -> None:
+    """out (=|+=) epilogue(x @ w.T + bias); see the EPI_* modes in kernels.py."""
+    if x.dtype == torch.bfloat16 and _aligned(x, w):
+        if x.shape[0] <= SKINNY_MAX_ROWS:
+            K.gemm_skinny(x, w, bias, out, mode)
+            return
+    if mode == SWIGLU:
+        gu = torch.empty((x.shape[0], w.shape[0]), dtype=x.dtype, device=x.device)
+        K.linear_simple(x, w, bias, gu, STORE)
+        K.swiglu(gu, out)
+        return
     K.linear_simple(x, w, bias, out, mode)

@@ -14,7 +14,7 @@ import torch
 from .. import kernels as K
 from .base import Runtime
 
-STORE, ADD_TO_F32, STORE_F32 = K.EPI_STORE, K.EPI_ADD_F32, K.EPI_STORE_F32
+STORE, ADD_TO_F32, STORE_F32, SWIGLU = K.EPI_STORE, K.EPI_ADD_F32, K.EPI_STORE_F32, K.EPI_SWIGLU
 
 
 class Linear:
@@ -27,13 +27,14 @@ class Linear:
         self.out_features, self.in_features = weight.shape
 
     def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, mode: int = STORE) -> torch.Tensor:
-        """mode STORE: new tensor of x's dtype; ADD_TO_F32: out (float32) += y; STORE_F32: float32 out."""
+        """mode STORE: new tensor of x's dtype; ADD_TO_F32: out (float32) += y; STORE_F32: float32 out;
+        SWIGLU: rows of W alternate gate and up, out[m][j] = silu(y[m][2j]) * y[m][2j+1] in x's dtype."""
         M = x.shape[0]
         if out is None:
             if mode == ADD_TO_F32:
                 raise ValueError("ADD_TO_F32 needs the tensor to add into")
-            out = self.runtime.empty(M, self.out_features,
-                                     dtype=x.dtype if mode == STORE else torch.float32)
+            width = self.out_features // 2 if mode == SWIGLU else self.out_features
+            out = self.runtime.empty(M, width, dtype=torch.float32 if mode == STORE_F32 else x.dtype)
         if M == 0:
             return out
         from . import gemm_dispatch

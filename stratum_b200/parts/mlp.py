@@ -10,9 +10,8 @@ from typing import Dict, Mapping, Optional
 
 import torch
 
-from .. import kernels as K
 from .base import FeedForward
-from .linear import ADD_TO_F32, STORE, Linear
+from .linear import ADD_TO_F32, SWIGLU, Linear
 from .registry import register_part
 from .spec import TensorSpec
 
@@ -52,7 +51,5 @@ class SwiGLU(FeedForward):
         self.down = Linear(self.runtime, weights[p + "down_proj.weight"], weights.get(p + "down_proj.bias"))
 
     def forward(self, xn: torch.Tensor, residual: torch.Tensor, step) -> None:
-        gu = self.gate_up(xn, mode=STORE)
-        a = self.runtime.empty(xn.shape[0], self.intermediate)
-        K.swiglu(gu, a)
+        a = self.gate_up(xn, mode=SWIGLU)
         self.down(a, out=residual, mode=ADD_TO_F32)

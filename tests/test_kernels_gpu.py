@@ -1,0 +1,294 @@
+"""Each kernel alone against its plain reference, at sizes other than the engine tests use."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from plain import llama_plain as P
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def dev(a, dtype=torch.float32):
+    return torch.tensor(np.asarray(a), dtype=dtype, device="cuda")
+
+
+def as64(t):
+    return t.detach().float().cpu().numpy().astype(np.float64)
+
+
+def rel_err(got, ref):
+    return float(np.max(np.abs(got - ref)) / (np.max(np.abs(ref)) + 1e-30))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden", [100, 4096, 5120 + 8])
+def test_rmsnorm(dtype, hidden):
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(hidden)
+    x = dev(rng.standard_normal((7, hidden)) * 3.0)
+    gain = dev(rng.random(hidden) + 0.5)
+    out = torch.empty(7, hidden, dtype=DT[dtype], device="cuda")
+    K.rmsnorm(x, gain, 1e-5, out)
+    ref = P.rms_norm(as64(x), as64(gain), 1e-5)
+    assert rel_err(as64(out), ref) < (2e-6 if dtype == "float32" else 5e-3)
+    rows = dev([5, 0, 5], torch.int32)
+    out2 = torch.empty(3, hidden, dtype=DT[dtype], device="cuda")
+    K.rmsnorm(x, gain, 1e-5, out2, rows)
+    assert torch.equal(out2, out[[5, 0, 5]])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed_gather(dtype):
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(1)
+    table = dev(rng.standard_normal((1000, 72)), DT[dtype])
+    ids = dev([999, 0, 17, 17], torch.int32)
+    out = torch.empty(4, 72, dtype=torch.float32, device="cuda")
+    K.embed_gather(table, ids, out)
+    assert torch.equal(out, table[[999, 0, 17, 17]].float())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu(dtype):
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(2)
+    g, u = rng.standard_normal((5, 176)) * 4, rng.standard_normal((5, 176))
+    gu = dev(np.stack([g, u], axis=2).reshape(5, 352), DT[dtype])
+    out = torch.empty(5, 176, dtype=DT[dtype], device="cuda")
+    K.swiglu(gu, out)
+    g64, u64 = as64(gu)[:, 0::2], as64(gu)[:, 1::2]
+    assert rel_err(as64(out), P.silu(g64) * u64) < (1e-6 if dtype == "float32" else 5e-3)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M,N,K_", [(1, 50, 24), (70, 130, 96), (3, 1000, 176), (129, 64, 520)])
+def test_linear_simple(dtype, M, N, K_):
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(M * N)
+    x = dev(rng.standard_normal((M, K_)), DT[dtype])
+    w = dev(rng.standard_normal((N, K_)) * 0.1, DT[dtype])
+    b = dev(rng.standard_normal(N))
+    ref = P.linear(as64(x), as64(w), as64(b))
+    tol = 1e-5 if dtype == "float32" else 6e-3
+    out = torch.empty(M, N, dtype=DT[dtype], device="cuda")
+    K.linear_simple(x, w, b, out, K.EPI_STORE)
+    assert rel_err(as64(out), ref) < tol
+    res = dev(rng.standard_normal((M, N)))
+    keep = as64(res)
+    K.linear_simple(x, w, None, res, K.EPI_ADD_F32)
+    assert rel_err(as64(res), keep + P.linear(as64(x), as64(w))) < 1e-5
+    out32 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    K.linear_simple(x, w, b, out32, K.EPI_STORE_F32)
+    assert rel_err(as64(out32), ref) < 1e-5
+    # a row's value does not depend on the rows beside it
+    one = torch.empty(1, N, dtype=torch.float32, device="cuda")
+    K.linear_simple(x[M - 1:M], w, b, one, K.EPI_STORE_F32)
+    assert torch.equal(one[0], out32[M - 1])
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 13, 16, 32])
+@pytest.mark.parametrize("N,K_", [(48, 64), (1000, 200), (4096 + 16, 4096), (2 * 177, 96)])
+def test_gemm_skinny(M, N, K_):
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(M + N)
+    x = dev(rng.standard_normal((M, K_)), torch.bfloat16)
+    w = dev(rng.standard_normal((N, K_)) * 0.1, torch.bfloat16)
+    b = dev(rng.standard_normal(N))
+    ref = P.linear(as64(x), as64(w), as64(b))
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    K.gemm_skinny(x, w, b, out, K.EPI_STORE)
+    assert rel_err(as64(out), ref) < 6e-3
+    out32 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    K.gemm_skinny(x, w, b, out32, K.EPI_STORE_F32)
+    assert rel_err(as64(out32), ref) < 2e-5
+    res = dev(rng.standard_normal((M, N)))
+    keep = as64(res)
+    K.gemm_skinny(x, w, None, res, K.EPI_ADD_F32)
+    assert rel_err(as64(res), keep + P.linear(as64(x), as64(w))) < 2e-5
+    act = torch.empty(M, N // 2, dtype=torch.bfloat16, device="cuda")
+    K.gemm_skinny(x, w, b, act, K.EPI_SWIGLU)
+    r16 = as64(dev(ref, torch.bfloat16))
+    assert rel_err(as64(act), P.silu(r16[:, 0::2]) * r16[:, 1::2]) < 2e-2
+    # the same row alone gives the same bits
+    one = torch.empty(1, N, dtype=torch.float32, device="cuda")
+    K.gemm_skinny(x[M - 1:M], w, b, one, K.EPI_STORE_F32)
+    assert torch.equal(one[0], out32[M - 1])
+
+
+def test_gemm_skinny_refuses_what_it_cannot_do():
+    from stratum_b200 import kernels as K
+    x = torch.zeros(2, 20, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(8, 20, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros(2, 8, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(K.KernelError, match="shape"):
+        K.gemm_skinny(x, w, None, out, K.EPI_STORE)            # K = 20 is no multiple of 8
+    x = torch.zeros(40, 16, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(8, 16, dtype=torch.bfloat16, device="cuda")
+    out = torch.zeros(40, 8, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(K.KernelError, match="limit"):
+        K.gemm_skinny(x, w, None, out, K.EPI_STORE)
+
+
+# ------------------------------------------------------------------ rope + cache write, attention
+def _paged(rng, n_pages, n_kv, hd, dtype):
+    return (torch.zeros(n_pages, n_kv, 64, hd, dtype=DT[dtype], device="cuda"),
+            torch.zeros(n_pages, n_kv, 64, hd, dtype=DT[dtype], device="cuda"))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_rope_store_rotates_and_lands_in_the_right_rows(dtype, interleaved):
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(4)
+    n_q, n_kv, hd, rope_dim = 6, 2, 48, 32
+    # two sequences: the first continues at position 130 with 3 tokens, the second starts with 2
+    pos = [130, 131, 132, 0, 1]
+    seq = [0, 0, 0, 1, 1]
+    table = np.array([[7, 3, 9], [5, -1, -1]], dtype=np.int32)       # pages in an order of their own
+    qkv = dev(rng.standard_normal((5, (n_q + 2 * n_kv) * hd)), DT[dtype])
+    before = as64(qkv)
+    inv = P.rope_inv_freq(rope_dim, 10000.0).astype(np.float32)
+    kc, vc = _paged(rng, 10, n_kv, hd, dtype)
+    K.rope_store(qkv, dev(pos, torch.int32), dev(seq, torch.int32), dev(table, torch.int32), dev(inv), interleaved,
+                 1.0, kc, vc, n_q, n_kv, hd, 64, True)
+    heads = before.reshape(5, n_q + 2 * n_kv, hd)
+    q_ref = P.apply_rope(heads[:, :n_q], np.array(pos), inv.astype(np.float64), interleaved)
+    k_ref = P.apply_rope(heads[:, n_q:n_q + n_kv], np.array(pos), inv.astype(np.float64), interleaved)
+    v_ref = heads[:, n_q + n_kv:]
+    tol = 2e-6 if dtype == "float32" else 5e-3
+    assert rel_err(as64(qkv).reshape(5, -1, hd)[:, :n_q], q_ref) < tol
+    assert np.array_equal(as64(qkv).reshape(5, -1, hd)[:, n_q:], heads[:, n_q:])       # k and v stay as projected
+    for t in range(5):
+        page = table[seq[t], pos[t] // 64]
+        assert rel_err(as64(kc[page, :, pos[t] % 64]), k_ref[t]) < tol
+        assert np.array_equal(as64(vc[page, :, pos[t] % 64]), v_ref[t])
+    written = {(int(table[s, p // 64]), p % 64) for s, p in zip(seq, pos)}
+    mask = torch.ones(10, 64, dtype=torch.bool)
+    for pg, r in written:
+        mask[pg, r] = False
+    assert float(kc.float().abs().sum(dim=(1, 3)).cpu()[mask].sum()) == 0.0            # nothing else was touched
+
+
+def _attention_case(rng, lens_before, n_new, n_q, n_kv, hd, dtype, window=0, spike=None):
+    """Build a paged cache holding random keys/values and run the kernel for the new tokens."""
+    from stratum_b200 import kernels as K
+    B = len(lens_before)
+    total = [a + b for a, b in zip(lens_before, n_new)]
+    n_pages = sum((t + 63) // 64 for t in total)
+    order = rng.permutation(n_pages).tolist()
+    kc, vc = _paged(rng, n_pages, n_kv, hd, dtype)
+    width = max((t + 63) // 64 for t in total)
+    table = np.full((B, width), -1, dtype=np.int32)
+    ks, vs, qs = [], [], []
+    for s in range(B):
+        k = rng.standard_normal((total[s], n_kv, hd))
+        v = rng.standard_normal((total[s], n_kv, hd))
+        q = rng.standard_normal((n_new[s], n_q, hd))
+        if spike is not None:
+            spike(s, q, k, v)
+        k = as64(dev(k, DT[dtype])); v = as64(dev(v, DT[dtype])); q = as64(dev(q, DT[dtype]))
+        for p in range((total[s] + 63) // 64):
+            pg = order.pop()
+            table[s, p] = pg
+            n = min(64, total[s] - 64 * p)
+            kc[pg, :, :n] = dev(k[64 * p:64 * p + n].transpose(1, 0, 2), DT[dtype])
+            vc[pg, :, :n] = dev(v[64 * p:64 * p + n].transpose(1, 0, 2), DT[dtype])
+        ks.append(k); vs.append(v); qs.append(q)
+    T = sum(n_new)
+    qkv = torch.zeros(T, (n_q + 2 * n_kv) * hd, dtype=DT[dtype], device="cuda")
+    pos, seq, r = [], [], 0
+    for s in range(B):
+        qkv[r:r + n_new[s], :n_q * hd] = dev(qs[s].reshape(n_new[s], -1), DT[dtype])
+        pos += list(range(lens_before[s], total[s])); seq += [s] * n_new[s]; r += n_new[s]
+    ref = []
+    for s in range(B):
+        scale = 1.0 / math.sqrt(hd)
+        for i in range(n_new[s]):
+            p = lens_before[s] + i
+            lo = 0 if window <= 0 else max(0, p - window + 1)
+            row = np.zeros((n_q, hd))
+            for h in range(n_q):
+                kv = h // (n_q // n_kv)
+                sc = ks[s][lo:p + 1, kv] @ qs[s][i, h] * scale
+                row[h] = P.softmax(sc) @ vs[s][lo:p + 1, kv]
+            ref.append(row.reshape(-1))
+    return dict(qkv=qkv, kc=kc, vc=vc, pos=dev(pos, torch.int32), seq=dev(seq, torch.int32),
+                table=dev(table, torch.int32), ref=np.stack(ref), T=T)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_q,n_kv,hd", [(8, 2, 128), (5, 5, 48), (6, 1, 16), (2, 1, 256)])
+def test_attention_simple(dtype, n_q, n_kv, hd):
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(hd)
+    c = _attention_case(rng, [0, 130, 63, 700], [70, 1, 3, 1], n_q, n_kv, hd, dtype)
+    out = torch.empty(c["T"], n_q * hd, dtype=DT[dtype], device="cuda")
+    K.attention_simple(c["qkv"], c["kc"], c["vc"], c["pos"], c["seq"], c["table"], out, n_q, n_kv, hd, 64, 0,
+                       1.0 / math.sqrt(hd))
+    assert rel_err(as64(out), c["ref"]) < (3e-6 if dtype == "float32" else 8e-3)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_finds_one_far_key_among_hundreds(dtype):
+    """Scale one query and one key so that a single far score dominates: the output must be that key's value."""
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(11)
+    n_q, n_kv, hd = 4, 2, 64
+    far = {0: 3, 1: 517}                      # sequence -> position of the key to find
+
+    def spike(s, q, k, v):
+        d = rng.standard_normal(hd)
+        d /= np.linalg.norm(d)
+        k[far[s], :, :] = d * 12.0
+        q[-1, :, :] = d * 12.0                # the last new token looks for it
+
+    c = _attention_case(rng, [699, 600], [1, 2], n_q, n_kv, hd, dtype, spike=spike)
+    out = torch.empty(c["T"], n_q * hd, dtype=DT[dtype], device="cuda")
+    K.attention_simple(c["qkv"], c["kc"], c["vc"], c["pos"], c["seq"], c["table"], out, n_q, n_kv, hd, 64, 0,
+                       1.0 / math.sqrt(hd))
+    assert rel_err(as64(out), c["ref"]) < (3e-6 if dtype == "float32" else 8e-3)
+    # and the reference itself is (almost) that one value row: the case does test the far key
+    v_far = as64(c["vc"][c["table"][0, far[0] // 64].item(), 0, far[0] % 64])
+    assert np.max(np.abs(c["ref"][0][:hd] - v_far)) < 1e-3
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_window_edge(dtype):
+    """With a window of W keys the key at p-W+1 counts and the key at p-W does not."""
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(12)
+    n_q, n_kv, hd, W = 2, 1, 32, 100
+    p = 299
+
+    def spike(s, q, k, v):
+        d = rng.standard_normal(hd)
+        d /= np.linalg.norm(d)
+        q[-1, :, :] = d * 10.0
+        k[p - W + 1 if s == 0 else p - W, :, :] = d * 10.0       # just inside / just outside
+
+    c = _attention_case(rng, [p, p], [1, 1], n_q, n_kv, hd, dtype, window=W, spike=spike)
+    out = torch.empty(c["T"], n_q * hd, dtype=DT[dtype], device="cuda")
+    K.attention_simple(c["qkv"], c["kc"], c["vc"], c["pos"], c["seq"], c["table"], out, n_q, n_kv, hd, 64, W,
+                       1.0 / math.sqrt(hd))
+    assert rel_err(as64(out), c["ref"]) < (3e-6 if dtype == "float32" else 8e-3)
+    inside = as64(c["vc"][c["table"][0, (p - W + 1) // 64].item(), 0, (p - W + 1) % 64])
+    outside = as64(c["vc"][c["table"][1, (p - W) // 64].item(), 0, (p - W) % 64])
+    assert np.max(np.abs(c["ref"][0][:hd] - inside)) < 1e-2          # found
+    assert np.max(np.abs(c["ref"][1][:hd] - outside)) > 0.1          # not seen
+
+
+def test_fill_normal_is_seeded_and_normal():
+    from stratum_b200 import kernels as K
+    a = torch.empty(1 << 20, dtype=torch.float32, device="cuda")
+    b = torch.empty(1 << 20, dtype=torch.float32, device="cuda")
+    K.fill_normal(a, 5, 0.02); K.fill_normal(b, 5, 0.02)
+    assert torch.equal(a, b)
+    K.fill_normal(b, 6, 0.02)
+    assert not torch.equal(a, b)
+    assert abs(float(a.mean())) < 1e-4 and abs(float(a.std()) - 0.02) < 2e-4
+    c = torch.empty(1 << 20, dtype=torch.bfloat16, device="cuda")
+    K.fill_normal(c, 5, 0.02)
+    assert torch.equal(c, a.bfloat16())
