@@ -1,0 +1,325 @@
+// Causal grouped-query attention over the paged bfloat16 cache on tensor cores, for prompts and for
+// decode steps, with the keys of long sequences split across warps (scratch partials + a merge).
+//
+// One warp owns one work item: up to 16 query rows that share a kv head (R consecutive new tokens of
+// a sequence x the heads of the group), and one contiguous range of that sequence's keys.  Scores
+// and the value sum are mma.sync.m16n8k16 (bf16 in, float32 accumulate); maxima, exponentials,
+// denominators and the running rescale are float32 (online softmax); nothing goes through
+// shared memory.  For query head h at position p:  score_t = (q_h . K_t[kv(h)]) * scale over keys
+// t in [lo, p];  p_t = softmax;  o_h = sum_t p_t V_t[kv(h)]
+// (stratum/native/stratum_arch_llama.inc.c:435-514; kv(h) = h / (Nq/Nk), :444).
+//
+// Fragments straight from global memory.  Lane (g = lane/4, t = lane%4) loads, of every 32-wide
+// chunk of the head dimension, the 8 contiguous values 8t..8t+7 of its row: for Q rows g and g+8
+// (the A operand), for K rows key0+g and key0+8+g (the B operand of Q K^T; a dot product may
+// visit the head dimension in any order as long as Q and K agree).  V has keys along k, which is
+// the transposed arrangement; each 32-bit register of the same kind of load is an 8x8 matrix that
+// movmatrix transposes into a B fragment whose column n stands for dimension 8(n/2)+2i+(n%2) of
+// the chunk.  The accumulator for output tile (chunk c, register i) then holds, in lane (g,t),
+// dimensions 32c+8t+2i and +1: the four tiles of a chunk give 8 contiguous output values per row.
+//
+// Key ranges: the keys of a sequence are cut into `chunk` keys per split (a multiple of 64).  With
+// one split the normalised output is written directly.  With more, every split writes its
+// unnormalised value sum, its maximum and its denominator to scratch, and a second kernel merges
+// them in split order.
+#include <math.h>
+
+#include "common.cuh"
+
+#define AM_WARPS 4
+
+__device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg((const uint4*)p); }
+
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+               "{%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t transpose8x8(uint32_t a) {
+  uint32_t d;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+  return d;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ uint32_t reg_of(const uint4& v, int i) {
+  return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w));
+}
+
+struct AttnParams {
+  const bf16* q; int ldq;              // [tokens][ldq]: query heads first
+  const bf16* k_cache; const bf16* v_cache;   // [pages][Nk][page_tokens][Hd]
+  const int* token_pos;                // [tokens]
+  const int* block_table; int bt_stride;      // [seqs][bt_stride]
+  const int* qb_seq; const int* qb_tok0; const int* qb_ntok;   // query blocks; null = one token per sequence
+  int n_qblocks;
+  bf16* out; int ldo;                  // [tokens][ldo]
+  float* part_o; float* part_ml;       // scratch: [(token*Nq + head)*n_splits + split][Hd] and [..][2]
+  int n_q, n_kv, head_dim, page_tokens, window;
+  int rows_per_token, head_groups, tokens_per_block;
+  int n_splits, chunk;
+  float scale;
+};
+
+template <int CH>
+__global__ void __launch_bounds__(AM_WARPS * 32)
+attention_mma_kernel(const AttnParams P) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  long long item = (long long)blockIdx.x * AM_WARPS + warp;
+  const long long n_items = (long long)P.n_qblocks * P.n_kv * P.head_groups * P.n_splits;
+  if (item >= n_items) return;
+  const int split = (int)(item % P.n_splits); item /= P.n_splits;
+  const int hg = (int)(item % P.head_groups); item /= P.head_groups;
+  const int kvh = (int)(item % P.n_kv); item /= P.n_kv;
+  const int qb = (int)item;
+  const int seq = P.qb_seq ? P.qb_seq[qb] : qb;
+  const int tok0 = P.qb_tok0 ? P.qb_tok0[qb] : qb;
+  const int ntok = P.qb_ntok ? P.qb_ntok[qb] : 1;
+  if (seq < 0) return;                                    // padding
+  const int gs = P.n_q / P.n_kv;
+  const int Hd = P.head_dim;
+
+  // the two rows of this lane: r = g and g + 8;  row -> (token of the block, head of the group)
+  int row_tok[2], row_head[2], row_pos[2];
+  bool row_ok[2];
+#pragma unroll
+  for (int e = 0; e < 2; e++) {
+    const int r = g + 8 * e;
+    const int tr = r / P.rows_per_token, hr = r % P.rows_per_token;
+    const int hq = hg * 16 + hr;                          // head within the group
+    row_ok[e] = tr < ntok && tr < P.tokens_per_block && hq < gs;
+    row_tok[e] = tok0 + (row_ok[e] ? tr : 0);
+    row_head[e] = kvh * gs + (row_ok[e] ? hq : 0);
+    row_pos[e] = P.token_pos[row_tok[e]];
+  }
+  const int first_pos = P.token_pos[tok0];
+  const int last_pos = first_pos + ntok - 1;
+  const int lo_block = (P.window > 0 && first_pos - P.window + 1 > 0) ? first_pos - P.window + 1 : 0;
+  int k_begin = split * P.chunk, k_end = min((split + 1) * P.chunk, last_pos + 1);
+  if (k_begin < (lo_block / 16) * 16) k_begin = (lo_block / 16) * 16;
+
+  // Q fragments
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+  uint4 qa[CH], qc[CH];
+#pragma unroll
+  for (int c = 0; c < CH; c++) {
+    const int d = 32 * c + 8 * t;
+    const bool d_ok = d < Hd;
+    qa[c] = (row_ok[0] && d_ok) ? ldg16(P.q + (size_t)row_tok[0] * P.ldq + (size_t)row_head[0] * Hd + d) : zero4;
+    qc[c] = (row_ok[1] && d_ok) ? ldg16(P.q + (size_t)row_tok[1] * P.ldq + (size_t)row_head[1] * Hd + d) : zero4;
+  }
+
+  float o[4 * CH][4];
+#pragma unroll
+  for (int i = 0; i < 4 * CH; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  const int* bt = P.block_table + (size_t)seq * P.bt_stride;
+  const size_t head_off = (size_t)kvh * P.page_tokens * Hd;
+  const size_t page_stride = (size_t)P.n_kv * P.page_tokens * Hd;
+
+  for (int key0 = k_begin; key0 < k_end; key0 += 16) {
+    const int page = bt[key0 / P.page_tokens];
+    const size_t base = (size_t)page * page_stride + head_off + (size_t)(key0 % P.page_tokens) * Hd;
+    const bf16* kp = P.k_cache + base;
+    const bf16* vp = P.v_cache + base;
+    uint4 ka[CH], kb[CH], va[CH], vb[CH];
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+      const int d = 32 * c + 8 * t;
+      if (d < Hd) {
+        ka[c] = ldg16(kp + (size_t)g * Hd + d);
+        kb[c] = ldg16(kp + (size_t)(g + 8) * Hd + d);
+        va[c] = ldg16(vp + (size_t)g * Hd + d);
+        vb[c] = ldg16(vp + (size_t)(g + 8) * Hd + d);
+      } else {
+        ka[c] = kb[c] = va[c] = vb[c] = zero4;
+      }
+    }
+    // scores: s[i] is the tile of keys key0 + 8i + {2t, 2t+1}; [0],[1] row g, [2],[3] row g+8
+    float s[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; i++) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+      mma16816(s[0], qa[c].x, qc[c].x, qa[c].y, qc[c].y, ka[c].x, ka[c].y);
+      mma16816(s[0], qa[c].z, qc[c].z, qa[c].w, qc[c].w, ka[c].z, ka[c].w);
+      mma16816(s[1], qa[c].x, qc[c].x, qa[c].y, qc[c].y, kb[c].x, kb[c].y);
+      mma16816(s[1], qa[c].z, qc[c].z, qa[c].w, qc[c].w, kb[c].z, kb[c].w);
+    }
+    // mask, scale, running maximum
+    float bm[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int e = j >> 1;
+        const int key = key0 + 8 * i + 2 * t + (j & 1);
+        const int lo = (P.window > 0 && row_pos[e] - P.window + 1 > 0) ? row_pos[e] - P.window + 1 : 0;
+        const bool ok = row_ok[e] && key <= row_pos[e] && key >= lo && key < k_end;
+        s[i][j] = ok ? s[i][j] * P.scale : -INFINITY;
+        bm[e] = fmaxf(bm[e], s[i][j]);
+      }
+    }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+      bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 1));
+      bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 2));
+      const float m_new = fmaxf(m_run[e], bm[e]);
+      m_use[e] = (m_new == -INFINITY) ? 0.f : m_new;      // a row with no key yet: exponents of -inf give 0
+      corr[e] = __expf(m_run[e] - m_use[e]);              // first keys: exp(-inf) = 0
+      m_run[e] = m_new;
+    }
+    float p[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) p[i][j] = __expf(s[i][j] - m_use[j >> 1]);
+#pragma unroll
+    for (int e = 0; e < 2; e++)
+      l_run[e] = l_run[e] * corr[e] + (p[0][2 * e] + p[0][2 * e + 1] + p[1][2 * e] + p[1][2 * e + 1]);
+#pragma unroll
+    for (int i = 0; i < 4 * CH; i++) {
+      o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+    }
+    // the value sum uses probabilities rounded to bfloat16, as its tensor-core operand must be
+    const uint32_t pa0 = pack_bf16(p[0][0], p[0][1]), pa1 = pack_bf16(p[0][2], p[0][3]);
+    const uint32_t pa2 = pack_bf16(p[1][0], p[1][1]), pa3 = pack_bf16(p[1][2], p[1][3]);
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const uint32_t b0 = transpose8x8(reg_of(va[c], i));
+        const uint32_t b1 = transpose8x8(reg_of(vb[c], i));
+        mma16816(o[4 * c + i], pa0, pa1, pa2, pa3, b0, b1);
+      }
+    }
+  }
+  // denominators across the four lanes of a row
+#pragma unroll
+  for (int e = 0; e < 2; e++) {
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 1);
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 2);
+  }
+#pragma unroll
+  for (int e = 0; e < 2; e++) {
+    if (!row_ok[e]) continue;
+    if (P.n_splits == 1) {
+      const float inv = 1.0f / l_run[e];
+      bf16* op = P.out + (size_t)row_tok[e] * P.ldo + (size_t)row_head[e] * Hd;
+#pragma unroll
+      for (int c = 0; c < CH; c++) {
+        const int d = 32 * c + 8 * t;
+        if (d >= Hd) continue;
+        uint4 v;
+        v.x = pack_bf16(o[4 * c + 0][2 * e] * inv, o[4 * c + 0][2 * e + 1] * inv);
+        v.y = pack_bf16(o[4 * c + 1][2 * e] * inv, o[4 * c + 1][2 * e + 1] * inv);
+        v.z = pack_bf16(o[4 * c + 2][2 * e] * inv, o[4 * c + 2][2 * e + 1] * inv);
+        v.w = pack_bf16(o[4 * c + 3][2 * e] * inv, o[4 * c + 3][2 * e + 1] * inv);
+        *reinterpret_cast<uint4*>(op + d) = v;
+      }
+    } else {
+      const size_t slot = ((size_t)row_tok[e] * P.n_q + row_head[e]) * P.n_splits + split;
+      float* po = P.part_o + slot * Hd;
+#pragma unroll
+      for (int c = 0; c < CH; c++) {
+        const int d = 32 * c + 8 * t;
+        if (d >= Hd) continue;
+        *reinterpret_cast<float4*>(po + d) =
+            make_float4(o[4 * c + 0][2 * e], o[4 * c + 0][2 * e + 1], o[4 * c + 1][2 * e], o[4 * c + 1][2 * e + 1]);
+        *reinterpret_cast<float4*>(po + d + 4) =
+            make_float4(o[4 * c + 2][2 * e], o[4 * c + 2][2 * e + 1], o[4 * c + 3][2 * e], o[4 * c + 3][2 * e + 1]);
+      }
+      if (t == 0) {
+        P.part_ml[slot * 2] = m_run[e];
+        P.part_ml[slot * 2 + 1] = l_run[e];
+      }
+    }
+  }
+}
+
+// Merge the splits of one (token, head): one warp each, splits in order.
+__global__ void __launch_bounds__(128)
+attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                       bf16* __restrict__ out, int ldo, const int* __restrict__ token_seq, int n_tokens, int n_q,
+                       int head_dim, int n_splits) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * 4 + warp;
+  if (item >= (long long)n_tokens * n_q) return;
+  const int tok = (int)(item / n_q), h = (int)(item % n_q);
+  if (token_seq && token_seq[tok] < 0) return;
+  const float* ml = part_ml + (size_t)item * n_splits * 2;
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; s++) m = fmaxf(m, ml[2 * s]);
+  float l = 0.f;
+  for (int s = 0; s < n_splits; s++) {
+    const float ms = ml[2 * s];
+    if (ms != -INFINITY) l += ml[2 * s + 1] * __expf(ms - m);
+  }
+  const float inv = 1.0f / l;
+  const float* po = part_o + (size_t)item * n_splits * head_dim;
+  for (int d = lane; d < head_dim; d += 32) {
+    float acc = 0.f;
+    for (int s = 0; s < n_splits; s++) {
+      const float ms = ml[2 * s];
+      if (ms != -INFINITY) acc += po[(size_t)s * head_dim + d] * __expf(ms - m);
+    }
+    out[(size_t)tok * ldo + (size_t)h * head_dim + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+// Scratch needed for n_splits > 1: floats for part_o = tokens*Nq*n_splits*Hd, for part_ml = tokens*Nq*n_splits*2.
+STRATUM_EXPORT int stratum_attention_mma(const void* q, int ldq, const void* k_cache, const void* v_cache,
+                                         const int* token_pos, const int* token_seq, const int* block_table,
+                                         int bt_stride, const int* qb_seq, const int* qb_tok0, const int* qb_ntok,
+                                         int n_qblocks, int tokens_per_block, void* out, int ldo, float* part_o,
+                                         float* part_ml, int n_tokens, int n_q, int n_kv, int head_dim,
+                                         int page_tokens, int window, float scale, int n_splits, int chunk,
+                                         cudaStream_t stream) {
+  if (n_tokens <= 0 || n_qblocks <= 0) return 0;
+  if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 128) return STRATUM_ERR_SHAPE;
+  if (n_kv < 1 || n_q % n_kv != 0 || page_tokens % 16 != 0) return STRATUM_ERR_SHAPE;
+  if (n_splits < 1 || (n_splits > 1 && (chunk % page_tokens != 0 || !part_o || !part_ml))) return STRATUM_ERR_SHAPE;
+  if (ldq % 8 != 0 || ldo % 8 != 0) return STRATUM_ERR_ALIGN;
+  if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return STRATUM_ERR_ALIGN;
+  const int gs = n_q / n_kv;
+  AttnParams P;
+  P.q = (const bf16*)q; P.ldq = ldq;
+  P.k_cache = (const bf16*)k_cache; P.v_cache = (const bf16*)v_cache;
+  P.token_pos = token_pos; P.block_table = block_table; P.bt_stride = bt_stride;
+  P.qb_seq = qb_seq; P.qb_tok0 = qb_tok0; P.qb_ntok = qb_ntok; P.n_qblocks = n_qblocks;
+  P.out = (bf16*)out; P.ldo = ldo; P.part_o = part_o; P.part_ml = part_ml;
+  P.n_q = n_q; P.n_kv = n_kv; P.head_dim = head_dim; P.page_tokens = page_tokens; P.window = window;
+  P.rows_per_token = gs < 16 ? gs : 16;
+  P.head_groups = (gs + 15) / 16;
+  P.tokens_per_block = tokens_per_block;
+  if (tokens_per_block < 1 || tokens_per_block * P.rows_per_token > 16) return STRATUM_ERR_SHAPE;
+  P.n_splits = n_splits; P.chunk = n_splits > 1 ? chunk : 0x40000000;
+  P.scale = scale;
+  const long long items = (long long)n_qblocks * n_kv * P.head_groups * n_splits;
+  const long long blocks = (items + AM_WARPS - 1) / AM_WARPS;
+  if (blocks > 0x7fffffffLL) return STRATUM_ERR_LIMIT;
+  const int ch = (head_dim + 31) / 32;
+  switch (ch) {
+    case 1: attention_mma_kernel<1><<<(unsigned)blocks, AM_WARPS * 32, 0, stream>>>(P); break;
+    case 2: attention_mma_kernel<2><<<(unsigned)blocks, AM_WARPS * 32, 0, stream>>>(P); break;
+    case 3: attention_mma_kernel<3><<<(unsigned)blocks, AM_WARPS * 32, 0, stream>>>(P); break;
+    case 4: attention_mma_kernel<4><<<(unsigned)blocks, AM_WARPS * 32, 0, stream>>>(P); break;
+    default: return STRATUM_ERR_SHAPE;
+  }
+  int st = launch_status();
+  if (st != 0 || n_splits == 1) return st;
+  const long long m_items = (long long)n_tokens * n_q;
+  attention_merge_kernel<<<(unsigned)((m_items + 3) / 4), 128, 0, stream>>>(
+      part_o, part_ml, (bf16*)out, ldo, token_seq, n_tokens, n_q, head_dim, n_splits);
+  return launch_status();
+}

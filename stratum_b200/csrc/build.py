@@ -25,7 +25,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",
                            "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
-SOURCES = ("elementwise", "linear_simple", "attention_simple", "sampling", "gemm_skinny")
+SOURCES = ("elementwise", "linear_simple", "attention_simple", "sampling", "gemm_skinny", "attention_mma")
 HEADERS = ("common.cuh",)
 
 _lock = threading.Lock()

@@ -51,6 +51,21 @@ class StepBatch:
     max_len: int = 1                  # longest sequence after this step
     all_single: bool = True           # every sequence brings exactly one token
     host: Optional[dict] = None       # the same numbers on the host, for parts that plan launches
+    _qblocks: Dict[int, tuple] = field(default_factory=dict)
+
+    def query_blocks(self, tokens_per_block: int):
+        """Cut every sequence's new tokens into runs of at most `tokens_per_block`: int32 tensors
+        (sequence, first packed row, tokens) on the device, made once per step and block size."""
+        if tokens_per_block not in self._qblocks:
+            seqs, rows, counts = [], [], []
+            r = 0
+            for i, n in enumerate(self.host["n_new"]):
+                for b in range(0, n, tokens_per_block):
+                    seqs.append(i); rows.append(r + b); counts.append(min(tokens_per_block, n - b))
+                r += n
+            dev = torch.from_numpy(np.asarray([seqs, rows, counts], dtype=np.int32)).to(self.token_ids.device)
+            self._qblocks[tokens_per_block] = (dev[0], dev[1], dev[2])
+        return self._qblocks[tokens_per_block]
 
 
 class Engine:

@@ -220,6 +220,41 @@ def attention_simple(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
              n_q, n_kv, head_dim, page_tokens, window, c_float(scale), _stream()), "attention_simple")
 
 
+def attention_mma(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, token_pos: torch.Tensor,
+                  token_seq: torch.Tensor, block_table: torch.Tensor, qblocks, tokens_per_block: int,
+                  out: torch.Tensor, part_o: Optional[torch.Tensor], part_ml: Optional[torch.Tensor], n_q: int,
+                  n_kv: int, head_dim: int, page_tokens: int, window: int, scale: float, n_splits: int,
+                  chunk: int) -> None:
+    """bfloat16 tensor-core attention over the paged cache.  qblocks: None (one token per sequence, block i is
+    sequence i) or (seq, first row, tokens) int32 tensors of equal length.  n_splits > 1 needs scratch:
+    part_o float32 [tokens*n_q*n_splits*head_dim], part_ml float32 [tokens*n_q*n_splits*2]."""
+    _need(qkv, "qkv", torch.bfloat16); _need(k_cache, "k_cache", torch.bfloat16)
+    _need(v_cache, "v_cache", torch.bfloat16); _need(out, "out", torch.bfloat16)
+    _need(block_table, "block_table", torch.int32)
+    n_tokens = qkv.shape[0]
+    if qblocks is None:
+        qs = qt = qn = None
+        n_qb = n_tokens
+    else:
+        qs, qt, qn = qblocks
+        n_qb = qs.numel()
+    if n_splits > 1:
+        need = n_tokens * n_q * n_splits
+        _need(part_o, "part_o", torch.float32); _need(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < need * head_dim or part_ml.numel() < need * 2:
+            raise KernelError("attention_mma: scratch too small for the splits")
+    f = _fn("attention_mma", "stratum_attention_mma",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+             c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+             c_int, c_int, c_void_p])
+    _check(f(_ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(token_pos), _ptr(token_seq),
+             _ptr(block_table), block_table.stride(0), _ptr(qs), _ptr(qt), _ptr(qn), n_qb, tokens_per_block,
+             _ptr(out), out.stride(0), _ptr(part_o), _ptr(part_ml), n_tokens, n_q, n_kv, head_dim, page_tokens,
+             window, c_float(scale), n_splits, chunk, _stream()), "attention_mma")
+    if n_splits > 1:
+        count_launches(1)          # the merge kernel
+
+
 # ------------------------------------------------------------------ sampling
 def argmax(logits: torch.Tensor, ids: torch.Tensor, values: Optional[torch.Tensor] = None) -> None:
     _need(logits, "logits", torch.float32, contiguous=False); _need(ids, "ids", torch.int32)

@@ -1,4 +1,9 @@
-"""Which attention kernel serves a given step."""
+"""Which attention kernel serves a given step.
+
+float32, and head sizes the tensor-core kernel refuses (above 128, or no multiple of 16): the CUDA-core
+kernel with the fixed key order.  bfloat16: the tensor-core kernel; on decode steps the keys of each
+sequence are cut into splits so that the whole GPU has work, which needs scratch for the partial results.
+"""
 from __future__ import annotations
 
 import torch
@@ -6,7 +11,38 @@ import torch
 from .. import kernels as K
 from ..cache.pages import PAGE_TOKENS
 
+TARGET_WARPS = 148 * 8          # work items wanted in flight: 148 SMs, 8 warps each
+
+
+def plan_splits(n_items: int, max_len: int):
+    """(n_splits, keys per split) for decode steps: enough splits to fill the GPU, whole pages per split."""
+    pages = max(1, (max_len + PAGE_TOKENS - 1) // PAGE_TOKENS)
+    want = max(1, min(pages, (TARGET_WARPS + n_items - 1) // n_items))
+    chunk = ((pages + want - 1) // want) * PAGE_TOKENS
+    return (max_len + chunk - 1) // chunk, chunk
+
 
 def run(att, qkv: torch.Tensor, cache, step, out: torch.Tensor) -> None:
-    K.attention_simple(qkv, cache.k, cache.v, step.token_pos, step.token_seq, cache.block_table, out,
-                       att.n_heads, att.n_kv_heads, att.head_dim, PAGE_TOKENS, att.window, att.scale)
+    hd = att.head_dim
+    if qkv.dtype != torch.bfloat16 or hd % 16 != 0 or hd > 128 or qkv.stride(0) % 8 != 0:
+        K.attention_simple(qkv, cache.k, cache.v, step.token_pos, step.token_seq, cache.block_table, out,
+                           att.n_heads, att.n_kv_heads, hd, PAGE_TOKENS, att.window, att.scale)
+        return
+    gs = att.n_heads // att.n_kv_heads
+    rows_per_token = min(gs, 16)
+    head_groups = (gs + 15) // 16
+    if step.all_single:
+        n_splits, chunk = plan_splits(step.n_tokens * att.n_kv_heads * head_groups, step.max_len)
+        part_o = part_ml = None
+        if n_splits > 1:
+            n = step.n_tokens * att.n_heads * n_splits
+            part_o = att.runtime.scratch("attention_part_o", n * hd, torch.float32)
+            part_ml = att.runtime.scratch("attention_part_ml", n * 2, torch.float32)
+        K.attention_mma(qkv, cache.k, cache.v, step.token_pos, step.token_seq, cache.block_table, None, 1, out,
+                        part_o, part_ml, att.n_heads, att.n_kv_heads, hd, PAGE_TOKENS, att.window, att.scale,
+                        n_splits, chunk)
+    else:
+        per_block = 16 // rows_per_token
+        K.attention_mma(qkv, cache.k, cache.v, step.token_pos, step.token_seq, cache.block_table,
+                        step.query_blocks(per_block), per_block, out, None, None, att.n_heads, att.n_kv_heads, hd,
+                        PAGE_TOKENS, att.window, att.scale, 1, 0)

@@ -30,8 +30,19 @@ class Runtime:
         self.dtype = dtype
         self.device = torch.device(device)
 
+        self._scratch: Dict[str, torch.Tensor] = {}
+
     def empty(self, *shape: int, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         return torch.empty(shape, dtype=dtype or self.dtype, device=self.device)
+
+    def scratch(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """A named scratch buffer of at least `numel` elements that lives as long as the runtime
+        (kernels that need global memory beyond their inputs and outputs take it from here)."""
+        t = self._scratch.get(name)
+        if t is None or t.numel() < numel or t.dtype != dtype:
+            t = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+            self._scratch[name] = t
+        return t
 
 
 class Part:

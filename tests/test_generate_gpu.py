@@ -93,13 +93,11 @@ def test_temperature_sampling_matches_plain_draws(folders):
             ids, probs = P.filtered_distribution(plain_logits(cfg, w, seq)[-1], 0.8, 0, 1.0)
             u = stream.uniform()
             cum = np.cumsum(probs)
-            expect = P.sample_inverse_cdf(ids, probs, u)
-            # unless u sits within float32 noise of a step of the cumulative distribution
-            near = np.min(np.abs(cum - u)) < 1e-5
-            assert tok == expect or near, (i, seq, tok, expect)
+            # the picked id's stretch of the cumulative distribution holds u, up to float32 noise
+            below = cum[tok - 1] if tok > 0 else 0.0
+            assert below - 4e-6 <= u < cum[tok] + 4e-6, (i, seq, tok, P.sample_inverse_cdf(ids, probs, u))
             seq.append(tok)
-    # request 1's draws come from its own stream whatever the batch: alone it is request 0, so other draws
-    assert alone.tokens != res[1].tokens or True
+    assert len(alone.tokens) == 6
 
 
 def test_command_line_prints_the_reference_lines(folders):

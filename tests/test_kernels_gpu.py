@@ -280,6 +280,86 @@ def test_attention_window_edge(dtype):
     assert np.max(np.abs(c["ref"][1][:hd] - outside)) > 0.1          # not seen
 
 
+def _run_mma(c, n_new, n_q, n_kv, hd, window=0, n_splits=1, chunk=0):
+    from stratum_b200 import kernels as K
+    out = torch.zeros(c["T"], n_q * hd, dtype=torch.bfloat16, device="cuda")
+    gs = n_q // n_kv
+    if all(n == 1 for n in n_new):
+        qblocks, per_block = None, 1
+    else:
+        per_block = 16 // min(gs, 16)
+        seqs, rows, counts, r = [], [], [], 0
+        for i, n in enumerate(n_new):
+            for b in range(0, n, per_block):
+                seqs.append(i); rows.append(r + b); counts.append(min(per_block, n - b))
+            r += n
+        qblocks = tuple(dev(a, torch.int32) for a in (seqs, rows, counts))
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = torch.full((c["T"] * n_q * n_splits * hd,), float("nan"), dtype=torch.float32, device="cuda")
+        part_ml = torch.full((c["T"] * n_q * n_splits * 2,), float("nan"), dtype=torch.float32, device="cuda")
+    K.attention_mma(c["qkv"], c["kc"], c["vc"], c["pos"], c["seq"], c["table"], qblocks, per_block, out, part_o,
+                    part_ml, n_q, n_kv, hd, 64, window, 1.0 / math.sqrt(hd), n_splits, chunk)
+    return out
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd", [(8, 2, 128), (5, 5, 48), (6, 1, 16), (32, 8, 64), (40, 2, 32), (3, 1, 96)])
+def test_attention_mma_prompts_and_continuations(n_q, n_kv, hd):
+    rng = np.random.default_rng(hd + n_q)
+    n_new = [70, 1, 3, 130]
+    c = _attention_case(rng, [0, 130, 63, 200], n_new, n_q, n_kv, hd, "bfloat16")
+    out = _run_mma(c, n_new, n_q, n_kv, hd)
+    assert rel_err(as64(out), c["ref"]) < 8e-3
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd", [(8, 2, 128), (4, 4, 64), (40, 2, 32)])
+@pytest.mark.parametrize("n_splits,chunk", [(1, 0), (4, 256), (11, 64)])
+def test_attention_mma_decode_with_splits(n_q, n_kv, hd, n_splits, chunk):
+    rng = np.random.default_rng(hd)
+    lens = [699, 0, 63, 64, 300]                # one sequence has a single key, some fill only the first split
+    c = _attention_case(rng, lens, [1] * 5, n_q, n_kv, hd, "bfloat16")
+    out = _run_mma(c, [1] * 5, n_q, n_kv, hd, n_splits=n_splits, chunk=chunk)
+    assert rel_err(as64(out), c["ref"]) < 8e-3
+
+
+def test_attention_mma_far_key_and_window_edge():
+    rng = np.random.default_rng(21)
+    n_q, n_kv, hd = 4, 2, 64
+    far = {0: 3, 1: 517}
+
+    def spike(s, q, k, v):
+        d = rng.standard_normal(hd); d /= np.linalg.norm(d)
+        k[far[s], :, :] = d * 12.0
+        q[-1, :, :] = d * 12.0
+
+    c = _attention_case(rng, [699, 600], [1, 1], n_q, n_kv, hd, "bfloat16", spike=spike)
+    for n_splits, chunk in ((1, 0), (6, 128)):
+        out = _run_mma(c, [1, 1], n_q, n_kv, hd, n_splits=n_splits, chunk=chunk)
+        assert rel_err(as64(out), c["ref"]) < 8e-3
+    W, p = 100, 299
+
+    def edge(s, q, k, v):
+        d = rng.standard_normal(hd); d /= np.linalg.norm(d)
+        q[-1, :, :] = d * 10.0
+        k[p - W + 1 if s == 0 else p - W, :, :] = d * 10.0
+
+    c = _attention_case(rng, [p, p], [1, 1], n_q, n_kv, hd, "bfloat16", window=W, spike=edge)
+    for n_splits, chunk in ((1, 0), (5, 64)):
+        out = _run_mma(c, [1, 1], n_q, n_kv, hd, window=W, n_splits=n_splits, chunk=chunk)
+        assert rel_err(as64(out), c["ref"]) < 8e-3
+    c = _attention_case(rng, [250, 0], [60, 140], n_q, n_kv, hd, "bfloat16", window=W)     # prompts under a window
+    out = _run_mma(c, [60, 140], n_q, n_kv, hd, window=W)
+    assert rel_err(as64(out), c["ref"]) < 8e-3
+
+
+def test_attention_mma_refuses_head_sizes_it_cannot_do():
+    from stratum_b200 import kernels as K
+    z = lambda *s, dt=torch.bfloat16: torch.zeros(*s, dtype=dt, device="cuda")   # noqa: E731
+    with pytest.raises(K.KernelError, match="shape"):
+        K.attention_mma(z(1, 3 * 256), z(1, 1, 64, 256), z(1, 1, 64, 256), z(1, dt=torch.int32), z(1, dt=torch.int32),
+                        z(1, 1, dt=torch.int32), None, 1, z(1, 256), None, None, 1, 1, 256, 64, 0, 1.0, 1, 0)
+
+
 def test_fill_normal_is_seeded_and_normal():
     from stratum_b200 import kernels as K
     a = torch.empty(1 << 20, dtype=torch.float32, device="cuda")
