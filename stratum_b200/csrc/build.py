@@ -25,8 +25,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",
                            "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
-SOURCES = ("elementwise", "linear_simple", "attention_simple", "sampling", "gemm_skinny", "attention_mma")
+SOURCES = ("elementwise", "linear_simple", "attention_simple", "sampling", "gemm_skinny", "attention_mma",
+           "attention_static")
 HEADERS = ("common.cuh",)
+EXTRA_DEPS = {"attention_static": ("attention_mma.cu", "attention_static.h")}   # files a source includes
 
 _lock = threading.Lock()
 _loaded: Dict[str, ctypes.CDLL] = {}
@@ -67,7 +69,7 @@ def build_dir() -> str:
 
 def _fingerprint(name: str, extra_flags: Iterable[str]) -> str:
     h = hashlib.sha256()
-    for f in (name + ".cu",) + HEADERS:
+    for f in (name + ".cu",) + HEADERS + EXTRA_DEPS.get(name, ()):
         with open(os.path.join(HERE, f), "rb") as fh:
             h.update(fh.read())
     h.update(" ".join(NVCC_FLAGS + list(extra_flags)).encode())
