@@ -26,7 +26,7 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",
                            "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 SOURCES = ("elementwise", "linear_simple", "attention_simple", "sampling", "gemm_skinny", "attention_mma",
-           "attention_static")
+           "gemm_tc", "attention_static")
 HEADERS = ("common.cuh",)
 EXTRA_DEPS = {"attention_static": ("attention_mma.cu", "attention_static.h")}   # files a source includes
 

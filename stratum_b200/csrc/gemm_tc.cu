@@ -1,0 +1,471 @@
+// y = x W^T (+ bias) on the 5th-generation tensor cores: TMA-fed, tcgen05.mma into TMEM, persistent.
+//
+// W is row-major [N][K] as stored in the file and x is row-major [M][K], so both operands are
+// "K-major" and y[m][n] = sum_k x[m][k] W[n][k] (stratum/native/stratum_linear.h:491-507) needs no
+// transpose anywhere.  Each CTA owns one SM and walks over output tiles of 128 x BN:
+//
+//   warp 0   one lane issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle) of a 128 x 64
+//            tile of x and a BN x 64 tile of W per k-block into a ring of shared-memory stages;
+//   warp 1   allocates tensor memory; one lane issues four tcgen05.mma (128 x BN x 16, bf16 in,
+//            float32 accumulate) per k-block, then tcgen05.commit to hand the stage back, and after
+//            the last k-block a commit that tells the epilogue the accumulator is complete;
+//   warps 2-5 the epilogue: tcgen05.ld the accumulator (lane = output row, 32 columns at a time),
+//            add bias, and store bf16 / add into the float32 residual stream / store float32 /
+//            apply SwiGLU to column pairs.  Two accumulators (2 x BN columns of TMEM) let the
+//            epilogue of one tile overlap the k-loop of the next.
+//
+// With SWAP the roles of x and W are exchanged (the accumulator holds y^T: 128 weight rows by up
+// to 64 rows of x); that form serves decode steps with more rows than the streaming kernel takes.
+//
+// Every wait on an mbarrier is bounded.  If one runs out, the kernel records where in a status
+// word, tells its other warps through shared memory, lets copies in flight land, frees its tensor
+// memory and returns; the host turns the status into an error.  No wait can hang the GPU.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_THREADS 192
+#define TC_SPIN_LIMIT (1u << 22)     // polls of some tens of ns or more each: a fraction of a second at least
+
+#define STRATUM_ERR_WAIT (-5)
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false if the limit ran out or another warp has already given up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < TC_SPIN_LIMIT; i++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, void* dst, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* holder, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(holder)), "r"(cols));
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols));
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+      "%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major tile with 128-byte swizzle: rows of 128 bytes, groups of 8 rows
+// 1024 bytes apart (stride byte offset), version 1 (sm_100), layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFF) >> 4);            // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                            // leading byte offset (unused under 128-byte swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;                  // stride byte offset
+  d |= (uint64_t)1 << 46;                            // descriptor version
+  d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor, kind::f16: D float32, A and B bfloat16, both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t instr_desc_bf16(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+}
+
+struct TcParams {
+  const float* bias;
+  void* out;
+  int* status;        // 0, or a code of where a wait ran out
+  int M, N, K;        // logical sizes of y = x W^T: x [M][K], W [N][K]
+  int ldo;
+};
+
+template <int BN, int STAGES>
+struct TcSmem {
+  alignas(1024) bf16 a[STAGES][TC_BM * TC_BK];
+  alignas(1024) bf16 b[STAGES][BN * TC_BK];
+  uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// EPI: 0 store bf16, 1 add into float32, 2 store float32, 3 SwiGLU pairs -> bf16.
+// SWAP = false: A tiles come from x (rows m), B tiles from W (rows n).  SWAP = true: A from W, B from x.
+template <int BN, int STAGES, int EPI, bool SWAP>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const TcParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  using Smem = TcSmem<BN, STAGES>;
+  Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;      // a power of two >= 32
+  constexpr uint32_t STAGE_BYTES = (TC_BM + BN) * TC_BK * sizeof(bf16);
+
+  const int rows_a = SWAP ? P.N : P.M, rows_b = SWAP ? P.M : P.N;
+  const int tiles_a = (rows_a + TC_BM - 1) / TC_BM, tiles_b = (rows_b + BN - 1) / BN;
+  const int n_tiles = tiles_a * tiles_b;
+  const int n_kb = (P.K + TC_BK - 1) / TC_BK;
+  volatile int* abort_flag = &S.abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
+    for (int b = 0; b < 2; b++) { mbar_init(&S.acc_full[b], 1); mbar_init(&S.acc_empty[b], 4); }
+    S.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(&S.tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = S.tmem_base;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        // consecutive CTAs take consecutive A tiles of the same B tile, so that a wave shares B in L2
+        const int ta = tile % tiles_a, tb = tile / tiles_a;
+        for (int kb = 0; kb < n_kb; kb++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&S.empty[s], ph ^ 1, abort_flag)) {
+            atomicCAS(P.status, 0, 101); S.abort_flag = 1; ok = false; break;
+          }
+          mbar_expect_tx(&S.full[s], STAGE_BYTES);
+          tma_load_2d(&map_a, S.a[s], &S.full[s], kb * TC_BK, ta * TC_BM);
+          tma_load_2d(&map_b, S.b[s], &S.full[s], kb * TC_BK, tb * BN);
+        }
+      }
+      if (!ok) {
+        // let copies already issued land before this block's shared memory can be given to another block
+        for (int i = 0; i < 2000; i++) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc_bf16(BN);
+      uint32_t it = 0, t = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, t++) {
+        const int buf = t & 1;
+        const uint32_t acc_ph = (t >> 1) & 1;
+        if (!mbar_wait(&S.acc_empty[buf], acc_ph ^ 1, abort_flag)) {
+          atomicCAS(P.status, 0, 102); S.abort_flag = 1; ok = false; break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < n_kb; kb++, it++) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&S.full[s], ph, abort_flag)) {
+            atomicCAS(P.status, 0, 103); S.abort_flag = 1; ok = false; break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(S.a[s]), b_addr = smem_u32(S.b[s]);
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; k++) {
+            // 16 k-values = 32 bytes further along each 128-byte swizzled row
+            umma_bf16(d_tmem, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
+                      (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&S.empty[s]);           // arrives once the MMAs above have read this stage
+        }
+        if (ok) umma_commit(&S.acc_full[buf]);  // arrives once the whole accumulator is written
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5)
+    const int quarter = warp & 3;                 // the TMEM lanes this warp may read: 32*quarter ..
+    uint32_t t = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, t++) {
+      const int ta = tile % tiles_a, tb = tile / tiles_a;
+      const int buf = t & 1;
+      const uint32_t acc_ph = (t >> 1) & 1;
+      if (!mbar_wait(&S.acc_full[buf], acc_ph, abort_flag)) {
+        if (lane == 0) { atomicCAS(P.status, 0, 104); S.abort_flag = 1; }
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int row_a = ta * TC_BM + quarter * 32 + lane;       // row of the A operand this thread holds
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+      constexpr int CW = (BN >= 32) ? 32 : 16;                  // columns per tcgen05.ld
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += CW) {
+        uint32_t r[CW];
+        if constexpr (CW == 32) tmem_ld32(taddr + c0, r); else tmem_ld16(taddr + c0, r);
+        tmem_ld_wait();
+        const int col_b0 = tb * BN + c0;                        // first row of the B operand in this chunk
+        if (!SWAP) {
+          // thread = output row m, columns n = col_b0 .. col_b0 + CW - 1 (contiguous in memory)
+          const int m = row_a;
+          if (m < P.M) {
+            float v[CW];
+#pragma unroll
+            for (int j = 0; j < CW; j++) {
+              v[j] = __uint_as_float(r[j]);
+              if (P.bias && col_b0 + j < P.N) v[j] += P.bias[col_b0 + j];
+            }
+            const bool whole = col_b0 + CW <= P.N;
+            if (EPI == 3) {
+              bf16* o = (bf16*)P.out + (size_t)m * P.ldo + (col_b0 >> 1);
+              uint32_t packed[CW / 4];
+#pragma unroll
+              for (int j = 0; j < CW; j += 4) {
+                float a[2];
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                  const float gate = __bfloat162float(__float2bfloat16_rn(v[j + 2 * e]));
+                  const float up = __bfloat162float(__float2bfloat16_rn(v[j + 2 * e + 1]));
+                  a[e] = gate / (1.0f + __expf(-gate)) * up;
+                }
+                __nv_bfloat162 pr = __floats2bfloat162_rn(a[0], a[1]);
+                packed[j / 4] = *reinterpret_cast<uint32_t*>(&pr);
+              }
+              if (whole && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+                for (int q = 0; q < CW / 16; q++)
+                  reinterpret_cast<uint4*>(o)[q] =
+                      make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < CW; j += 2)
+                  if (col_b0 + j + 1 < P.N) {
+                    const __nv_bfloat162 pr = *reinterpret_cast<__nv_bfloat162*>(&packed[j / 4]);
+                    o[j >> 1] = (j & 2) ? pr.y : pr.x;
+                  }
+              }
+            } else if (EPI == 0) {
+              bf16* o = (bf16*)P.out + (size_t)m * P.ldo + col_b0;
+              if (whole && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+                for (int q = 0; q < CW / 8; q++) {
+                  uint32_t w4[4];
+#pragma unroll
+                  for (int e = 0; e < 4; e++) {
+                    __nv_bfloat162 pr = __floats2bfloat162_rn(v[8 * q + 2 * e], v[8 * q + 2 * e + 1]);
+                    w4[e] = *reinterpret_cast<uint32_t*>(&pr);
+                  }
+                  reinterpret_cast<uint4*>(o)[q] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < CW; j++)
+                  if (col_b0 + j < P.N) o[j] = __float2bfloat16_rn(v[j]);
+              }
+            } else {
+              float* o = (float*)P.out + (size_t)m * P.ldo + col_b0;
+              if (whole && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+                for (int q = 0; q < CW / 4; q++) {
+                  float4 w4 = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                  if (EPI == 1) {
+                    const float4 old = reinterpret_cast<float4*>(o)[q];
+                    w4.x += old.x; w4.y += old.y; w4.z += old.z; w4.w += old.w;
+                  }
+                  reinterpret_cast<float4*>(o)[q] = w4;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < CW; j++)
+                  if (col_b0 + j < P.N) o[j] = (EPI == 1) ? o[j] + v[j] : v[j];
+              }
+            }
+          }
+        } else {
+          // thread = weight row n, columns m = col_b0 .. (rows of x): lanes are neighbours in n
+          const int n = row_a;
+#pragma unroll
+          for (int j = 0; j < CW; j++) {
+            const int m = col_b0 + j;
+            float v = __uint_as_float(r[j]);
+            if (P.bias && n < P.N) v += P.bias[n];
+            if (EPI == 3) {
+              v = __bfloat162float(__float2bfloat16_rn(v));
+              const float other = __shfl_xor_sync(0xffffffffu, v, 1);     // gate (even n) <-> up (odd n)
+              if (m < P.M && n + 1 < P.N && (n & 1) == 0)
+                ((bf16*)P.out)[(size_t)m * P.ldo + (n >> 1)] = __float2bfloat16_rn(v / (1.0f + __expf(-v)) * other);
+            } else if (m < P.M && n < P.N) {
+              const size_t idx = (size_t)m * P.ldo + n;
+              if (EPI == 0) ((bf16*)P.out)[idx] = __float2bfloat16_rn(v);
+              else if (EPI == 1) ((float*)P.out)[idx] += v;
+              else ((float*)P.out)[idx] = v;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&S.acc_empty[buf]);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// A [rows][K] bf16 matrix with row pitch `ld` elements, fetched in boxes of box_rows x 64 with 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return STRATUM_ERR_LIMIT;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(bf16)};
+  cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : STRATUM_ERR_SHAPE;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int BN, int STAGES, bool SWAP>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& P, int epilogue, int n_tiles,
+                     cudaStream_t stream) {
+  const size_t smem = sizeof(TcSmem<BN, STAGES>) + 1024;
+  const int grid = n_tiles < sm_count() ? n_tiles : sm_count();
+#define TC_LAUNCH(E)                                                                                        \
+  {                                                                                                         \
+    auto kern = gemm_tc_kernel<BN, STAGES, E, SWAP>;                                                        \
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+    if (e != cudaSuccess) return (int)e;                                                                    \
+    kern<<<grid, TC_THREADS, smem, stream>>>(ma, mb, P);                                                    \
+  }
+  switch (epilogue) {
+    case 0: TC_LAUNCH(0) break;
+    case 1: TC_LAUNCH(1) break;
+    case 2: TC_LAUNCH(2) break;
+    case 3: TC_LAUNCH(3) break;
+    default: return STRATUM_ERR_SHAPE;
+  }
+#undef TC_LAUNCH
+  return launch_status();
+}
+
+// x: bf16 [M][ldx], w: bf16 [N][K], bias float32 [N] or null, out [M][ldo] (SwiGLU: [M][N/2]).
+// status: one int in device memory, 0 before the call; non-zero afterwards means a wait inside the kernel ran out.
+// Needs K % 8 == 0, ldx % 8 == 0, 16-byte aligned x and w (a TMA copy starts on a 16-byte boundary and its
+// row pitch is a multiple of 16 bytes; the k coordinate of every copy here is a multiple of 64).
+STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bias, void* out, int epilogue, int M,
+                                   int N, int K, int ldx, int ldo, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldx < K) return STRATUM_ERR_SHAPE;
+  if (((uintptr_t)x | (uintptr_t)w) & 15) return STRATUM_ERR_ALIGN;
+  if (epilogue == 3 && (N % 2 != 0)) return STRATUM_ERR_SHAPE;
+  if (!status) return STRATUM_ERR_SHAPE;
+  TcParams P;
+  P.bias = bias; P.out = out; P.status = status; P.M = M; P.N = N; P.K = K; P.ldo = ldo;
+  CUtensorMap ma, mb;
+  const bool swap = M <= 64;
+  int st;
+  if (!swap) {
+    // prompts: 128 rows of x by 256 (or 128) rows of W per tile
+    const bool wide = N >= 2048;
+    if ((st = make_map(&ma, x, M, K, ldx, TC_BM)) != 0) return st;
+    if ((st = make_map(&mb, w, N, K, K, wide ? 256 : 128)) != 0) return st;
+    const int tiles_m = (M + TC_BM - 1) / TC_BM;
+    if (wide) return launch_tc<256, 4, false>(ma, mb, P, epilogue, tiles_m * ((N + 255) / 256), stream);
+    return launch_tc<128, 6, false>(ma, mb, P, epilogue, tiles_m * ((N + 127) / 128), stream);
+  }
+  // few rows of x: 128 rows of W by all rows of x per tile
+  const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  if ((st = make_map(&ma, w, N, K, K, TC_BM)) != 0) return st;
+  if ((st = make_map(&mb, x, M, K, ldx, bn)) != 0) return st;
+  const int tiles = (N + TC_BM - 1) / TC_BM;
+  if (bn == 16) return launch_tc<16, 8, true>(ma, mb, P, epilogue, tiles, stream);
+  if (bn == 32) return launch_tc<32, 8, true>(ma, mb, P, epilogue, tiles, stream);
+  return launch_tc<64, 8, true>(ma, mb, P, epilogue, tiles, stream);
+}

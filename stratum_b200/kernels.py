@@ -205,6 +205,40 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
            "gemm_skinny")
 
 
+_status_word: Optional[torch.Tensor] = None
+
+
+def status_word() -> torch.Tensor:
+    """One int32 on the device that kernels with bounded waits write to when a wait runs out."""
+    global _status_word
+    if _status_word is None:
+        _status_word = torch.zeros(1, dtype=torch.int32, device="cuda")
+    return _status_word
+
+
+def check_status() -> None:
+    """Synchronise and raise if a kernel gave up a wait (the word is cleared for the next run)."""
+    if _status_word is None:
+        return
+    code = int(_status_word.item())
+    if code != 0:
+        _status_word.zero_()
+        where = {101: "the TMA producer waiting for a free stage", 102: "the MMA warp waiting for a free accumulator",
+                 103: "the MMA warp waiting for a loaded stage", 104: "the epilogue waiting for an accumulator"}
+        raise KernelError(f"a device-side wait ran out in {where.get(code, f'code {code}')}; results are invalid")
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+            epilogue: int) -> None:
+    """bfloat16 tile kernel on the 5th-generation tensor cores (TMA + tcgen05/TMEM); see EPI_*."""
+    M, N, Kd = _linear_shapes(x, w, bias, out, epilogue, "gemm_tc")
+    _need(x, "x", torch.bfloat16, contiguous=False)
+    f = _fn("gemm_tc", "stratum_gemm_tc",
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), epilogue, M, N, Kd, x.stride(0), out.stride(0),
+             _ptr(status_word()), _stream()), "gemm_tc")
+
+
 # ------------------------------------------------------------------ attention (any sizes, CUDA cores)
 def attention_simple(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, token_pos: torch.Tensor,
                      token_seq: torch.Tensor, block_table: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int,

@@ -27,7 +27,9 @@ def run(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: tor
     if x.dtype == torch.bfloat16 and _aligned(x, w):
         if x.shape[0] <= SKINNY_MAX_ROWS:
             K.gemm_skinny(x, w, bias, out, mode)
-            return
+        else:
+            K.gemm_tc(x, w, bias, out, mode)
+        return
     if mode == SWIGLU:
         gu = torch.empty((x.shape[0], w.shape[0]), dtype=x.dtype, device=x.device)
         K.linear_simple(x, w, bias, gu, STORE)

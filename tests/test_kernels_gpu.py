@@ -118,6 +118,33 @@ def test_gemm_skinny(M, N, K_):
     assert torch.equal(one[0], out32[M - 1])
 
 
+@pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (33, 48, 64), (64, 1000, 200), (100, 256, 4096), (300, 4096 + 16, 512),
+                                     (2048, 2 * 177, 96), (129, 6144, 1024), (1, 128, 128), (17, 130, 72)])
+def test_gemm_tc(M, N, K_):
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(M + N + K_)
+    x = dev(rng.standard_normal((M, K_)), torch.bfloat16)
+    w = dev(rng.standard_normal((N, K_)) * 0.1, torch.bfloat16)
+    b = dev(rng.standard_normal(N))
+    ref = as64(x) @ as64(w).T + as64(b)
+    out32 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    K.gemm_tc(x, w, b, out32, K.EPI_STORE_F32)
+    K.check_status()
+    assert rel_err(as64(out32), ref) < 2e-5
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    K.gemm_tc(x, w, b, out, K.EPI_STORE)
+    assert rel_err(as64(out), ref) < 6e-3
+    res = dev(rng.standard_normal((M, N)))
+    keep = as64(res)
+    K.gemm_tc(x, w, None, res, K.EPI_ADD_F32)
+    assert rel_err(as64(res), keep + as64(x) @ as64(w).T) < 2e-5
+    act = torch.empty(M, N // 2, dtype=torch.bfloat16, device="cuda")
+    K.gemm_tc(x, w, b, act, K.EPI_SWIGLU)
+    K.check_status()
+    r16 = as64(dev(ref, torch.bfloat16))
+    assert rel_err(as64(act), P.silu(r16[:, 0::2]) * r16[:, 1::2]) < 2e-2
+
+
 def test_gemm_skinny_refuses_what_it_cannot_do():
     from stratum_b200 import kernels as K
     x = torch.zeros(2, 20, dtype=torch.bfloat16, device="cuda")
