@@ -138,13 +138,13 @@ def time_decode(llm, batch, context, steps, warmup, vocab, rng):
         fill_to(llm, slots, context - steps - warmup, vocab, rng)
         toks = rng.integers(0, vocab, size=(steps + warmup, batch)).tolist()
         for i in range(warmup):
-            llm.step([StepEntry(s, [t], [0]) for s, t in zip(slots, toks[i])])
+            llm.decode_step(slots, toks[i])
         torch.cuda.synchronize()
         l0 = kernels.launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(warmup, warmup + steps):
-            llm.step([StepEntry(s, [t], [0]) for s, t in zip(slots, toks[i])])
+            llm.decode_step(slots, toks[i])
         e1.record()
         torch.cuda.synchronize()
         return e0.elapsed_time(e1) / steps, (kernels.launch_count() - l0) / steps

@@ -57,6 +57,7 @@ struct AttnParams {
   const bf16* q; int ldq;              // [tokens][ldq]: query heads first
   const bf16* k_cache; const bf16* v_cache;   // [pages][Nk][page_tokens][Hd]
   const int* token_pos;                // [tokens]
+  const int* token_seq;                // [tokens]: index of the token's sequence in the step, -1 = padding
   const int* block_table; int bt_stride;      // [seqs][bt_stride]
   const int* qb_seq; const int* qb_tok0; const int* qb_ntok;   // query blocks; null = one token per sequence
   int n_qblocks;
@@ -80,7 +81,7 @@ attention_mma_kernel(const AttnParams P) {
   const int hg = (int)(item % P.head_groups); item /= P.head_groups;
   const int kvh = (int)(item % P.n_kv); item /= P.n_kv;
   const int qb = (int)item;
-  const int seq = P.qb_seq ? P.qb_seq[qb] : qb;
+  const int seq = P.qb_seq ? P.qb_seq[qb] : P.token_seq[qb];
   const int tok0 = P.qb_tok0 ? P.qb_tok0[qb] : qb;
   const int ntok = P.qb_ntok ? P.qb_ntok[qb] : 1;
   if (seq < 0) return;                                    // padding
@@ -295,7 +296,7 @@ STRATUM_EXPORT int stratum_attention_mma(const void* q, int ldq, const void* k_c
   AttnParams P;
   P.q = (const bf16*)q; P.ldq = ldq;
   P.k_cache = (const bf16*)k_cache; P.v_cache = (const bf16*)v_cache;
-  P.token_pos = token_pos; P.block_table = block_table; P.bt_stride = bt_stride;
+  P.token_pos = token_pos; P.token_seq = token_seq; P.block_table = block_table; P.bt_stride = bt_stride;
   P.qb_seq = qb_seq; P.qb_tok0 = qb_tok0; P.qb_ntok = qb_ntok; P.n_qblocks = n_qblocks;
   P.out = (bf16*)out; P.ldo = ldo; P.part_o = part_o; P.part_ml = part_ml;
   P.n_q = n_q; P.n_kv = n_kv; P.head_dim = head_dim; P.page_tokens = page_tokens; P.window = window;

@@ -420,8 +420,12 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
 #define TC_LAUNCH(E)                                                                                        \
   {                                                                                                         \
     auto kern = gemm_tc_kernel<BN, STAGES, E, SWAP>;                                                        \
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
-    if (e != cudaSuccess) return (int)e;                                                                    \
+    static bool configured = false; /* once per instantiation; not a stream operation */                   \
+    if (!configured) {                                                                                      \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+      if (e != cudaSuccess) return (int)e;                                                                  \
+      configured = true;                                                                                    \
+    }                                                                                                       \
     kern<<<grid, TC_THREADS, smem, stream>>>(ma, mb, P);                                                    \
   }
   switch (epilogue) {

@@ -16,6 +16,7 @@ import torch
 from ..config.base import ModelConfig
 from ..sampling import Pcg32, Sampler, SamplingParams
 from .generate import Backend, GenerationResult, generate
+from .graphs import DecodeGraphs
 from .model import load_model, random_model_on_device
 from .step import Engine, StepEntry
 
@@ -23,8 +24,8 @@ _DTYPES = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bf
 
 
 class _EngineBackend(Backend):
-    def __init__(self, engine: Engine, sampler: Sampler):
-        self.engine, self.sampler = engine, sampler
+    def __init__(self, engine: Engine, sampler: Sampler, graphs=None):
+        self.engine, self.sampler, self.graphs = engine, sampler, graphs
         self.n_pages, self.max_seqs = engine.cache.n_pages, engine.cache.max_seqs
         self.on_logits = None          # optional hook(logits [n, vocab] on the device, picked ids list)
 
@@ -35,6 +36,13 @@ class _EngineBackend(Backend):
         self.engine.release(slot)
 
     def step_and_pick(self, work, streams, params):
+        if self.graphs is not None and all(len(toks) == 1 for _, toks in work):
+            uniforms = None if params.greedy else [st.uniform() for st in streams]
+            picked, values, captured = self.graphs.step([s for s, _ in work], [toks[0] for _, toks in work],
+                                                        params.temperature, params.top_k, params.top_p, uniforms)
+            if self.on_logits is not None:
+                self.on_logits(captured.logits[:len(work)], picked)
+            return picked, values
         logits = self.engine.step([StepEntry(s, toks, [len(toks) - 1]) for s, toks in work])
         ids, values = self.sampler.pick(logits, params, streams, want_values=True)
         both = torch.stack([ids.to(torch.float64), values.to(torch.float64)]).cpu()     # one device-to-host copy
@@ -48,7 +56,8 @@ class Stratum:
     """A loaded model with its cache.  dtype: "bfloat16" (serving kernels) or "float32" (true 32-bit)."""
 
     def __init__(self, model_dir: Optional[str] = None, dtype: str = "bfloat16", max_tokens: int = 4096,
-                 max_seqs: Optional[int] = None, device: str = "cuda", *, _model=None, _config=None):
+                 max_seqs: Optional[int] = None, device: str = "cuda", use_graphs: bool = True, *,
+                 _model=None, _config=None):
         if dtype not in _DTYPES:
             raise ValueError(f"dtype {dtype!r} not one of {sorted(_DTYPES)}")
         if not torch.cuda.is_available():
@@ -59,14 +68,16 @@ class Stratum:
         self.dtype = dtype
         self.engine = Engine(self.model, max_tokens=max_tokens, max_seqs=max_seqs)
         self.sampler = Sampler(self.model.runtime.device)
-        self._backend = _EngineBackend(self.engine, self.sampler)
+        self.graphs = DecodeGraphs(self.engine) if use_graphs else None
+        self._backend = _EngineBackend(self.engine, self.sampler, self.graphs)
 
     @classmethod
     def from_random(cls, config: ModelConfig, seed: int = 0, dtype: str = "bfloat16", max_tokens: int = 4096,
-                    max_seqs: Optional[int] = None, device: str = "cuda", std: float = 0.02) -> "Stratum":
+                    max_seqs: Optional[int] = None, device: str = "cuda", std: float = 0.02,
+                    use_graphs: bool = True) -> "Stratum":
         """Random weights made on the device from (config, seed); nothing is read or written."""
         model = random_model_on_device(config, seed, _DTYPES[dtype], device, std)
-        return cls(None, dtype, max_tokens, max_seqs, device, _model=model, _config=config)
+        return cls(None, dtype, max_tokens, max_seqs, device, use_graphs, _model=model, _config=config)
 
     # -- stepping by hand -----------------------------------------------------
     def acquire(self) -> int:
@@ -76,7 +87,18 @@ class Stratum:
         self.engine.release(slot)
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run the entries' tokens; float32 logits [wanted places, vocab] on the device."""
         return self.engine.step(entries)
+
+    def decode_step(self, slots: Sequence[int], tokens: Sequence[int],
+                    sampling: SamplingParams = SamplingParams(), streams: Optional[Sequence[Pcg32]] = None):
+        """One token for each slot, picked on the device: (ids, logits of the ids) as host lists.  The step
+        runs as a replayed CUDA graph (or launch by launch when graphs are off)."""
+        if self.graphs is None:
+            return self._backend.step_and_pick([(s, [t]) for s, t in zip(slots, tokens)], streams, sampling)
+        uniforms = None if sampling.greedy else [st.uniform() for st in streams]
+        ids, vals, _ = self.graphs.step(slots, tokens, sampling.temperature, sampling.top_k, sampling.top_p, uniforms)
+        return ids, vals
 
     # -- generation ---------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens=16, stop_ids: Optional[Sequence[int]] = None,

@@ -1,0 +1,180 @@
+"""Decode steps as replayed CUDA graphs.
+
+A decode step is some three hundred small launches; issued one by one from Python they cost more
+host time than the GPU needs to run them.  So the whole step (embedding, every layer, final norm,
+head, token pick) is captured once per shape into a CUDA graph and replayed: per step the host
+fills one pinned buffer with the step's description (token ids, positions, page tables, sampling
+numbers), copies it to the device in one go, replays, and reads the picked ids back.
+
+A graph is specific to (rows, page-table width): rows is the batch padded up a little (padding
+rows carry sequence index -1, which every kernel that touches the cache skips; rows never mix, so
+padding changes no result), and the width is the next power of two of the pages the longest
+sequence holds, which also fixes how the keys are split across warps.  The reference queues its
+decode steps on the GPU ahead of time for the same reason
+(stratum/native/stratum_arch_llama.inc.c:1994-2038).
+"""
+from __future__ import annotations
+
+from collections import OrderedDict
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import kernels as K
+from ..cache.pages import PAGE_TOKENS, pages_for
+from ..cache.store import KVSpec
+from .step import Engine, StepBatch, StepError
+
+
+def padded_rows(n: int) -> int:
+    """Rows a graph is captured for: exact up to 8, then the next multiple of 8."""
+    return n if n <= 8 else ((n + 7) // 8) * 8
+
+
+def width_bucket(n_pages: int) -> int:
+    w = 1
+    while w < n_pages:
+        w *= 2
+    return w
+
+
+class _Captured:
+    def __init__(self, rows: int, width: int, n_groups: int, device):
+        self.rows, self.width = rows, width
+        B = rows
+        # int32 words: ids | pos | seq | want | slot | start | len | tables | temperature | top_k | top_p | uniform
+        self.off = {}
+        o = 0
+        for name, n in (("ids", B), ("pos", B), ("seq", B), ("want", B), ("slot", B), ("start", B + 1), ("len", B),
+                        ("tables", n_groups * B * width), ("temperature", B), ("top_k", B), ("top_p", B),
+                        ("uniform", B)):
+            self.off[name] = (o, n)
+            o += n
+        self.total = o
+        self.host = torch.empty(o, dtype=torch.int32).pin_memory()
+        self.np = self.host.numpy()
+        self.dev = torch.zeros(o, dtype=torch.int32, device=device)
+        self.out_ids = torch.zeros(B, dtype=torch.int32, device=device)
+        self.out_vals = torch.zeros(B, dtype=torch.float32, device=device)
+        self.out_host = torch.empty(2 * B, dtype=torch.int32).pin_memory()
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.kernels = 0
+        self.logits: Optional[torch.Tensor] = None
+
+    def view(self, name: str, dev: bool):
+        o, n = self.off[name]
+        return (self.dev if dev else self.np)[o:o + n]
+
+
+class DecodeGraphs:
+    """Runs one-token-per-sequence steps of an Engine through captured graphs."""
+
+    def __init__(self, engine: Engine, max_graphs: int = 16):
+        self.engine = engine
+        self.max_graphs = max_graphs
+        self.graphs: "OrderedDict[Tuple[int, int], _Captured]" = OrderedDict()
+        self.groups = [gi for gi, g in enumerate(engine.cache.groups) if isinstance(g.spec, KVSpec)]
+        self.pool = None
+        self.done = torch.cuda.Event()
+        self.captures = 0
+
+    # ------------------------------------------------------------------ building blocks
+    def _batch(self, c: _Captured) -> StepBatch:
+        B, W = c.rows, c.width
+        tables = {}
+        o, _ = c.off["tables"]
+        for j, gi in enumerate(self.groups):
+            tables[gi] = c.dev[o + j * B * W: o + (j + 1) * B * W].view(B, W)
+        return StepBatch(n_tokens=B, n_seqs=B, token_ids=c.view("ids", True), token_pos=c.view("pos", True),
+                         token_seq=c.view("seq", True), want_rows=c.view("want", True),
+                         seq_slot=c.view("slot", True), seq_start=c.view("start", True), seq_len=c.view("len", True),
+                         block_tables=tables, max_new=1, max_len=W * PAGE_TOKENS, all_single=True,
+                         host={"n_new": [1] * B, "before": None})
+
+    def _forward_and_pick(self, c: _Captured) -> None:
+        logits = self.engine.model.forward(self._batch(c), self.engine.cache)
+        K.sample(logits, c.view("temperature", True).view(torch.float32), c.view("top_k", True),
+                 c.view("top_p", True).view(torch.float32), c.view("uniform", True).view(torch.float32),
+                 c.out_ids, c.out_vals)
+        c.logits = logits
+
+    def _capture(self, c: _Captured) -> None:
+        self._forward_and_pick(c)                     # once for real: compiles, sizes scratch, warms up
+        torch.cuda.synchronize()
+        if self.pool is None:
+            self.pool = torch.cuda.graph_pool_handle()
+        g = torch.cuda.CUDAGraph()
+        before = K.launch_count()
+        with torch.cuda.graph(g, pool=self.pool):
+            self._forward_and_pick(c)
+        c.kernels = K.launch_count() - before
+        K.count_launches(-c.kernels)                  # captured, not run
+        c.graph = g
+        self.captures += 1
+
+    def _get(self, rows: int, width: int) -> _Captured:
+        key = (rows, width)
+        c = self.graphs.get(key)
+        if c is None:
+            while len(self.graphs) >= self.max_graphs:
+                self.graphs.popitem(last=False)
+            c = _Captured(rows, width, len(self.groups), self.engine.runtime.device)
+            self.graphs[key] = c
+        else:
+            self.graphs.move_to_end(key)
+        return c
+
+    # ------------------------------------------------------------------ one step
+    def step(self, slots: Sequence[int], tokens: Sequence[int], temperature: float, top_k: int, top_p: float,
+             uniforms: Optional[Sequence[float]]) -> Tuple[List[int], List[float], _Captured]:
+        """One token for each slot; returns the picked ids and their logits (host lists)."""
+        eng = self.engine
+        B = len(slots)
+        if B == 0:
+            raise StepError("a step needs at least one entry")
+        if len(set(slots)) != B:
+            raise StepError("a slot appears twice in one step")
+        for s, t in zip(slots, tokens):
+            if not eng.cache.slots.is_live(s):
+                raise StepError(f"slot {s} is not held by a sequence")
+            if not (0 <= int(t) < eng.vocab):
+                raise StepError(f"slot {s}: token id {t} outside the vocabulary [0, {eng.vocab})")
+        eng.cache.reserve(slots, [1] * B)
+        before = [eng.cache.length(s) for s in slots]
+        c = self._get(padded_rows(B), width_bucket(pages_for(max(before) + 1)))
+        R, W = c.rows, c.width
+        h = c.np
+        v = lambda name: c.view(name, False)          # noqa: E731
+        v("ids")[:] = 0; v("ids")[:B] = tokens
+        v("pos")[:] = 0; v("pos")[:B] = before
+        v("seq")[:] = -1; v("seq")[:B] = np.arange(B, dtype=np.int32)
+        v("want")[:] = np.arange(R, dtype=np.int32)
+        v("slot")[:] = 0; v("slot")[:B] = slots
+        v("start")[:] = np.arange(R + 1, dtype=np.int32)
+        v("len")[:] = 0; v("len")[:B] = np.asarray(before, dtype=np.int32) + 1
+        o, n = c.off["tables"]
+        tb = h[o:o + n].reshape(len(self.groups), R, W)
+        tb.fill(-1)
+        for j, gi in enumerate(self.groups):
+            for i, row in enumerate(eng.cache.page_table_rows(slots, gi)):
+                tb[j, i, :len(row)] = row
+        v("temperature").view(np.float32)[:] = temperature
+        v("top_k")[:] = top_k
+        v("top_p").view(np.float32)[:] = top_p
+        u = v("uniform").view(np.float32)
+        u[:] = 0.0
+        if uniforms is not None:
+            u[:B] = uniforms
+        c.dev.copy_(c.host, non_blocking=True)
+        if c.graph is None:
+            self._capture(c)
+        c.graph.replay()
+        K.count_launches(c.kernels)
+        c.out_host[:R].copy_(c.out_ids, non_blocking=True)
+        c.out_host[R:].copy_(c.out_vals.view(torch.int32), non_blocking=True)
+        self.done.record()
+        self.done.synchronize()
+        eng.cache.advance(slots, [1] * B)
+        out = c.out_host.numpy()
+        return out[:B].tolist(), out[R:R + B].view(np.float32).tolist(), c
