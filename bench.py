@@ -199,6 +199,8 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (0 = all)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
+    ap.add_argument("--decode-only", action="store_true",
+                    help="time the decode steps only and print a short line (for profiler runs)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -224,7 +226,7 @@ def main() -> int:
     cfg = LlamaConfig.from_dict(raw)
     peaks = load_peaks()
     rng = np.random.default_rng(0)
-    biggest = max(args.batch, 1 if args.no_points else 64)
+    biggest = max(args.batch, 1 if (args.no_points or args.decode_only) else 64)
     llm = Stratum.from_random(cfg, seed=0, dtype="bfloat16",
                               max_tokens=biggest * (args.context + 64), max_seqs=biggest)
     vocab = cfg.vocab
@@ -233,6 +235,11 @@ def main() -> int:
         ms_step, launches = time_decode(llm, args.batch, args.context, args.steps, args.warmup, vocab, rng)
     value = args.batch * 1000.0 / ms_step
     clock_summary = clocks.summary()
+    if args.decode_only:
+        print(json.dumps({"decode_only": True, "batch": args.batch, "context": args.context, "layers": n_layers,
+                          "ms_per_step": round(ms_step, 4), "tokens_per_s": round(value, 1),
+                          "launches_per_step": launches}))
+        return 0
 
     e2e_value = time_e2e(llm, args.batch, args.context, args.steps, args.warmup, vocab, rng)
     prefill_ms = time_prefill(llm, PREFILL_TOKENS, vocab, rng)

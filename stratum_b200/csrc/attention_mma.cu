@@ -74,6 +74,9 @@ __global__ void __launch_bounds__(AM_WARPS * 32)
 attention_mma_kernel(const AttnParams P) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
+  pdl_trigger();
+  // the step's description (positions, page tables, query blocks) is read before waiting for the kernel
+  // that wrote q and the newest keys; q and the cache only after it
   long long item = (long long)blockIdx.x * AM_WARPS + warp;
   const long long n_items = (long long)P.n_qblocks * P.n_kv * P.head_groups * P.n_splits;
   if (item >= n_items) return;
@@ -107,6 +110,10 @@ attention_mma_kernel(const AttnParams P) {
   int k_begin = split * P.chunk, k_end = min((split + 1) * P.chunk, last_pos + 1);
   if (k_begin < (lo_block / 16) * 16) k_begin = (lo_block / 16) * 16;
 
+  const int* bt = P.block_table + (size_t)seq * P.bt_stride;
+  const int first_page = (k_begin < k_end) ? bt[k_begin / P.page_tokens] : 0;
+  pdl_wait();
+
   // Q fragments
   const uint4 zero4 = make_uint4(0, 0, 0, 0);
   uint4 qa[CH], qc[CH];
@@ -123,12 +130,11 @@ attention_mma_kernel(const AttnParams P) {
   for (int i = 0; i < 4 * CH; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
-  const int* bt = P.block_table + (size_t)seq * P.bt_stride;
   const size_t head_off = (size_t)kvh * P.page_tokens * Hd;
   const size_t page_stride = (size_t)P.n_kv * P.page_tokens * Hd;
 
   for (int key0 = k_begin; key0 < k_end; key0 += 16) {
-    const int page = bt[key0 / P.page_tokens];
+    const int page = (key0 == k_begin) ? first_page : bt[key0 / P.page_tokens];
     const size_t base = (size_t)page * page_stride + head_off + (size_t)(key0 % P.page_tokens) * Hd;
     const bf16* kp = P.k_cache + base;
     const bf16* vp = P.v_cache + base;
@@ -248,34 +254,31 @@ attention_mma_kernel(const AttnParams P) {
   }
 }
 
-// Merge the splits of one (token, head): one warp each, splits in order.
+// Merge the splits of one (token, head): one block each, one thread per output dimension, splits in order.
 __global__ void __launch_bounds__(128)
 attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                        bf16* __restrict__ out, int ldo, const int* __restrict__ token_seq, int n_tokens, int n_q,
                        int head_dim, int n_splits) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long item = (long long)blockIdx.x * 4 + warp;
-  if (item >= (long long)n_tokens * n_q) return;
-  const int tok = (int)(item / n_q), h = (int)(item % n_q);
+  pdl_trigger();
+  const int item = blockIdx.x;
+  const int tok = item / n_q, h = item % n_q;
   if (token_seq && token_seq[tok] < 0) return;
+  pdl_wait();
   const float* ml = part_ml + (size_t)item * n_splits * 2;
   float m = -INFINITY;
   for (int s = 0; s < n_splits; s++) m = fmaxf(m, ml[2 * s]);
-  float l = 0.f;
+  const float* po = part_o + (size_t)item * n_splits * head_dim;
+  const int d = threadIdx.x;
+  if (d >= head_dim) return;
+  float l = 0.f, acc = 0.f;
+#pragma unroll 4
   for (int s = 0; s < n_splits; s++) {
     const float ms = ml[2 * s];
-    if (ms != -INFINITY) l += ml[2 * s + 1] * __expf(ms - m);
+    const float wgt = (ms == -INFINITY) ? 0.f : __expf(ms - m);
+    l += ml[2 * s + 1] * wgt;
+    acc += po[(size_t)s * head_dim + d] * wgt;
   }
-  const float inv = 1.0f / l;
-  const float* po = part_o + (size_t)item * n_splits * head_dim;
-  for (int d = lane; d < head_dim; d += 32) {
-    float acc = 0.f;
-    for (int s = 0; s < n_splits; s++) {
-      const float ms = ml[2 * s];
-      if (ms != -INFINITY) acc += po[(size_t)s * head_dim + d] * __expf(ms - m);
-    }
-    out[(size_t)tok * ldo + (size_t)h * head_dim + d] = __float2bfloat16_rn(acc * inv);
-  }
+  out[(size_t)tok * ldo + (size_t)h * head_dim + d] = __float2bfloat16_rn(acc / l);
 }
 
 // Scratch needed for n_splits > 1: floats for part_o = tokens*Nq*n_splits*Hd, for part_ml = tokens*Nq*n_splits*2.
@@ -310,17 +313,17 @@ STRATUM_EXPORT int stratum_attention_mma(const void* q, int ldq, const void* k_c
   const long long blocks = (items + AM_WARPS - 1) / AM_WARPS;
   if (blocks > 0x7fffffffLL) return STRATUM_ERR_LIMIT;
   const int ch = (head_dim + 31) / 32;
+  int st = 0;
   switch (ch) {
-    case 1: attention_mma_kernel<1><<<(unsigned)blocks, AM_WARPS * 32, 0, stream>>>(P); break;
-    case 2: attention_mma_kernel<2><<<(unsigned)blocks, AM_WARPS * 32, 0, stream>>>(P); break;
-    case 3: attention_mma_kernel<3><<<(unsigned)blocks, AM_WARPS * 32, 0, stream>>>(P); break;
-    case 4: attention_mma_kernel<4><<<(unsigned)blocks, AM_WARPS * 32, 0, stream>>>(P); break;
+    case 1: st = launch_pdl(attention_mma_kernel<1>, (unsigned)blocks, AM_WARPS * 32, 0, stream, P); break;
+    case 2: st = launch_pdl(attention_mma_kernel<2>, (unsigned)blocks, AM_WARPS * 32, 0, stream, P); break;
+    case 3: st = launch_pdl(attention_mma_kernel<3>, (unsigned)blocks, AM_WARPS * 32, 0, stream, P); break;
+    case 4: st = launch_pdl(attention_mma_kernel<4>, (unsigned)blocks, AM_WARPS * 32, 0, stream, P); break;
     default: return STRATUM_ERR_SHAPE;
   }
-  int st = launch_status();
   if (st != 0 || n_splits == 1) return st;
   const long long m_items = (long long)n_tokens * n_q;
-  attention_merge_kernel<<<(unsigned)((m_items + 3) / 4), 128, 0, stream>>>(
-      part_o, part_ml, (bf16*)out, ldo, token_seq, n_tokens, n_q, head_dim, n_splits);
-  return launch_status();
+  if (m_items > 0x7fffffffLL) return STRATUM_ERR_LIMIT;
+  return launch_pdl(attention_merge_kernel, (unsigned)m_items, 128, 0, stream, (const float*)part_o,
+                    (const float*)part_ml, (bf16*)out, ldo, token_seq, n_tokens, n_q, head_dim, n_splits);
 }

@@ -52,6 +52,41 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
   return scratch[32];
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with launch_pdl may begin while the kernel before it in the stream is still
+// finishing.  Whatever it does before pdl_wait() must not touch memory an earlier kernel writes (it
+// may read weights and the step's description, compute addresses, warm up); pdl_wait() returns once
+// every earlier kernel has completed and its writes are visible.  pdl_trigger() lets the kernel
+// after this one start its own preamble.  Launched the ordinary way, both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <stdlib.h>
+static inline bool pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("STRATUM_PDL");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 static inline int launch_status() {
   cudaError_t e = cudaGetLastError();
   return (int)e;

@@ -11,6 +11,8 @@
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int hidden, int vocab) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) id = 0;   // ids are range-checked on the host before a step; never trust twice
@@ -24,12 +26,12 @@ STRATUM_EXPORT int stratum_embed_gather(const void* table, int dtype, const int*
   if (n_tokens <= 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (dtype == STRATUM_DT_F32)
-    embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, hidden, vocab);
-  else if (dtype == STRATUM_DT_BF16)
-    embed_gather_kernel<bf16><<<n_tokens, threads, 0, stream>>>((const bf16*)table, ids, out, hidden, vocab);
-  else
-    return STRATUM_ERR_DTYPE;
-  return launch_status();
+    return launch_pdl(embed_gather_kernel<float>, n_tokens, threads, 0, stream, (const float*)table, ids, out, hidden,
+                      vocab);
+  if (dtype == STRATUM_DT_BF16)
+    return launch_pdl(embed_gather_kernel<bf16>, n_tokens, threads, 0, stream, (const bf16*)table, ids, out, hidden,
+                      vocab);
+  return STRATUM_ERR_DTYPE;
 }
 
 // ---------------------------------------------------------------- RMSNorm
@@ -40,6 +42,8 @@ template <typename T>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
                                const int* __restrict__ rows, T* __restrict__ out, int hidden, float eps) {
   __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   const float* xr = x + (size_t)src * hidden;
@@ -54,17 +58,73 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<T>(xr[i] * scale * gain[i]);
 }
 
+// The same, four values per thread and iteration held in registers between the sum and the scaling, so a
+// row is read once.  hidden % 4 == 0 and hidden <= 4 * VPT * blockDim.x.
+template <typename T, int VPT>
+__global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ gain,
+                                   const int* __restrict__ rows, T* __restrict__ out, int hidden, float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  const int r = blockIdx.x;
+  const int n4 = hidden >> 2;
+  float4 gv[VPT];
+#pragma unroll
+  for (int j = 0; j < VPT; j++) {               // the gain is a weight: it may be read before the wait
+    const int i = threadIdx.x + j * blockDim.x;
+    gv[j] = i < n4 ? reinterpret_cast<const float4*>(gain)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  pdl_wait();
+  const int src = rows ? rows[r] : r;
+  const float4* xr = reinterpret_cast<const float4*>(x + (size_t)src * hidden);
+  float4 v[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPT; j++) {
+    const int i = threadIdx.x + j * blockDim.x;
+    v[j] = i < n4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+    ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+  T* o = out + (size_t)r * hidden;
+#pragma unroll
+  for (int j = 0; j < VPT; j++) {
+    const int i = threadIdx.x + j * blockDim.x;
+    if (i >= n4) continue;
+    const float a = v[j].x * scale * gv[j].x, b = v[j].y * scale * gv[j].y;
+    const float c = v[j].z * scale * gv[j].z, d = v[j].w * scale * gv[j].w;
+    if constexpr (sizeof(T) == 4) {
+      reinterpret_cast<float4*>(o)[i] = make_float4(a, b, c, d);
+    } else {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(o)[i] = pk;
+    }
+  }
+}
+
+template <typename T>
+static int launch_rmsnorm(const float* x, const float* gain, const int* rows, T* out, int n_rows, int hidden,
+                          float eps, cudaStream_t stream) {
+  const bool vec = hidden % 4 == 0 && ((((uintptr_t)x | (uintptr_t)gain | (uintptr_t)out) & 15) == 0);
+  if (vec && hidden <= 4 * 1024)
+    return launch_pdl(rmsnorm_vec_kernel<T, 1>, n_rows, ((hidden / 4 + 31) / 32) * 32, 0, stream, x, gain, rows, out,
+                      hidden, eps);
+  if (vec && hidden <= 4 * 4 * 1024)
+    return launch_pdl(rmsnorm_vec_kernel<T, 4>, n_rows, 1024, 0, stream, x, gain, rows, out, hidden, eps);
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  return launch_pdl(rmsnorm_kernel<T>, n_rows, threads, 0, stream, x, gain, rows, out, hidden, eps);
+}
+
 STRATUM_EXPORT int stratum_rmsnorm(const float* x, const float* gain, const int* rows, void* out, int out_dtype,
                                    int n_rows, int hidden, float eps, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
-  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-  if (out_dtype == STRATUM_DT_F32)
-    rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, gain, rows, (float*)out, hidden, eps);
-  else if (out_dtype == STRATUM_DT_BF16)
-    rmsnorm_kernel<bf16><<<n_rows, threads, 0, stream>>>(x, gain, rows, (bf16*)out, hidden, eps);
-  else
-    return STRATUM_ERR_DTYPE;
-  return launch_status();
+  if (out_dtype == STRATUM_DT_F32) return launch_rmsnorm<float>(x, gain, rows, (float*)out, n_rows, hidden, eps, stream);
+  if (out_dtype == STRATUM_DT_BF16) return launch_rmsnorm<bf16>(x, gain, rows, (bf16*)out, n_rows, hidden, eps, stream);
+  return STRATUM_ERR_DTYPE;
 }
 
 // ---------------------------------------------------------------- SwiGLU
@@ -111,6 +171,9 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ t
                                   int interleaved, float mscale, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                   int n_q, int n_kv, int head_dim, int page_tokens, int write_cache) {
   extern __shared__ float cs[];   // cos[n_pairs], sin[n_pairs]
+  pdl_trigger();
+  // positions, page tables and frequencies belong to the step's description and the weights: they are
+  // read, and the angles computed, before waiting for the projection that produced qkv
   const int t = blockIdx.x;
   const int seq = token_seq[t];
   if (seq < 0) return;
@@ -122,7 +185,6 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ t
     cs[k] = c * mscale;
     cs[n_pairs + k] = s * mscale;
   }
-  __syncthreads();
   const int row_elems = (n_q + 2 * n_kv) * head_dim;
   T* row = qkv + (size_t)t * row_elems;
   const int half = head_dim / 2;          // work items per head: one per pair slot (rotated or not)
@@ -131,6 +193,8 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ t
     const int page = block_table[(size_t)seq * bt_stride + pos / page_tokens];
     kv_row_base = ((size_t)page * n_kv * page_tokens + (pos % page_tokens)) * (size_t)head_dim;
   }
+  __syncthreads();
+  pdl_wait();
   const size_t head_stride = (size_t)page_tokens * head_dim;   // between kv heads inside a page
   // q and k heads: item = (head, slot); slot < n_pairs rotates a pair, slot >= n_pairs copies two plain dims
   const int n_rot_heads = n_q + (write_cache ? n_kv : 0);
@@ -177,16 +241,14 @@ STRATUM_EXPORT int stratum_rope_store(void* qkv, int dtype, const int* token_pos
   const int threads = 256;
   const size_t smem = (size_t)2 * n_pairs * sizeof(float);
   if (dtype == STRATUM_DT_F32)
-    rope_store_kernel<float><<<n_tokens, threads, smem, stream>>>(
-        (float*)qkv, token_pos, token_seq, block_table, bt_stride, inv_freq, n_pairs, interleaved, mscale,
-        (float*)k_cache, (float*)v_cache, n_q, n_kv, head_dim, page_tokens, write_cache);
-  else if (dtype == STRATUM_DT_BF16)
-    rope_store_kernel<bf16><<<n_tokens, threads, smem, stream>>>(
-        (bf16*)qkv, token_pos, token_seq, block_table, bt_stride, inv_freq, n_pairs, interleaved, mscale,
-        (bf16*)k_cache, (bf16*)v_cache, n_q, n_kv, head_dim, page_tokens, write_cache);
-  else
-    return STRATUM_ERR_DTYPE;
-  return launch_status();
+    return launch_pdl(rope_store_kernel<float>, n_tokens, threads, smem, stream, (float*)qkv, token_pos, token_seq,
+                      block_table, bt_stride, inv_freq, n_pairs, interleaved, mscale, (float*)k_cache,
+                      (float*)v_cache, n_q, n_kv, head_dim, page_tokens, write_cache);
+  if (dtype == STRATUM_DT_BF16)
+    return launch_pdl(rope_store_kernel<bf16>, n_tokens, threads, smem, stream, (bf16*)qkv, token_pos, token_seq,
+                      block_table, bt_stride, inv_freq, n_pairs, interleaved, mscale, (bf16*)k_cache,
+                      (bf16*)v_cache, n_q, n_kv, head_dim, page_tokens, write_cache);
+  return STRATUM_ERR_DTYPE;
 }
 
 // ---------------------------------------------------------------- seeded fill (random weights on the device)

@@ -68,20 +68,36 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
   const bf16* w1 = w + (size_t)(r1_ok ? r1 : 0) * K;
   const uint4 zero = make_uint4(0, 0, 0, 0);
 
-  for (int c = c_begin; c < c_end; c += SK_UNROLL) {
-    uint4 a0[SK_UNROLL], a1[SK_UNROLL], b[SK_UNROLL][MT];
+  // Weights do not depend on the kernels before this one: the first batch of weight loads is issued
+  // before waiting for them (programmatic dependent launch); rows of x are read only after the wait.
+  // From then on the weights of the next batch are requested before the products of the current one.
+  uint4 a0[SK_UNROLL], a1[SK_UNROLL];
+  auto load_weights = [&](int c, uint4 (&d0)[SK_UNROLL], uint4 (&d1)[SK_UNROLL]) {
 #pragma unroll
     for (int u = 0; u < SK_UNROLL; u++) {
       const int k = (c + u) * 32 + t * 8;
       const bool k_ok = (c + u) < c_end && k < K;       // K is a multiple of 8: a 16-byte piece is all in or all out
-      a0[u] = (k_ok && r0_ok) ? ld_stream16(w0 + k) : zero;
-      a1[u] = (k_ok && r1_ok) ? ld_stream16(w1 + k) : zero;
+      d0[u] = (k_ok && r0_ok) ? ld_stream16(w0 + k) : zero;
+      d1[u] = (k_ok && r1_ok) ? ld_stream16(w1 + k) : zero;
+    }
+  };
+  pdl_trigger();
+  load_weights(c_begin, a0, a1);
+  pdl_wait();
+  for (int c = c_begin; c < c_end; c += SK_UNROLL) {
+    uint4 b[SK_UNROLL][MT];
+#pragma unroll
+    for (int u = 0; u < SK_UNROLL; u++) {
+      const int k = (c + u) * 32 + t * 8;
+      const bool k_ok = (c + u) < c_end && k < K;
 #pragma unroll
       for (int i = 0; i < MT; i++) {
         const int m = i * 8 + g;
         b[u][i] = (k_ok && m < M) ? __ldg((const uint4*)(x + (size_t)m * ldx + k)) : zero;
       }
     }
+    uint4 next0[SK_UNROLL], next1[SK_UNROLL];
+    load_weights(c + SK_UNROLL, next0, next1);
 #pragma unroll
     for (int u = 0; u < SK_UNROLL; u++) {
 #pragma unroll
@@ -90,6 +106,8 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
         mma_bf16_16x8x16(acc[i], a0[u].z, a1[u].z, a0[u].w, a1[u].w, b[u][i].z, b[u][i].w);
       }
     }
+#pragma unroll
+    for (int u = 0; u < SK_UNROLL; u++) { a0[u] = next0[u]; a1[u] = next1[u]; }
   }
   // accumulator: c0,c1 -> (weight row g, x row 2t, 2t+1); c2,c3 -> (weight row g+8, same x rows)
 #pragma unroll
@@ -139,13 +157,12 @@ static int launch_skinny(const bf16* x, const bf16* w, const float* bias, void* 
                          int K, int ldx, int ldo, cudaStream_t stream) {
   const int blocks = (N + 16 * RT - 1) / (16 * RT);
   switch (epilogue) {
-    case 0: gemm_skinny_kernel<MT, RT, 0><<<blocks, SK_WARPS * 32, 0, stream>>>(x, w, bias, out, M, N, K, ldx, ldo); break;
-    case 1: gemm_skinny_kernel<MT, RT, 1><<<blocks, SK_WARPS * 32, 0, stream>>>(x, w, bias, out, M, N, K, ldx, ldo); break;
-    case 2: gemm_skinny_kernel<MT, RT, 2><<<blocks, SK_WARPS * 32, 0, stream>>>(x, w, bias, out, M, N, K, ldx, ldo); break;
-    case 3: gemm_skinny_kernel<MT, RT, 3><<<blocks, SK_WARPS * 32, 0, stream>>>(x, w, bias, out, M, N, K, ldx, ldo); break;
+    case 0: return launch_pdl(gemm_skinny_kernel<MT, RT, 0>, blocks, SK_WARPS * 32, 0, stream, x, w, bias, out, M, N, K, ldx, ldo);
+    case 1: return launch_pdl(gemm_skinny_kernel<MT, RT, 1>, blocks, SK_WARPS * 32, 0, stream, x, w, bias, out, M, N, K, ldx, ldo);
+    case 2: return launch_pdl(gemm_skinny_kernel<MT, RT, 2>, blocks, SK_WARPS * 32, 0, stream, x, w, bias, out, M, N, K, ldx, ldo);
+    case 3: return launch_pdl(gemm_skinny_kernel<MT, RT, 3>, blocks, SK_WARPS * 32, 0, stream, x, w, bias, out, M, N, K, ldx, ldo);
     default: return STRATUM_ERR_SHAPE;
   }
-  return launch_status();
 }
 
 // x: bf16 [M][ldx], w: bf16 [N][K], bias float32 [N] or null, out [M][ldo] (for SwiGLU: [M][N/2]).

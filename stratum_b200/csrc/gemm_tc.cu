@@ -152,6 +152,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   using Smem = TcSmem<BN, STAGES>;
   Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_trigger();          // barriers and tensor memory are set up while the kernel before this one finishes
   constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;      // a power of two >= 32
   constexpr uint32_t STAGE_BYTES = (TC_BM + BN) * TC_BK * sizeof(bf16);
 
@@ -175,6 +176,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = S.tmem_base;
+  pdl_wait();             // from here on x, the residual stream and the output may be touched
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -426,7 +428,8 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
       if (e != cudaSuccess) return (int)e;                                                                  \
       configured = true;                                                                                    \
     }                                                                                                       \
-    kern<<<grid, TC_THREADS, smem, stream>>>(ma, mb, P);                                                    \
+    const int st = launch_pdl(kern, grid, TC_THREADS, smem, stream, ma, mb, P);                             \
+    if (st != 0) return st;                                                                                 \
   }
   switch (epilogue) {
     case 0: TC_LAUNCH(0) break;

@@ -67,6 +67,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ ids,
               float* __restrict__ values) {
   __shared__ MaxIdx scratch[33];
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const MaxIdx best = row_argmax(logits + (size_t)r * ld, vocab, scratch);
   if (threadIdx.x == 0) {
@@ -75,12 +77,69 @@ argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restri
   }
 }
 
+// The same over ARGMAX_SPLITS blocks per row: each block finds the best of its stretch of the row; the block
+// that finishes last (a counter per row tells) picks among the stretches, lowest index first among equals,
+// and resets the counter, so the scratch needs zeroing only once, when it is made.
+#define ARGMAX_SPLITS 32
+__global__ void __launch_bounds__(256)
+argmax_split_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ ids,
+                    float* __restrict__ values, float* __restrict__ part_v, int* __restrict__ part_i,
+                    unsigned* __restrict__ counters) {
+  __shared__ MaxIdx scratch[33];
+  __shared__ bool last;
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x, sp = blockIdx.y;
+  const float* row = logits + (size_t)r * ld;
+  const int chunk = (vocab + ARGMAX_SPLITS - 1) / ARGMAX_SPLITS;
+  const int b = sp * chunk, e = min(vocab, b + chunk);
+  MaxIdx mine{-INFINITY, 0x7fffffff};
+  for (int i = b + threadIdx.x; i < e; i += blockDim.x) {
+    const float v = row[i];
+    if (v > mine.v) { mine.v = v; mine.i = i; }
+  }
+  const MaxIdx best = block_argmax(mine, scratch);
+  if (threadIdx.x == 0) {
+    part_v[r * ARGMAX_SPLITS + sp] = best.v;
+    part_i[r * ARGMAX_SPLITS + sp] = best.i;
+    __threadfence();
+    last = atomicAdd(&counters[r], 1u) == ARGMAX_SPLITS - 1;
+  }
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  if (threadIdx.x < 32) {
+    MaxIdx t{-INFINITY, 0x7fffffff};
+    if (threadIdx.x < ARGMAX_SPLITS) {
+      t.v = __ldcg(&part_v[r * ARGMAX_SPLITS + threadIdx.x]);
+      t.i = __ldcg(&part_i[r * ARGMAX_SPLITS + threadIdx.x]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      MaxIdx other;
+      other.v = __shfl_xor_sync(0xffffffffu, t.v, o);
+      other.i = __shfl_xor_sync(0xffffffffu, t.i, o);
+      t = better(t, other);
+    }
+    if (threadIdx.x == 0) {
+      if (t.i == 0x7fffffff) { t.i = 0; t.v = row[0]; }
+      ids[r] = t.i;
+      if (values) values[r] = t.v;
+      counters[r] = 0;
+    }
+  }
+}
+
+// scratch (optional): part_v float[n_rows*32], part_i int[n_rows*32], counters unsigned[n_rows] zeroed once by
+// the caller; with it, large rows are searched by 32 blocks each.
 STRATUM_EXPORT int stratum_argmax(const float* logits, int ld, int n_rows, int vocab, int* ids, float* values,
-                                  cudaStream_t stream) {
+                                  float* part_v, int* part_i, unsigned* counters, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (vocab < 1) return STRATUM_ERR_SHAPE;
-  argmax_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, ids, values);
-  return launch_status();
+  if (part_v && part_i && counters && vocab >= 8192)
+    return launch_pdl(argmax_split_kernel, dim3(n_rows, ARGMAX_SPLITS), 256, 0, stream, logits, ld, vocab, ids, values,
+                      part_v, part_i, counters);
+  return launch_pdl(argmax_kernel, n_rows, SAMPLE_THREADS, 0, stream, logits, ld, vocab, ids, values);
 }
 
 // ---------------------------------------------------------------- temperature sampling
@@ -104,6 +163,8 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
   __shared__ int cand_i[SAMPLE_CAND_MAX];
   __shared__ unsigned sh_prefix, sh_remaining, sh_count, sh_equal_total;
 
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x, tid = threadIdx.x;
   const float* row = logits + (size_t)r * ld;
   const float temp = temperature[r];
@@ -260,7 +321,6 @@ STRATUM_EXPORT int stratum_sample(const float* logits, int ld, int n_rows, int v
                                   float* values, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (vocab < 1) return STRATUM_ERR_SHAPE;
-  sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, vocab, temperature, top_k, top_p, uniform,
-                                                      ids, values);
-  return launch_status();
+  return launch_pdl(sample_kernel, n_rows, SAMPLE_THREADS, 0, stream, logits, ld, vocab, temperature, top_k, top_p,
+                    uniform, ids, values);
 }

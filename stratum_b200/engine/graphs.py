@@ -6,7 +6,7 @@ head, token pick) is captured once per shape into a CUDA graph and replayed: per
 fills one pinned buffer with the step's description (token ids, positions, page tables, sampling
 numbers), copies it to the device in one go, replays, and reads the picked ids back.
 
-A graph is specific to (rows, page-table width): rows is the batch padded up a little (padding
+A graph is specific to (rows, page-table width, greedy or sampling): rows is the batch padded up a little (padding
 rows carry sequence index -1, which every kernel that touches the cache skips; rows never mix, so
 padding changes no result), and the width is the next power of two of the pages the longest
 sequence holds, which also fixes how the keys are split across warps.  The reference queues its
@@ -40,8 +40,8 @@ def width_bucket(n_pages: int) -> int:
 
 
 class _Captured:
-    def __init__(self, rows: int, width: int, n_groups: int, device):
-        self.rows, self.width = rows, width
+    def __init__(self, rows: int, width: int, n_groups: int, device, greedy: bool):
+        self.rows, self.width, self.greedy = rows, width, greedy
         B = rows
         # int32 words: ids | pos | seq | want | slot | start | len | tables | temperature | top_k | top_p | uniform
         self.off = {}
@@ -73,7 +73,7 @@ class DecodeGraphs:
     def __init__(self, engine: Engine, max_graphs: int = 16):
         self.engine = engine
         self.max_graphs = max_graphs
-        self.graphs: "OrderedDict[Tuple[int, int], _Captured]" = OrderedDict()
+        self.graphs: "OrderedDict[Tuple[int, int, bool], _Captured]" = OrderedDict()
         self.groups = [gi for gi, g in enumerate(engine.cache.groups) if isinstance(g.spec, KVSpec)]
         self.pool = None
         self.done = torch.cuda.Event()
@@ -94,9 +94,12 @@ class DecodeGraphs:
 
     def _forward_and_pick(self, c: _Captured) -> None:
         logits = self.engine.model.forward(self._batch(c), self.engine.cache)
-        K.sample(logits, c.view("temperature", True).view(torch.float32), c.view("top_k", True),
-                 c.view("top_p", True).view(torch.float32), c.view("uniform", True).view(torch.float32),
-                 c.out_ids, c.out_vals)
+        if c.greedy:
+            K.argmax(logits, c.out_ids, c.out_vals)
+        else:
+            K.sample(logits, c.view("temperature", True).view(torch.float32), c.view("top_k", True),
+                     c.view("top_p", True).view(torch.float32), c.view("uniform", True).view(torch.float32),
+                     c.out_ids, c.out_vals)
         c.logits = logits
 
     def _capture(self, c: _Captured) -> None:
@@ -113,13 +116,13 @@ class DecodeGraphs:
         c.graph = g
         self.captures += 1
 
-    def _get(self, rows: int, width: int) -> _Captured:
-        key = (rows, width)
+    def _get(self, rows: int, width: int, greedy: bool) -> _Captured:
+        key = (rows, width, greedy)
         c = self.graphs.get(key)
         if c is None:
             while len(self.graphs) >= self.max_graphs:
                 self.graphs.popitem(last=False)
-            c = _Captured(rows, width, len(self.groups), self.engine.runtime.device)
+            c = _Captured(rows, width, len(self.groups), self.engine.runtime.device, greedy)
             self.graphs[key] = c
         else:
             self.graphs.move_to_end(key)
@@ -142,7 +145,7 @@ class DecodeGraphs:
                 raise StepError(f"slot {s}: token id {t} outside the vocabulary [0, {eng.vocab})")
         eng.cache.reserve(slots, [1] * B)
         before = [eng.cache.length(s) for s in slots]
-        c = self._get(padded_rows(B), width_bucket(pages_for(max(before) + 1)))
+        c = self._get(padded_rows(B), width_bucket(pages_for(max(before) + 1)), not (temperature > 0.0))
         R, W = c.rows, c.width
         h = c.np
         v = lambda name: c.view(name, False)          # noqa: E731

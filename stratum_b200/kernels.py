@@ -290,13 +290,32 @@ def attention_mma(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 
 
 # ------------------------------------------------------------------ sampling
+ARGMAX_SPLITS = 32
+_argmax_scratch = None
+
+
+def _argmax_scratch_for(rows: int, device):
+    """(best values, best ids, counters) for the many-blocks-per-row argmax; the counters start at zero and
+    every launch leaves them at zero."""
+    global _argmax_scratch
+    if _argmax_scratch is None or _argmax_scratch[2].numel() < rows:
+        n = max(rows, 64)
+        _argmax_scratch = (torch.empty(n * ARGMAX_SPLITS, dtype=torch.float32, device=device),
+                           torch.empty(n * ARGMAX_SPLITS, dtype=torch.int32, device=device),
+                           torch.zeros(n, dtype=torch.int32, device=device))
+    return _argmax_scratch
+
+
 def argmax(logits: torch.Tensor, ids: torch.Tensor, values: Optional[torch.Tensor] = None) -> None:
+    """ids[r] = index of the largest logit of row r, the lowest index among equals."""
     _need(logits, "logits", torch.float32, contiguous=False); _need(ids, "ids", torch.int32)
     if values is not None:
         _need(values, "values", torch.float32)
-    f = _fn("sampling", "stratum_argmax", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    pv, pi, cnt = _argmax_scratch_for(logits.shape[0], logits.device)
+    f = _fn("sampling", "stratum_argmax",
+            [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(f(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(ids), _ptr(values),
-             _stream()), "argmax")
+             _ptr(pv), _ptr(pi), _ptr(cnt), _stream()), "argmax")
 
 
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
