@@ -28,7 +28,8 @@
 
 #define AM_WARPS 4
 
-__device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg((const uint4*)p); }
+// q and the newest rows of the cache were written by the kernel before this one
+__device__ __forceinline__ uint4 ldg16(const void* p) { return ld_fresh((const uint4*)p); }
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -133,23 +134,39 @@ attention_mma_kernel(const AttnParams P) {
   const size_t head_off = (size_t)kvh * P.page_tokens * Hd;
   const size_t page_stride = (size_t)P.n_kv * P.page_tokens * Hd;
 
-  for (int key0 = k_begin; key0 < k_end; key0 += 16) {
+  // K of the next block of 16 keys is requested before the current block is worked on; V of the current block
+  // is requested first thing, so that it arrives while the scores are computed.
+  auto block_base = [&](int key0) -> size_t {
     const int page = (key0 == k_begin) ? first_page : bt[key0 / P.page_tokens];
-    const size_t base = (size_t)page * page_stride + head_off + (size_t)(key0 % P.page_tokens) * Hd;
-    const bf16* kp = P.k_cache + base;
-    const bf16* vp = P.v_cache + base;
-    uint4 ka[CH], kb[CH], va[CH], vb[CH];
+    return (size_t)page * page_stride + head_off + (size_t)(key0 % P.page_tokens) * Hd;
+  };
+  uint4 ka[CH], kb[CH];
+  size_t base = 0;
+  if (k_begin < k_end) {
+    base = block_base(k_begin);
 #pragma unroll
     for (int c = 0; c < CH; c++) {
       const int d = 32 * c + 8 * t;
-      if (d < Hd) {
-        ka[c] = ldg16(kp + (size_t)g * Hd + d);
-        kb[c] = ldg16(kp + (size_t)(g + 8) * Hd + d);
-        va[c] = ldg16(vp + (size_t)g * Hd + d);
-        vb[c] = ldg16(vp + (size_t)(g + 8) * Hd + d);
-      } else {
-        ka[c] = kb[c] = va[c] = vb[c] = zero4;
-      }
+      ka[c] = d < Hd ? ldg16(P.k_cache + base + (size_t)g * Hd + d) : zero4;
+      kb[c] = d < Hd ? ldg16(P.k_cache + base + (size_t)(g + 8) * Hd + d) : zero4;
+    }
+  }
+  for (int key0 = k_begin; key0 < k_end; key0 += 16) {
+    const bf16* vp = P.v_cache + base;
+    uint4 va[CH], vb[CH], nka[CH], nkb[CH];
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+      const int d = 32 * c + 8 * t;
+      va[c] = d < Hd ? ldg16(vp + (size_t)g * Hd + d) : zero4;
+      vb[c] = d < Hd ? ldg16(vp + (size_t)(g + 8) * Hd + d) : zero4;
+    }
+    const bool more = key0 + 16 < k_end;
+    if (more) base = block_base(key0 + 16);
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+      const int d = 32 * c + 8 * t;
+      nka[c] = (more && d < Hd) ? ldg16(P.k_cache + base + (size_t)g * Hd + d) : zero4;
+      nkb[c] = (more && d < Hd) ? ldg16(P.k_cache + base + (size_t)(g + 8) * Hd + d) : zero4;
     }
     // scores: s[i] is the tile of keys key0 + 8i + {2t, 2t+1}; [0],[1] row g, [2],[3] row g+8
     float s[2][4];
@@ -210,6 +227,8 @@ attention_mma_kernel(const AttnParams P) {
         mma16816(o[4 * c + i], pa0, pa1, pa2, pa3, b0, b1);
       }
     }
+#pragma unroll
+    for (int c = 0; c < CH; c++) { ka[c] = nka[c]; kb[c] = nkb[c]; }
   }
   // denominators across the four lanes of a row
 #pragma unroll
@@ -266,17 +285,17 @@ attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict
   pdl_wait();
   const float* ml = part_ml + (size_t)item * n_splits * 2;
   float m = -INFINITY;
-  for (int s = 0; s < n_splits; s++) m = fmaxf(m, ml[2 * s]);
+  for (int s = 0; s < n_splits; s++) m = fmaxf(m, ld_fresh(ml + 2 * s));
   const float* po = part_o + (size_t)item * n_splits * head_dim;
   const int d = threadIdx.x;
   if (d >= head_dim) return;
   float l = 0.f, acc = 0.f;
 #pragma unroll 4
   for (int s = 0; s < n_splits; s++) {
-    const float ms = ml[2 * s];
+    const float ms = ld_fresh(ml + 2 * s);
     const float wgt = (ms == -INFINITY) ? 0.f : __expf(ms - m);
-    l += ml[2 * s + 1] * wgt;
-    acc += po[(size_t)s * head_dim + d] * wgt;
+    l += ld_fresh(ml + 2 * s + 1) * wgt;
+    acc += ld_fresh(po + (size_t)s * head_dim + d) * wgt;
   }
   out[(size_t)tok * ldo + (size_t)h * head_dim + d] = __float2bfloat16_rn(acc / l);
 }

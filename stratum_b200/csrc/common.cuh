@@ -58,6 +58,17 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 // may read weights and the step's description, compute addresses, warm up); pdl_wait() returns once
 // every earlier kernel has completed and its writes are visible.  pdl_trigger() lets the kernel
 // after this one start its own preamble.  Launched the ordinary way, both are no-ops.
+//
+// Loads of anything an earlier kernel of the same step produced must not use the read-only path
+// (ld.global.nc / __ldg, which the compiler also picks by itself for `const T* __restrict__`): with an early
+// start that data changes during this kernel's lifetime, and a stale line may be served.  Such loads go
+// through ld_fresh (ld.global.cg: served from L2, where the producer's writes are).
+__device__ __forceinline__ float ld_fresh(const float* p) { return __ldcg(p); }
+__device__ __forceinline__ float4 ld_fresh(const float4* p) { return __ldcg(p); }
+__device__ __forceinline__ uint4 ld_fresh(const uint4* p) { return __ldcg(p); }
+__device__ __forceinline__ float ld_fresh(const bf16* p) {
+  return __bfloat162float(__ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(p))));
+}
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -49,13 +49,13 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
   const float* xr = x + (size_t)src * hidden;
   float ss = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float v = xr[i];
+    const float v = ld_fresh(xr + i);
     ss = fmaf(v, v, ss);
   }
   ss = block_sum(ss, scratch);
   const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
   T* o = out + (size_t)r * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<T>(xr[i] * scale * gain[i]);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<T>(ld_fresh(xr + i) * scale * gain[i]);
 }
 
 // The same, four values per thread and iteration held in registers between the sum and the scaling, so a
@@ -81,7 +81,7 @@ __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __r
 #pragma unroll
   for (int j = 0; j < VPT; j++) {
     const int i = threadIdx.x + j * blockDim.x;
-    v[j] = i < n4 ? xr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    v[j] = i < n4 ? ld_fresh(xr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
     ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
   }
@@ -170,64 +170,48 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ t
                                   int bt_stride, const float* __restrict__ inv_freq, int n_pairs,
                                   int interleaved, float mscale, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                   int n_q, int n_kv, int head_dim, int page_tokens, int write_cache) {
-  extern __shared__ float cs[];   // cos[n_pairs], sin[n_pairs]
+  // one block per (token, head): q heads, then k heads, then v heads; one thread per pair of dimensions
   pdl_trigger();
-  // positions, page tables and frequencies belong to the step's description and the weights: they are
-  // read, and the angles computed, before waiting for the projection that produced qkv
-  const int t = blockIdx.x;
+  const int t = blockIdx.x, h = blockIdx.y;
   const int seq = token_seq[t];
   if (seq < 0) return;
+  const int slot = threadIdx.x;                 // pair slot: < n_pairs rotates, the rest pass through
+  if (slot >= head_dim / 2) return;
+  const bool is_q = h < n_q, is_k = !is_q && h < n_q + n_kv;
+  if (!is_q && !write_cache) return;
+  // positions, page tables and frequencies belong to the step's description and the weights: they are read,
+  // and the angle evaluated, before waiting for the projection that produced qkv
   const int pos = token_pos[t];
-  for (int k = threadIdx.x; k < n_pairs; k += blockDim.x) {
-    const float angle = (float)pos * inv_freq[k];
-    float s, c;
+  int i0, i1;
+  float c = 1.f, s = 0.f;
+  if (slot < n_pairs && (is_q || is_k)) {
+    if (interleaved) { i0 = 2 * slot; i1 = i0 + 1; } else { i0 = slot; i1 = slot + n_pairs; }
+    const float angle = (float)pos * inv_freq[slot];
     sincosf(angle, &s, &c);
-    cs[k] = c * mscale;
-    cs[n_pairs + k] = s * mscale;
+    c *= mscale;
+    s *= mscale;
+  } else {
+    // dimensions beyond the rotated ones, and v: two plain neighbours per thread
+    i0 = (is_q || is_k) ? 2 * n_pairs + 2 * (slot - n_pairs) : 2 * slot;
+    i1 = i0 + 1;
   }
-  const int row_elems = (n_q + 2 * n_kv) * head_dim;
-  T* row = qkv + (size_t)t * row_elems;
-  const int half = head_dim / 2;          // work items per head: one per pair slot (rotated or not)
-  size_t kv_row_base = 0;
-  if (write_cache) {
+  T* dst = nullptr;
+  if (!is_q) {
     const int page = block_table[(size_t)seq * bt_stride + pos / page_tokens];
-    kv_row_base = ((size_t)page * n_kv * page_tokens + (pos % page_tokens)) * (size_t)head_dim;
+    const int kvh = is_k ? h - n_q : h - n_q - n_kv;
+    dst = (is_k ? k_cache : v_cache) +
+          (((size_t)page * n_kv + kvh) * page_tokens + (pos % page_tokens)) * (size_t)head_dim;
   }
-  __syncthreads();
+  T* hp = qkv + (size_t)t * ((size_t)(n_q + 2 * n_kv) * head_dim) + (size_t)h * head_dim;
   pdl_wait();
-  const size_t head_stride = (size_t)page_tokens * head_dim;   // between kv heads inside a page
-  // q and k heads: item = (head, slot); slot < n_pairs rotates a pair, slot >= n_pairs copies two plain dims
-  const int n_rot_heads = n_q + (write_cache ? n_kv : 0);
-  for (int item = threadIdx.x; item < n_rot_heads * half; item += blockDim.x) {
-    const int h = item / half, slot = item - h * half;
-    T* hp = row + (size_t)h * head_dim;
-    int i0, i1;
-    float y0, y1;
-    if (slot < n_pairs) {
-      if (interleaved) { i0 = 2 * slot; i1 = i0 + 1; } else { i0 = slot; i1 = slot + n_pairs; }
-      const float x0 = to_float(hp[i0]), x1 = to_float(hp[i1]);
-      const float c = cs[slot], s = cs[n_pairs + slot];
-      y0 = x0 * c - x1 * s;
-      y1 = x0 * s + x1 * c;
-    } else {
-      i0 = 2 * n_pairs + 2 * (slot - n_pairs); i1 = i0 + 1;
-      y0 = to_float(hp[i0]); y1 = to_float(hp[i1]);
-    }
-    if (h < n_q) {
-      hp[i0] = from_float<T>(y0);
-      hp[i1] = from_float<T>(y1);
-    } else {
-      T* dst = k_cache + kv_row_base + (size_t)(h - n_q) * head_stride;
-      dst[i0] = from_float<T>(y0);
-      dst[i1] = from_float<T>(y1);
-    }
-  }
-  if (write_cache) {
-    const T* vsrc = row + (size_t)(n_q + n_kv) * head_dim;
-    for (int item = threadIdx.x; item < n_kv * head_dim; item += blockDim.x) {
-      const int h = item / head_dim, d = item - h * head_dim;
-      v_cache[kv_row_base + (size_t)h * head_stride + d] = vsrc[item];
-    }
+  const float x0 = ld_fresh(hp + i0), x1 = ld_fresh(hp + i1);
+  const float y0 = x0 * c - x1 * s, y1 = x0 * s + x1 * c;     // c = 1, s = 0 where nothing rotates: exact copy
+  if (is_q) {
+    hp[i0] = from_float<T>(y0);
+    hp[i1] = from_float<T>(y1);
+  } else {
+    dst[i0] = from_float<T>(y0);
+    dst[i1] = from_float<T>(y1);
   }
 }
 
@@ -237,15 +221,16 @@ STRATUM_EXPORT int stratum_rope_store(void* qkv, int dtype, const int* token_pos
                                       int n_q, int n_kv, int head_dim, int page_tokens, int write_cache,
                                       cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (head_dim % 2 != 0 || 2 * n_pairs > head_dim || n_pairs < 0) return STRATUM_ERR_SHAPE;
-  const int threads = 256;
-  const size_t smem = (size_t)2 * n_pairs * sizeof(float);
+  if (head_dim % 2 != 0 || 2 * n_pairs > head_dim || n_pairs < 0 || head_dim > 2048) return STRATUM_ERR_SHAPE;
+  if (n_q + 2 * n_kv > 65535) return STRATUM_ERR_LIMIT;
+  const int threads = ((head_dim / 2 + 31) / 32) * 32;
+  const dim3 grid(n_tokens, n_q + 2 * n_kv);
   if (dtype == STRATUM_DT_F32)
-    return launch_pdl(rope_store_kernel<float>, n_tokens, threads, smem, stream, (float*)qkv, token_pos, token_seq,
+    return launch_pdl(rope_store_kernel<float>, grid, threads, 0, stream, (float*)qkv, token_pos, token_seq,
                       block_table, bt_stride, inv_freq, n_pairs, interleaved, mscale, (float*)k_cache,
                       (float*)v_cache, n_q, n_kv, head_dim, page_tokens, write_cache);
   if (dtype == STRATUM_DT_BF16)
-    return launch_pdl(rope_store_kernel<bf16>, n_tokens, threads, smem, stream, (bf16*)qkv, token_pos, token_seq,
+    return launch_pdl(rope_store_kernel<bf16>, grid, threads, 0, stream, (bf16*)qkv, token_pos, token_seq,
                       block_table, bt_stride, inv_freq, n_pairs, interleaved, mscale, (bf16*)k_cache,
                       (bf16*)v_cache, n_q, n_kv, head_dim, page_tokens, write_cache);
   return STRATUM_ERR_DTYPE;

@@ -46,13 +46,21 @@ __device__ __forceinline__ void mma_bf16_16x8x16(float (&c)[4], uint32_t a0, uin
 template <int MT, int RT, int EPI>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const float* __restrict__ bias,
-                   void* __restrict__ out, int M, int N, int K, int ldx, int ldo) {
+                   void* __restrict__ out, int M, int N, int K, int ldx, int ldo, int groups_per_block) {
   constexpr int KS = SK_WARPS / RT;                 // K parts
   __shared__ float part[RT][KS][MT * 8][16 + 1];    // [row tile][k part][x row][weight row]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int rt = warp / KS, ks = warp % KS;
-  const int n0 = (blockIdx.x * RT + rt) * 16;
+  pdl_trigger();
+  // a block works through `groups_per_block` consecutive groups of RT row tiles, so that the grid can be
+  // sized to what the GPU holds at once and every block gets (almost) the same share of W
+  const int n_groups = (N + 16 * RT - 1) / (16 * RT);
+  const int group_begin = blockIdx.x * groups_per_block;
+  const int group_end = min(n_groups, group_begin + groups_per_block);
+  bool waited = false;
+  for (int group = group_begin; group < group_end; group++) {
+  const int n0 = (group * RT + rt) * 16;
   // K range of this warp, in chunks of 32
   const int n_chunks = (K + 31) / 32;
   const int per = (n_chunks + KS - 1) / KS;
@@ -70,8 +78,8 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
 
   // Weights do not depend on the kernels before this one: the first batch of weight loads is issued
   // before waiting for them (programmatic dependent launch); rows of x are read only after the wait.
-  // From then on the weights of the next batch are requested before the products of the current one.
-  uint4 a0[SK_UNROLL], a1[SK_UNROLL];
+  // From then on the next batch of weights and rows is requested before the products of the current one.
+  uint4 a0[SK_UNROLL], a1[SK_UNROLL], b[SK_UNROLL][MT];
   auto load_weights = [&](int c, uint4 (&d0)[SK_UNROLL], uint4 (&d1)[SK_UNROLL]) {
 #pragma unroll
     for (int u = 0; u < SK_UNROLL; u++) {
@@ -81,11 +89,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
       d1[u] = (k_ok && r1_ok) ? ld_stream16(w1 + k) : zero;
     }
   };
-  pdl_trigger();
-  load_weights(c_begin, a0, a1);
-  pdl_wait();
-  for (int c = c_begin; c < c_end; c += SK_UNROLL) {
-    uint4 b[SK_UNROLL][MT];
+  auto load_rows = [&](int c, uint4 (&d)[SK_UNROLL][MT]) {
 #pragma unroll
     for (int u = 0; u < SK_UNROLL; u++) {
       const int k = (c + u) * 32 + t * 8;
@@ -93,11 +97,18 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
 #pragma unroll
       for (int i = 0; i < MT; i++) {
         const int m = i * 8 + g;
-        b[u][i] = (k_ok && m < M) ? __ldg((const uint4*)(x + (size_t)m * ldx + k)) : zero;
+        d[u][i] = (k_ok && m < M) ? ld_fresh((const uint4*)(x + (size_t)m * ldx + k)) : zero;
       }
     }
-    uint4 next0[SK_UNROLL], next1[SK_UNROLL];
+  };
+  load_weights(c_begin, a0, a1);
+  if (!waited) { pdl_wait(); waited = true; }
+  load_rows(c_begin, b);
+  for (int c = c_begin; c < c_end; c += SK_UNROLL) {
+    // request the next batch of weights and rows before multiplying the current one
+    uint4 next0[SK_UNROLL], next1[SK_UNROLL], nextb[SK_UNROLL][MT];
     load_weights(c + SK_UNROLL, next0, next1);
+    load_rows(c + SK_UNROLL, nextb);
 #pragma unroll
     for (int u = 0; u < SK_UNROLL; u++) {
 #pragma unroll
@@ -107,7 +118,11 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
       }
     }
 #pragma unroll
-    for (int u = 0; u < SK_UNROLL; u++) { a0[u] = next0[u]; a1[u] = next1[u]; }
+    for (int u = 0; u < SK_UNROLL; u++) {
+      a0[u] = next0[u]; a1[u] = next1[u];
+#pragma unroll
+      for (int i = 0; i < MT; i++) b[u][i] = nextb[u][i];
+    }
   }
   // accumulator: c0,c1 -> (weight row g, x row 2t, 2t+1); c2,c3 -> (weight row g+8, same x rows)
 #pragma unroll
@@ -123,7 +138,7 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
     for (int idx = threadIdx.x; idx < RT * MT * 8 * 16; idx += SK_WARPS * 32) {
       const int tile = idx / (MT * 8 * 16), rem = idx % (MT * 8 * 16);
       const int m = rem / 16, r = rem % 16;
-      const int n = (blockIdx.x * RT + tile) * 16 + r;
+      const int n = (group * RT + tile) * 16 + r;
       if (m >= M || n >= N) continue;
       float v = 0.f;
 #pragma unroll
@@ -131,14 +146,14 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
       if (bias) v += bias[n];
       const size_t o = (size_t)m * ldo + n;
       if (EPI == 0) ((bf16*)out)[o] = __float2bfloat16_rn(v);
-      else if (EPI == 1) ((float*)out)[o] += v;
+      else if (EPI == 1) ((float*)out)[o] = ld_fresh((const float*)out + o) + v;
       else ((float*)out)[o] = v;
     }
   } else {
     for (int idx = threadIdx.x; idx < RT * MT * 8 * 8; idx += SK_WARPS * 32) {
       const int tile = idx / (MT * 8 * 8), rem = idx % (MT * 8 * 8);
       const int m = rem / 8, jr = rem % 8;
-      const int n = (blockIdx.x * RT + tile) * 16 + 2 * jr;       // gate row; up row is n + 1
+      const int n = (group * RT + tile) * 16 + 2 * jr;       // gate row; up row is n + 1
       if (m >= M || n + 1 >= N) continue;
       float gate = 0.f, up = 0.f;
 #pragma unroll
@@ -150,17 +165,46 @@ gemm_skinny_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const
       ((bf16*)out)[(size_t)m * ldo + (n >> 1)] = __float2bfloat16_rn(gate / (1.0f + expf(-gate)) * up);
     }
   }
+  __syncthreads();          // the partial sums are reused by the next group
+  }
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+template <int MT, int RT, int EPI>
+static int launch_skinny_epi(const bf16* x, const bf16* w, const float* bias, void* out, int M, int N, int K,
+                             int ldx, int ldo, cudaStream_t stream) {
+  auto kern = gemm_skinny_kernel<MT, RT, EPI>;
+  static int resident = 0;                 // blocks of this kernel the whole GPU holds at once
+  if (!resident) {
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, SK_WARPS * 32, 0) != cudaSuccess || per_sm < 1)
+      per_sm = 1;
+    resident = per_sm * sm_count();
+  }
+  const int n_groups = (N + 16 * RT - 1) / (16 * RT);
+  const int per_block = (n_groups + resident - 1) / resident;
+  const int blocks = (n_groups + per_block - 1) / per_block;
+  return launch_pdl(kern, blocks, SK_WARPS * 32, 0, stream, x, w, bias, out, M, N, K, ldx, ldo, per_block);
 }
 
 template <int MT, int RT>
 static int launch_skinny(const bf16* x, const bf16* w, const float* bias, void* out, int epilogue, int M, int N,
                          int K, int ldx, int ldo, cudaStream_t stream) {
-  const int blocks = (N + 16 * RT - 1) / (16 * RT);
   switch (epilogue) {
-    case 0: return launch_pdl(gemm_skinny_kernel<MT, RT, 0>, blocks, SK_WARPS * 32, 0, stream, x, w, bias, out, M, N, K, ldx, ldo);
-    case 1: return launch_pdl(gemm_skinny_kernel<MT, RT, 1>, blocks, SK_WARPS * 32, 0, stream, x, w, bias, out, M, N, K, ldx, ldo);
-    case 2: return launch_pdl(gemm_skinny_kernel<MT, RT, 2>, blocks, SK_WARPS * 32, 0, stream, x, w, bias, out, M, N, K, ldx, ldo);
-    case 3: return launch_pdl(gemm_skinny_kernel<MT, RT, 3>, blocks, SK_WARPS * 32, 0, stream, x, w, bias, out, M, N, K, ldx, ldo);
+    case 0: return launch_skinny_epi<MT, RT, 0>(x, w, bias, out, M, N, K, ldx, ldo, stream);
+    case 1: return launch_skinny_epi<MT, RT, 1>(x, w, bias, out, M, N, K, ldx, ldo, stream);
+    case 2: return launch_skinny_epi<MT, RT, 2>(x, w, bias, out, M, N, K, ldx, ldo, stream);
+    case 3: return launch_skinny_epi<MT, RT, 3>(x, w, bias, out, M, N, K, ldx, ldo, stream);
     default: return STRATUM_ERR_SHAPE;
   }
 }

@@ -325,7 +325,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 for (int q = 0; q < CW / 4; q++) {
                   float4 w4 = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
                   if (EPI == 1) {
-                    const float4 old = reinterpret_cast<float4*>(o)[q];
+                    const float4 old = ld_fresh(reinterpret_cast<const float4*>(o) + q);
                     w4.x += old.x; w4.y += old.y; w4.z += old.z; w4.w += old.w;
                   }
                   reinterpret_cast<float4*>(o)[q] = w4;
@@ -333,7 +333,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               } else {
 #pragma unroll
                 for (int j = 0; j < CW; j++)
-                  if (col_b0 + j < P.N) o[j] = (EPI == 1) ? o[j] + v[j] : v[j];
+                  if (col_b0 + j < P.N) o[j] = (EPI == 1) ? ld_fresh(o + j) + v[j] : v[j];
               }
             }
           }
@@ -353,7 +353,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             } else if (m < P.M && n < P.N) {
               const size_t idx = (size_t)m * P.ldo + n;
               if (EPI == 0) ((bf16*)P.out)[idx] = __float2bfloat16_rn(v);
-              else if (EPI == 1) ((float*)P.out)[idx] += v;
+              else if (EPI == 1) ((float*)P.out)[idx] = ld_fresh((const float*)P.out + idx) + v;
               else ((float*)P.out)[idx] = v;
             }
           }

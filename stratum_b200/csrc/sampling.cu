@@ -55,11 +55,11 @@ __device__ __forceinline__ MaxIdx block_argmax(MaxIdx mine, MaxIdx* scratch /* 3
 __device__ __forceinline__ MaxIdx row_argmax(const float* __restrict__ row, int vocab, MaxIdx* scratch) {
   MaxIdx mine{-INFINITY, 0x7fffffff};
   for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = row[i];
+    const float v = ld_fresh(row + (i));
     if (v > mine.v) { mine.v = v; mine.i = i; }      // ascending i per thread: first of equals is kept
   }
   MaxIdx r = block_argmax(mine, scratch);
-  if (r.i == 0x7fffffff) { r.i = 0; r.v = row[0]; }  // every logit is -inf or NaN: index 0, as a scalar scan would give
+  if (r.i == 0x7fffffff) { r.i = 0; r.v = ld_fresh(row + (0)); }  // every logit is -inf or NaN: index 0, as a scalar scan would give
   return r;
 }
 
@@ -95,7 +95,7 @@ argmax_split_kernel(const float* __restrict__ logits, int ld, int vocab, int* __
   const int b = sp * chunk, e = min(vocab, b + chunk);
   MaxIdx mine{-INFINITY, 0x7fffffff};
   for (int i = b + threadIdx.x; i < e; i += blockDim.x) {
-    const float v = row[i];
+    const float v = ld_fresh(row + (i));
     if (v > mine.v) { mine.v = v; mine.i = i; }
   }
   const MaxIdx best = block_argmax(mine, scratch);
@@ -122,7 +122,7 @@ argmax_split_kernel(const float* __restrict__ logits, int ld, int vocab, int* __
       t = better(t, other);
     }
     if (threadIdx.x == 0) {
-      if (t.i == 0x7fffffff) { t.i = 0; t.v = row[0]; }
+      if (t.i == 0x7fffffff) { t.i = 0; t.v = ld_fresh(row + (0)); }
       ids[r] = t.i;
       if (values) values[r] = t.v;
       counters[r] = 0;
@@ -184,7 +184,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
     const int chunk = (vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
     const int b = tid * chunk, e = min(vocab, b + chunk);
     float s = 0.f;
-    for (int i = b; i < e; i++) s += expf((row[i] - best.v) * inv_t);
+    for (int i = b; i < e; i++) s += expf((ld_fresh(row + (i)) - best.v) * inv_t);
     partial[tid] = s;
     __syncthreads();
     if (tid == 0) {
@@ -203,12 +203,12 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
         const int ob = owner * chunk, oe = min(vocab, ob + chunk);
         pick = oe - 1;
         for (int i = ob; i < oe; i++) {
-          cum += expf((row[i] - best.v) * inv_t);
+          cum += expf((ld_fresh(row + (i)) - best.v) * inv_t);
           if (target < cum) { pick = i; break; }
         }
       }
       ids[r] = pick;
-      if (values) values[r] = row[pick];
+      if (values) values[r] = ld_fresh(row + (pick));
     }
     return;
   }
@@ -226,7 +226,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
     const unsigned prefix = sh_prefix;
     const unsigned mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
     for (int i = tid; i < vocab; i += blockDim.x) {
-      const uint32_t key = float_key(row[i]);
+      const uint32_t key = float_key(ld_fresh(row + (i)));
       if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
     }
     __syncthreads();
@@ -251,10 +251,10 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
   if (tid == 0) sh_count = 0;
   __syncthreads();
   for (int i = tid; i < vocab; i += blockDim.x) {
-    const uint32_t key = float_key(row[i]);
+    const uint32_t key = float_key(ld_fresh(row + (i)));
     if (key > kth_key || (take_all_equal && key == kth_key)) {
       const unsigned slot = atomicAdd(&sh_count, 1u);
-      cand_v[slot] = row[i];
+      cand_v[slot] = ld_fresh(row + (i));
       cand_i[slot] = i;
     }
   }
@@ -262,7 +262,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
   if (tid == 0 && !take_all_equal) {
     unsigned slot = sh_count, taken = 0;
     for (int i = 0; i < vocab && taken < n_equal_wanted; i++) {
-      if (float_key(row[i]) == kth_key) { cand_v[slot] = row[i]; cand_i[slot] = i; slot++; taken++; }
+      if (float_key(ld_fresh(row + (i))) == kth_key) { cand_v[slot] = ld_fresh(row + (i)); cand_i[slot] = i; slot++; taken++; }
     }
     sh_count = slot;
   }
