@@ -372,6 +372,251 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+// ---------------------------------------------------------------- few rows of x: stream-K
+// Decode steps multiply a handful of rows of x by all of W, so the time is the time to read W once, and
+// the work must be spread evenly over every SM whatever N is.  The k-blocks of all tiles (128 weight rows
+// x 64 k each) form one sequence of tiles*n_kb blocks; CTA c takes the contiguous stretch
+// [c*total/G, (c+1)*total/G).  A stretch covers the end of one tile, some whole tiles and the beginning of
+// another.  Whole tiles go straight from tensor memory through the epilogue.  A tile shared between CTAs is
+// written as float32 partial sums to scratch; a counter per tile tells the CTA that arrives last, which adds
+// the partial sums in the order of k (the order of the CTA numbers) and runs the epilogue.  The split depends
+// only on the shapes and the grid, never on the rows of x, so a row's result does not depend on its batch.
+// W tiles do not depend on earlier kernels and are requested before the programmatic-launch wait.
+struct SkParams {
+  const float* bias;
+  void* out;
+  int* status;
+  float* scratch;         // [gridDim.x][2][BN][128] float32 partial tiles (first / last tile of a CTA's stretch)
+  unsigned* counters;     // [tiles], zero before and after every launch
+  int M, N, K, ldo;
+  int tiles, n_kb, total_kb;
+};
+
+__device__ __forceinline__ int sk_begin(int c, int G, int total) { return (int)((long long)c * total / G); }
+__device__ __forceinline__ int sk_owner(int i, int G, int total) {
+  int c = (int)((long long)i * G / total);
+  while (c + 1 < G && sk_begin(c + 1, G, total) <= i) c++;
+  while (c > 0 && sk_begin(c, G, total) > i) c--;
+  return c;
+}
+
+// Final values of weight row n for x rows m0 .. m0+CW-1 (one thread per weight row, lanes are neighbours in n).
+template <int EPI, int CW>
+__device__ __forceinline__ void sk_store(const SkParams& P, int n, int m0, float (&v)[CW]) {
+#pragma unroll
+  for (int j = 0; j < CW; j++) {
+    const int m = m0 + j;
+    float val = v[j];
+    if (P.bias && n < P.N) val += P.bias[n];
+    if (EPI == 3) {
+      val = __bfloat162float(__float2bfloat16_rn(val));
+      const float other = __shfl_xor_sync(0xffffffffu, val, 1);     // gate (even n) <-> up (odd n)
+      if (m < P.M && n + 1 < P.N && (n & 1) == 0)
+        ((bf16*)P.out)[(size_t)m * P.ldo + (n >> 1)] = __float2bfloat16_rn(val / (1.0f + __expf(-val)) * other);
+    } else if (m < P.M && n < P.N) {
+      const size_t idx = (size_t)m * P.ldo + n;
+      if (EPI == 0) ((bf16*)P.out)[idx] = __float2bfloat16_rn(val);
+      else if (EPI == 1) ((float*)P.out)[idx] = ld_fresh((const float*)P.out + idx) + val;
+      else ((float*)P.out)[idx] = val;
+    }
+  }
+}
+
+template <int BN, int STAGES>
+struct SkSmem {
+  alignas(1024) bf16 a[STAGES][TC_BM * TC_BK];
+  alignas(1024) bf16 b[STAGES][BN * TC_BK];
+  uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int last_flag;
+};
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_streamk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                       const SkParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  using Smem = SkSmem<BN, STAGES>;
+  Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_trigger();
+  constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+  constexpr uint32_t A_BYTES = TC_BM * TC_BK * sizeof(bf16), B_BYTES = BN * TC_BK * sizeof(bf16);
+  const int G = gridDim.x, c = blockIdx.x;
+  const int kb0 = sk_begin(c, G, P.total_kb), kb1 = sk_begin(c + 1, G, P.total_kb);
+  volatile int* abort_flag = &S.abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
+    for (int b = 0; b < 2; b++) { mbar_init(&S.acc_full[b], 1); mbar_init(&S.acc_empty[b], 4); }
+    S.abort_flag = 0;
+    S.last_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(&S.tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = S.tmem_base;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+      const int count = kb1 - kb0;
+      const int pre = count < STAGES ? count : STAGES;
+      // weights of the first stages: requested while the kernel before this one may still be running
+      for (int i = 0; i < pre; i++) {
+        const int g = kb0 + i;
+        mbar_expect_tx(&S.full[i], A_BYTES + B_BYTES);
+        tma_load_2d(&map_w, S.a[i], &S.full[i], (g % P.n_kb) * TC_BK, (g / P.n_kb) * TC_BM);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; i++) tma_load_2d(&map_x, S.b[i], &S.full[i], ((kb0 + i) % P.n_kb) * TC_BK, 0);
+      bool ok = true;
+      for (int i = pre; i < count; i++) {
+        const int g = kb0 + i, s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (!mbar_wait(&S.empty[s], ph ^ 1, abort_flag)) {
+          atomicCAS(P.status, 0, 101); S.abort_flag = 1; ok = false; break;
+        }
+        mbar_expect_tx(&S.full[s], A_BYTES + B_BYTES);
+        tma_load_2d(&map_w, S.a[s], &S.full[s], (g % P.n_kb) * TC_BK, (g / P.n_kb) * TC_BM);
+        tma_load_2d(&map_x, S.b[s], &S.full[s], (g % P.n_kb) * TC_BK, 0);
+      }
+      if (!ok) {
+        for (int i = 0; i < 2000; i++) __nanosleep(1000);   // let copies already issued land
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc_bf16(BN);
+      uint32_t it = 0, seg = 0;
+      bool ok = true;
+      int g = kb0;
+      while (g < kb1 && ok) {
+        const int tile = g / P.n_kb;
+        const int seg_end = min(kb1, (tile + 1) * P.n_kb);
+        const int buf = seg & 1;
+        if (!mbar_wait(&S.acc_empty[buf], ((seg >> 1) & 1) ^ 1, abort_flag)) {
+          atomicCAS(P.status, 0, 102); S.abort_flag = 1; ok = false; break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        bool first = true;
+        for (; g < seg_end; g++, it++) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&S.full[s], (it / STAGES) & 1, abort_flag)) {
+            atomicCAS(P.status, 0, 103); S.abort_flag = 1; ok = false; break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(S.a[s]), b_addr = smem_u32(S.b[s]);
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; k++) {
+            umma_bf16(d_tmem, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
+                      (first && k == 0) ? 0u : 1u);
+          }
+          first = false;
+          umma_commit(&S.empty[s]);
+        }
+        if (ok) umma_commit(&S.acc_full[buf]);
+        seg++;
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5)
+    pdl_wait();                                   // the output, the residual stream and the scratch are shared
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;          // weight row within the tile held by this thread
+    const int first_tile = kb0 / P.n_kb;
+    constexpr int CW = (BN >= 32) ? 32 : 16;
+    uint32_t seg = 0;
+    bool ok = true;
+    int g = kb0;
+    while (g < kb1 && ok) {
+      const int tile = g / P.n_kb;
+      const int seg_end = min(kb1, (tile + 1) * P.n_kb);
+      const bool whole = (g == tile * P.n_kb) && (seg_end == (tile + 1) * P.n_kb);
+      const int buf = seg & 1;
+      if (!mbar_wait(&S.acc_full[buf], (seg >> 1) & 1, abort_flag)) {
+        if (lane == 0) { atomicCAS(P.status, 0, 104); S.abort_flag = 1; }
+      }
+      // the four epilogue warps go on, or give up, together: the barriers below have no limit of their own
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (S.abort_flag) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+      const int n = tile * TC_BM + row;
+      float* part = P.scratch + ((size_t)(c * 2 + (tile == first_tile ? 0 : 1)) * BN) * TC_BM;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += CW) {
+        uint32_t r[CW];
+        if constexpr (CW == 32) tmem_ld32(taddr + c0, r); else tmem_ld16(taddr + c0, r);
+        tmem_ld_wait();
+        if (whole) {
+          float v[CW];
+#pragma unroll
+          for (int j = 0; j < CW; j++) v[j] = __uint_as_float(r[j]);
+          sk_store<EPI, CW>(P, n, c0, v);
+        } else {
+#pragma unroll
+          for (int j = 0; j < CW; j++) part[(size_t)(c0 + j) * TC_BM + row] = __uint_as_float(r[j]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&S.acc_empty[buf]);
+      if (!whole) {
+        // every epilogue thread's partial sums are written; count this CTA in; the last one to arrive finishes
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          const int first_c = sk_owner(tile * P.n_kb, G, P.total_kb);
+          const int last_c = sk_owner((tile + 1) * P.n_kb - 1, G, P.total_kb);
+          const unsigned old = atomicAdd(&P.counters[tile], 1u);
+          const int is_last = (old == (unsigned)(last_c - first_c));
+          if (is_last) P.counters[tile] = 0;       // everyone has arrived: ready for the next launch
+          S.last_flag = is_last;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (S.last_flag) {
+          __threadfence();
+          const int first_c = sk_owner(tile * P.n_kb, G, P.total_kb);
+          const int last_c = sk_owner((tile + 1) * P.n_kb - 1, G, P.total_kb);
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += CW) {
+            float v[CW];
+#pragma unroll
+            for (int j = 0; j < CW; j++) v[j] = 0.f;
+            for (int cc = first_c; cc <= last_c; cc++) {       // in the order of k
+              const int slot = (tile == sk_begin(cc, G, P.total_kb) / P.n_kb) ? 0 : 1;
+              const float* src = P.scratch + ((size_t)(cc * 2 + slot) * BN) * TC_BM;
+#pragma unroll
+              for (int j = 0; j < CW; j++) v[j] += ld_fresh(src + (size_t)(c0 + j) * TC_BM + row);
+            }
+            sk_store<EPI, CW>(P, n, c0, v);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");    // last_flag is reused by the next shared tile
+      }
+      g = seg_end;
+      seg++;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 // ---------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -442,12 +687,45 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
   return launch_status();
 }
 
+template <int BN, int STAGES>
+static int launch_streamk(const CUtensorMap& mw, const CUtensorMap& mx, const SkParams& P, int epilogue,
+                          cudaStream_t stream) {
+  const size_t smem = sizeof(SkSmem<BN, STAGES>) + 1024;
+  const int grid = P.total_kb < sm_count() ? P.total_kb : sm_count();
+#define SK_LAUNCH(E)                                                                                        \
+  {                                                                                                         \
+    auto kern = gemm_tc_streamk_kernel<BN, STAGES, E>;                                                      \
+    static bool configured = false;                                                                         \
+    if (!configured) {                                                                                      \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+      if (e != cudaSuccess) return (int)e;                                                                  \
+      configured = true;                                                                                    \
+    }                                                                                                       \
+    return launch_pdl(kern, grid, TC_THREADS, smem, stream, mw, mx, P);                                     \
+  }
+  switch (epilogue) {
+    case 0: SK_LAUNCH(0)
+    case 1: SK_LAUNCH(1)
+    case 2: SK_LAUNCH(2)
+    case 3: SK_LAUNCH(3)
+    default: return STRATUM_ERR_SHAPE;
+  }
+#undef SK_LAUNCH
+}
+
+// Scratch the stream-K form needs: floats for partial tiles, and one counter per tile of 128 weight rows.
+STRATUM_EXPORT long long stratum_gemm_tc_scratch_floats(void) { return (long long)sm_count() * 2 * 64 * TC_BM; }
+STRATUM_EXPORT long long stratum_gemm_tc_counters(int N) { return (long long)(N + TC_BM - 1) / TC_BM; }
+
 // x: bf16 [M][ldx], w: bf16 [N][K], bias float32 [N] or null, out [M][ldo] (SwiGLU: [M][N/2]).
+// scratch / counters: used when M <= 64 (see stratum_gemm_tc_scratch_floats / _counters; the counters must be
+// zero before the first launch, and every launch leaves them zero).
 // status: one int in device memory, 0 before the call; non-zero afterwards means a wait inside the kernel ran out.
 // Needs K % 8 == 0, ldx % 8 == 0, 16-byte aligned x and w (a TMA copy starts on a 16-byte boundary and its
 // row pitch is a multiple of 16 bytes; the k coordinate of every copy here is a multiple of 64).
 STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bias, void* out, int epilogue, int M,
-                                   int N, int K, int ldx, int ldo, int* status, cudaStream_t stream) {
+                                   int N, int K, int ldx, int ldo, int* status, float* scratch, unsigned* counters,
+                                   cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldx < K) return STRATUM_ERR_SHAPE;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return STRATUM_ERR_ALIGN;
@@ -467,12 +745,18 @@ STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bi
     if (wide) return launch_tc<256, 4, false>(ma, mb, P, epilogue, tiles_m * ((N + 255) / 256), stream);
     return launch_tc<128, 6, false>(ma, mb, P, epilogue, tiles_m * ((N + 127) / 128), stream);
   }
-  // few rows of x: 128 rows of W by all rows of x per tile
+  // few rows of x: tiles of 128 rows of W by all rows of x, k-blocks spread evenly over the SMs
+  if (!scratch || !counters) return STRATUM_ERR_SHAPE;
   const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   if ((st = make_map(&ma, w, N, K, K, TC_BM)) != 0) return st;
   if ((st = make_map(&mb, x, M, K, ldx, bn)) != 0) return st;
-  const int tiles = (N + TC_BM - 1) / TC_BM;
-  if (bn == 16) return launch_tc<16, 8, true>(ma, mb, P, epilogue, tiles, stream);
-  if (bn == 32) return launch_tc<32, 8, true>(ma, mb, P, epilogue, tiles, stream);
-  return launch_tc<64, 8, true>(ma, mb, P, epilogue, tiles, stream);
+  SkParams Q;
+  Q.bias = bias; Q.out = out; Q.status = status; Q.scratch = scratch; Q.counters = counters;
+  Q.M = M; Q.N = N; Q.K = K; Q.ldo = ldo;
+  Q.tiles = (N + TC_BM - 1) / TC_BM;
+  Q.n_kb = (K + TC_BK - 1) / TC_BK;
+  Q.total_kb = Q.tiles * Q.n_kb;
+  if (bn == 16) return launch_streamk<16, 10>(ma, mb, Q, epilogue, stream);
+  if (bn == 32) return launch_streamk<32, 9>(ma, mb, Q, epilogue, stream);
+  return launch_streamk<64, 8>(ma, mb, Q, epilogue, stream);
 }

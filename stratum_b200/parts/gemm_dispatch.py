@@ -14,7 +14,14 @@ import torch
 from .. import kernels as K
 
 STORE, ADD_TO_F32, STORE_F32, SWIGLU = K.EPI_STORE, K.EPI_ADD_F32, K.EPI_STORE_F32, K.EPI_SWIGLU
-SKINNY_MAX_ROWS = 32
+import os
+
+# rows of x up to which the weight-streaming mma.sync kernel is used; above it (and up to 64 rows) the
+# stream-K tcgen05 kernel takes over.  STRATUM_SKINNY_MAX_ROWS overrides it for measurements.
+SKINNY_MAX_ROWS = int(os.environ.get("STRATUM_SKINNY_MAX_ROWS", 32))
+# weight matrices of at least this many elements go to the stream-K kernel even for few rows of x: its TMA
+# ring keeps more bytes in flight, which pays once the matrix is large enough to amortise its set-up
+STREAMK_MIN_WEIGHTS = int(os.environ.get("STRATUM_STREAMK_MIN_WEIGHTS", 400_000_000))
 
 
 def _aligned(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -25,7 +32,7 @@ def _aligned(x: torch.Tensor, w: torch.Tensor) -> bool:
 def run(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int) -> None:
     """out (=|+=) epilogue(x @ w.T + bias); see the EPI_* modes in kernels.py."""
     if x.dtype == torch.bfloat16 and _aligned(x, w):
-        if x.shape[0] <= SKINNY_MAX_ROWS:
+        if x.shape[0] <= SKINNY_MAX_ROWS and w.numel() < STREAMK_MIN_WEIGHTS:
             K.gemm_skinny(x, w, bias, out, mode)
         else:
             K.gemm_tc(x, w, bias, out, mode)

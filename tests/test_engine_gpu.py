@@ -82,3 +82,53 @@ def test_unequal_batches_slots_reused(setup):
                     live.remove(i)
         engine.cache.check()
     assert engine.cache.tokens_held() == 0
+
+
+def test_long_decoding_crosses_pages_and_buckets(setup):
+    """A short prompt, then some hundreds of tokens one by one: positions cross several pages."""
+    from stratum_b200.engine import StepEntry
+    name, dtype, cfg, w, engine = setup
+    rng = np.random.default_rng(4)
+    n = 330 if name != "C" else 200
+    toks = rand_tokens(rng, n, cfg["vocab_size"])
+    ref = plain_logits(cfg, w, toks)
+    slot = engine.acquire()
+    got = [engine.step([StepEntry(slot, toks[:3], [2])]).cpu().numpy()]
+    check = set(range(3, n, 37)) | {63, 64, 65, 127, 128, 129, n - 1}
+    for i in range(3, n):
+        out = engine.step([StepEntry(slot, [toks[i]], [0] if i in check else [])])
+        if i in check:
+            got.append(out.cpu().numpy())
+    engine.release(slot)
+    assert_close(np.concatenate(got), ref[[2] + sorted(check)], dtype, f"{name} long decode")
+
+
+def test_first_tokens_of_a_sequence(setup):
+    """Position 0 alone, then 1, 2, 3: the first tokens see the least context and have no page behind them."""
+    from stratum_b200.engine import StepEntry
+    name, dtype, cfg, w, engine = setup
+    rng = np.random.default_rng(6)
+    toks = rand_tokens(rng, 4, cfg["vocab_size"])
+    ref = plain_logits(cfg, w, toks)
+    slot = engine.acquire()
+    got = np.concatenate([engine.step([StepEntry(slot, [t], [0])]).cpu().numpy() for t in toks])
+    engine.release(slot)
+    assert_close(got, ref, dtype, f"{name} first tokens")
+
+
+def test_errors_leave_the_engine_unchanged(setup):
+    from stratum_b200.cache import CacheFull
+    from stratum_b200.engine import StepEntry, StepError
+    name, dtype, cfg, w, engine = setup
+    slot = engine.acquire()
+    with pytest.raises(StepError, match="outside the vocabulary"):
+        engine.step([StepEntry(slot, [cfg["vocab_size"]], [0])])
+    with pytest.raises(StepError, match="wanted place"):
+        engine.step([StepEntry(slot, [1, 2], [2])])
+    with pytest.raises(StepError, match="not held"):
+        engine.step([StepEntry(slot + 7, [1], [0])])
+    with pytest.raises(CacheFull):
+        engine.step([StepEntry(slot, [1] * (64 * 33), [])])      # beyond the 2048 tokens this engine holds
+    assert engine.length(slot) == 0
+    engine.release(slot)
+    engine.cache.check()
