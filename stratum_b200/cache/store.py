@@ -63,7 +63,7 @@ class _Group:
 class SequenceCache:
     """Slots, pages and storage for one model.
 
-    layer_specs: for each layer that owns a cache, its spec (None for layers without).
+    layer_specs: for each stop of the schedule that owns a cache, its spec (None for stops without).
     max_tokens: tokens that live sequences may hold together, each sequence's count rounded
                 up to a multiple of PAGE_TOKENS.
     max_seqs:   sequences that may be live at once.

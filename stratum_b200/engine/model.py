@@ -75,10 +75,19 @@ class Model:
         return out
 
     def cache_specs(self) -> List[Optional[CacheSpec]]:
-        """Per layer: what its mixer keeps per sequence (None if nothing, or if no stop owns its cache)."""
-        owners = {e.layer for e in self.schedule if e.cache_of is None}
-        owners |= {e.cache_of for e in self.schedule if e.cache_of is not None}
-        return [layer.mixer.cache_spec() if i in owners else None for i, layer in enumerate(self.layers)]
+        """Per stop of the schedule: what its mixer keeps per sequence (None if nothing, or if the stop
+        reads another stop's cache)."""
+        specs: List[Optional[CacheSpec]] = []
+        for i, e in enumerate(self.schedule):
+            own = self.layers[e.layer].mixer.cache_spec()
+            if e.cache_of is not None:
+                theirs = self.layers[self.schedule[e.cache_of].layer].mixer.cache_spec()
+                if theirs != own:
+                    raise ValueError(f"model spec: stop {i} needs {own} but reads the cache of stop {e.cache_of}, "
+                                     f"which holds {theirs}")
+                own = None
+            specs.append(own)
+        return specs
 
     # ------------------------------------------------------------------ weights
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
@@ -92,9 +101,9 @@ class Model:
     def forward(self, step, cache) -> torch.Tensor:
         """Run the tokens of one step through every stop of the schedule; float32 logits at the wanted rows."""
         x = self.embedding.forward(step.token_ids)
-        for entry in self.schedule:
+        for stop, entry in enumerate(self.schedule):
             layer = self.layers[entry.layer]
-            owner = entry.layer if entry.cache_of is None else entry.cache_of
+            owner = stop if entry.cache_of is None else entry.cache_of
             view = cache.layer_view(owner, entry.cache_of is None, step.block_tables)
             layer.arrangement.forward(layer, x, step, view)
         if step.want_rows.numel() == 0:

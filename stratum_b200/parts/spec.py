@@ -44,9 +44,10 @@ class LayerSpec:
 class ScheduleEntry:
     """One stop of the forward pass.
 
-    `layer` indexes ModelSpec.layers (a layer may appear more than once).
-    `cache_of`: the layer whose cache this stop reads; None means its own.  A stop
-    that reads another layer's cache does not write keys or state of its own.
+    `layer` indexes ModelSpec.layers; a layer may appear at more than one stop (its weights are
+    shared, each stop keeps a cache of its own).
+    `cache_of`: the earlier stop (its position in the schedule) whose cache this stop reads; None
+    means its own.  A stop that reads another stop's cache writes no keys or state of its own.
     """
     layer: int
     cache_of: Optional[int] = None
@@ -66,11 +67,14 @@ class ModelSpec:
         n = len(self.layers)
         if not self.schedule:
             raise ValueError("model spec: empty schedule")
-        for e in self.schedule:
+        for i, e in enumerate(self.schedule):
             if not (0 <= e.layer < n):
                 raise ValueError(f"model spec: schedule names layer {e.layer}, model has {n}")
-            if e.cache_of is not None and not (0 <= e.cache_of < n):
-                raise ValueError(f"model spec: schedule reads the cache of layer {e.cache_of}, model has {n}")
+            if e.cache_of is not None:
+                if not (0 <= e.cache_of < i):
+                    raise ValueError(f"model spec: stop {i} reads the cache of stop {e.cache_of}, which is not earlier")
+                if self.schedule[e.cache_of].cache_of is not None:
+                    raise ValueError(f"model spec: stop {i} reads the cache of stop {e.cache_of}, which has none of its own")
 
 
 @dataclass(frozen=True)
