@@ -201,6 +201,8 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--decode-only", action="store_true",
                     help="time the decode steps only and print a short line (for profiler runs)")
+    ap.add_argument("--prefill-only", action="store_true",
+                    help="time the 2,048-token prompt only and print a short line (for profiler runs)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -226,11 +228,16 @@ def main() -> int:
     cfg = LlamaConfig.from_dict(raw)
     peaks = load_peaks()
     rng = np.random.default_rng(0)
-    biggest = max(args.batch, 1 if (args.no_points or args.decode_only) else 64)
+    biggest = max(args.batch, 1 if (args.no_points or args.decode_only or args.prefill_only) else 64)
     llm = Stratum.from_random(cfg, seed=0, dtype="bfloat16",
                               max_tokens=biggest * (args.context + 64), max_seqs=biggest)
     vocab = cfg.vocab
 
+    if args.prefill_only:
+        ms = time_prefill(llm, PREFILL_TOKENS, vocab, rng, repeats=2)
+        print(json.dumps({"prefill_only": True, "tokens": PREFILL_TOKENS, "layers": n_layers, "ms": round(ms, 3),
+                          "tflops": round(prefill_flops(cfg, n_layers, PREFILL_TOKENS) / ms / 1e9, 1)}))
+        return 0
     with ClockSampler() as clocks:
         ms_step, launches = time_decode(llm, args.batch, args.context, args.steps, args.warmup, vocab, rng)
     value = args.batch * 1000.0 / ms_step

@@ -70,6 +70,75 @@ struct AttnParams {
   float scale;
 };
 
+// One block of 16 keys for the 16 query rows of a warp: scores, mask, online softmax, value sum.
+// ka/kb: K rows key0+g / key0+8+g; va/vb: V rows likewise (8 contiguous dims per chunk, see the top comment).
+template <int CH>
+__device__ __forceinline__ void attend_block(const AttnParams& P, const uint4 (&qa)[CH], const uint4 (&qc)[CH],
+                                             const uint4 (&ka)[CH], const uint4 (&kb)[CH], const uint4 (&va)[CH],
+                                             const uint4 (&vb)[CH], float (&o)[4 * CH][4], float (&m_run)[2],
+                                             float (&l_run)[2], const bool (&row_ok)[2], const int (&row_pos)[2],
+                                             int key0, int k_end, int t) {
+  // scores: s[i] is the tile of keys key0 + 8i + {2t, 2t+1}; [0],[1] row g, [2],[3] row g+8
+  float s[2][4];
+#pragma unroll
+  for (int i = 0; i < 2; i++) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
+#pragma unroll
+  for (int c = 0; c < CH; c++) {
+    mma16816(s[0], qa[c].x, qc[c].x, qa[c].y, qc[c].y, ka[c].x, ka[c].y);
+    mma16816(s[0], qa[c].z, qc[c].z, qa[c].w, qc[c].w, ka[c].z, ka[c].w);
+    mma16816(s[1], qa[c].x, qc[c].x, qa[c].y, qc[c].y, kb[c].x, kb[c].y);
+    mma16816(s[1], qa[c].z, qc[c].z, qa[c].w, qc[c].w, kb[c].z, kb[c].w);
+  }
+  // mask, scale, running maximum
+  float bm[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int i = 0; i < 2; i++) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+      const int e = j >> 1;
+      const int key = key0 + 8 * i + 2 * t + (j & 1);
+      const int lo = (P.window > 0 && row_pos[e] - P.window + 1 > 0) ? row_pos[e] - P.window + 1 : 0;
+      const bool ok = row_ok[e] && key <= row_pos[e] && key >= lo && key < k_end;
+      s[i][j] = ok ? s[i][j] * P.scale : -INFINITY;
+      bm[e] = fmaxf(bm[e], s[i][j]);
+    }
+  }
+  float corr[2], m_use[2];
+#pragma unroll
+  for (int e = 0; e < 2; e++) {
+    bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 1));
+    bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 2));
+    const float m_new = fmaxf(m_run[e], bm[e]);
+    m_use[e] = (m_new == -INFINITY) ? 0.f : m_new;      // a row with no key yet: exponents of -inf give 0
+    corr[e] = __expf(m_run[e] - m_use[e]);              // first keys: exp(-inf) = 0
+    m_run[e] = m_new;
+  }
+  float p[2][4];
+#pragma unroll
+  for (int i = 0; i < 2; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) p[i][j] = __expf(s[i][j] - m_use[j >> 1]);
+#pragma unroll
+  for (int e = 0; e < 2; e++)
+    l_run[e] = l_run[e] * corr[e] + (p[0][2 * e] + p[0][2 * e + 1] + p[1][2 * e] + p[1][2 * e + 1]);
+#pragma unroll
+  for (int i = 0; i < 4 * CH; i++) {
+    o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
+  }
+  // the value sum uses probabilities rounded to bfloat16, as its tensor-core operand must be
+  const uint32_t pa0 = pack_bf16(p[0][0], p[0][1]), pa1 = pack_bf16(p[0][2], p[0][3]);
+  const uint32_t pa2 = pack_bf16(p[1][0], p[1][1]), pa3 = pack_bf16(p[1][2], p[1][3]);
+#pragma unroll
+  for (int c = 0; c < CH; c++) {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const uint32_t b0 = transpose8x8(reg_of(va[c], i));
+      const uint32_t b1 = transpose8x8(reg_of(vb[c], i));
+      mma16816(o[4 * c + i], pa0, pa1, pa2, pa3, b0, b1);
+    }
+  }
+}
+
 template <int CH>
 __global__ void __launch_bounds__(AM_WARPS * 32)
 attention_mma_kernel(const AttnParams P) {
@@ -168,65 +237,7 @@ attention_mma_kernel(const AttnParams P) {
       nka[c] = (more && d < Hd) ? ldg16(P.k_cache + base + (size_t)g * Hd + d) : zero4;
       nkb[c] = (more && d < Hd) ? ldg16(P.k_cache + base + (size_t)(g + 8) * Hd + d) : zero4;
     }
-    // scores: s[i] is the tile of keys key0 + 8i + {2t, 2t+1}; [0],[1] row g, [2],[3] row g+8
-    float s[2][4];
-#pragma unroll
-    for (int i = 0; i < 2; i++) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f; }
-#pragma unroll
-    for (int c = 0; c < CH; c++) {
-      mma16816(s[0], qa[c].x, qc[c].x, qa[c].y, qc[c].y, ka[c].x, ka[c].y);
-      mma16816(s[0], qa[c].z, qc[c].z, qa[c].w, qc[c].w, ka[c].z, ka[c].w);
-      mma16816(s[1], qa[c].x, qc[c].x, qa[c].y, qc[c].y, kb[c].x, kb[c].y);
-      mma16816(s[1], qa[c].z, qc[c].z, qa[c].w, qc[c].w, kb[c].z, kb[c].w);
-    }
-    // mask, scale, running maximum
-    float bm[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int i = 0; i < 2; i++) {
-#pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const int e = j >> 1;
-        const int key = key0 + 8 * i + 2 * t + (j & 1);
-        const int lo = (P.window > 0 && row_pos[e] - P.window + 1 > 0) ? row_pos[e] - P.window + 1 : 0;
-        const bool ok = row_ok[e] && key <= row_pos[e] && key >= lo && key < k_end;
-        s[i][j] = ok ? s[i][j] * P.scale : -INFINITY;
-        bm[e] = fmaxf(bm[e], s[i][j]);
-      }
-    }
-    float corr[2], m_use[2];
-#pragma unroll
-    for (int e = 0; e < 2; e++) {
-      bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 1));
-      bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 2));
-      const float m_new = fmaxf(m_run[e], bm[e]);
-      m_use[e] = (m_new == -INFINITY) ? 0.f : m_new;      // a row with no key yet: exponents of -inf give 0
-      corr[e] = __expf(m_run[e] - m_use[e]);              // first keys: exp(-inf) = 0
-      m_run[e] = m_new;
-    }
-    float p[2][4];
-#pragma unroll
-    for (int i = 0; i < 2; i++)
-#pragma unroll
-      for (int j = 0; j < 4; j++) p[i][j] = __expf(s[i][j] - m_use[j >> 1]);
-#pragma unroll
-    for (int e = 0; e < 2; e++)
-      l_run[e] = l_run[e] * corr[e] + (p[0][2 * e] + p[0][2 * e + 1] + p[1][2 * e] + p[1][2 * e + 1]);
-#pragma unroll
-    for (int i = 0; i < 4 * CH; i++) {
-      o[i][0] *= corr[0]; o[i][1] *= corr[0]; o[i][2] *= corr[1]; o[i][3] *= corr[1];
-    }
-    // the value sum uses probabilities rounded to bfloat16, as its tensor-core operand must be
-    const uint32_t pa0 = pack_bf16(p[0][0], p[0][1]), pa1 = pack_bf16(p[0][2], p[0][3]);
-    const uint32_t pa2 = pack_bf16(p[1][0], p[1][1]), pa3 = pack_bf16(p[1][2], p[1][3]);
-#pragma unroll
-    for (int c = 0; c < CH; c++) {
-#pragma unroll
-      for (int i = 0; i < 4; i++) {
-        const uint32_t b0 = transpose8x8(reg_of(va[c], i));
-        const uint32_t b1 = transpose8x8(reg_of(vb[c], i));
-        mma16816(o[4 * c + i], pa0, pa1, pa2, pa3, b0, b1);
-      }
-    }
+    attend_block<CH>(P, qa, qc, ka, kb, va, vb, o, m_run, l_run, row_ok, row_pos, key0, k_end, t);
 #pragma unroll
     for (int c = 0; c < CH; c++) { ka[c] = nka[c]; kb[c] = nkb[c]; }
   }
@@ -270,6 +281,205 @@ attention_mma_kernel(const AttnParams P) {
         P.part_ml[slot * 2 + 1] = l_run[e];
       }
     }
+  }
+}
+
+// ---------------------------------------------------------------- prompts: key tiles shared through shared memory
+// Four warps share one kv head and 4 x 16 query rows (consecutive new tokens of one sequence x the heads of the
+// group).  The keys and values they all need are brought in once per tile of 64 keys (one page, 64 x Hd x 2
+// bytes each for K and V) with cp.async, two tiles in flight, and every warp reads its fragments from there with
+// the same 16-byte pieces as the direct kernel above.  Pieces are stored with bit 2 of their index flipped on odd
+// rows, so that the eight lanes of a quarter-warp (two rows, four pieces each) fall on different banks.
+#define AT_WARPS 4
+#define AT_KEYS 64
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
+               "l"(gmem_src) : "memory");
+}
+
+template <int CH>
+__global__ void __launch_bounds__(AT_WARPS * 32)
+attention_tile_kernel(const AttnParams P) {
+  extern __shared__ uint4 tile_smem[];           // [2 buffers][K | V][64 rows][Hd / 8 pieces]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  pdl_trigger();
+  const int qb = blockIdx.x;
+  const int kvh = blockIdx.y / P.head_groups, hg = blockIdx.y % P.head_groups;
+  const int seq = P.qb_seq[qb];
+  if (seq < 0) return;
+  const int tok0 = P.qb_tok0[qb], ntok = P.qb_ntok[qb];
+  const int gs = P.n_q / P.n_kv;
+  const int Hd = P.head_dim;
+  const int pieces = Hd / 8;                      // 16-byte pieces per row
+  const bool swizzle = (pieces % 8) == 0;
+
+  // this warp's share of the tile's tokens
+  const int wtok0 = tok0 + warp * P.tokens_per_block;
+  const int wntok = max(0, min(P.tokens_per_block, ntok - warp * P.tokens_per_block));
+  int row_tok[2], row_head[2], row_pos[2];
+  bool row_ok[2];
+#pragma unroll
+  for (int e = 0; e < 2; e++) {
+    const int r = g + 8 * e;
+    const int tr = r / P.rows_per_token, hr = r % P.rows_per_token;
+    const int hq = hg * 16 + hr;
+    row_ok[e] = tr < wntok && hq < gs;
+    row_tok[e] = row_ok[e] ? wtok0 + tr : tok0;
+    row_head[e] = kvh * gs + (row_ok[e] ? hq : 0);
+    row_pos[e] = P.token_pos[row_tok[e]];
+  }
+  const int first_pos = P.token_pos[tok0];
+  const int last_pos = first_pos + ntok - 1;
+  const int warp_last = first_pos + warp * P.tokens_per_block + wntok - 1;     // last position this warp attends from
+  const int lo_block = (P.window > 0 && first_pos - P.window + 1 > 0) ? first_pos - P.window + 1 : 0;
+  const int tile_begin = lo_block / AT_KEYS, tile_end = last_pos / AT_KEYS;    // inclusive
+  const int k_end = last_pos + 1;
+  const int* bt = P.block_table + (size_t)seq * P.bt_stride;
+  const size_t page_stride = (size_t)P.n_kv * P.page_tokens * Hd;
+  const size_t head_off = (size_t)kvh * P.page_tokens * Hd;
+  const int tile_pieces = AT_KEYS * pieces;       // per matrix
+  pdl_wait();                                      // q and the newest keys come from the kernel before this one
+
+  auto request_tile = [&](int tile, int buf) {
+    const size_t base = (size_t)bt[tile] * page_stride + head_off;    // a page holds exactly one tile per head
+    const uint4* ksrc = reinterpret_cast<const uint4*>(P.k_cache + base);
+    const uint4* vsrc = reinterpret_cast<const uint4*>(P.v_cache + base);
+    uint4* kdst = tile_smem + (size_t)buf * 2 * tile_pieces;
+    uint4* vdst = kdst + tile_pieces;
+    for (int i = threadIdx.x; i < tile_pieces; i += AT_WARPS * 32) {
+      const int row = i / pieces, pc = i % pieces;
+      const int at = row * pieces + (swizzle ? (pc ^ ((row & 1) << 2)) : pc);
+      cp_async16(kdst + at, ksrc + i);
+      cp_async16(vdst + at, vsrc + i);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  request_tile(tile_begin, 0);
+
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+  uint4 qa[CH], qc[CH];
+#pragma unroll
+  for (int c = 0; c < CH; c++) {
+    const int d = 32 * c + 8 * t;
+    const bool d_ok = d < Hd;
+    qa[c] = (row_ok[0] && d_ok) ? ldg16(P.q + (size_t)row_tok[0] * P.ldq + (size_t)row_head[0] * Hd + d) : zero4;
+    qc[c] = (row_ok[1] && d_ok) ? ldg16(P.q + (size_t)row_tok[1] * P.ldq + (size_t)row_head[1] * Hd + d) : zero4;
+  }
+  float o[4 * CH][4];
+#pragma unroll
+  for (int i = 0; i < 4 * CH; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+  for (int tile = tile_begin; tile <= tile_end; tile++) {
+    const int buf = (tile - tile_begin) & 1;
+    if (tile < tile_end) {
+      request_tile(tile + 1, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();                               // every thread's pieces of this tile have landed
+    const uint4* ks = tile_smem + (size_t)buf * 2 * tile_pieces;
+    const uint4* vs = ks + tile_pieces;
+    if (wntok > 0) {
+#pragma unroll 1
+      for (int sub = 0; sub < AT_KEYS / 16; sub++) {
+        const int key0 = tile * AT_KEYS + sub * 16;
+        if (key0 > warp_last) break;               // causal: nothing of this warp sees these keys
+        if (key0 + 15 < lo_block) continue;
+        uint4 ka[CH], kb[CH], va[CH], vb[CH];
+        const int r0 = sub * 16 + g, r1 = r0 + 8;
+#pragma unroll
+        for (int c = 0; c < CH; c++) {
+          const int pc = 4 * c + t;
+          if (pc < pieces) {
+            const int a0 = r0 * pieces + (swizzle ? (pc ^ ((r0 & 1) << 2)) : pc);
+            const int a1 = r1 * pieces + (swizzle ? (pc ^ ((r1 & 1) << 2)) : pc);
+            ka[c] = ks[a0]; kb[c] = ks[a1]; va[c] = vs[a0]; vb[c] = vs[a1];
+          } else {
+            ka[c] = kb[c] = va[c] = vb[c] = zero4;
+          }
+        }
+        attend_block<CH>(P, qa, qc, ka, kb, va, vb, o, m_run, l_run, row_ok, row_pos, key0, k_end, t);
+      }
+    }
+    __syncthreads();                               // the buffer is refilled two tiles from now
+  }
+#pragma unroll
+  for (int e = 0; e < 2; e++) {
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 1);
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 2);
+  }
+#pragma unroll
+  for (int e = 0; e < 2; e++) {
+    if (!row_ok[e]) continue;
+    const float inv = 1.0f / l_run[e];
+    bf16* op = P.out + (size_t)row_tok[e] * P.ldo + (size_t)row_head[e] * Hd;
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+      const int d = 32 * c + 8 * t;
+      if (d >= Hd) continue;
+      uint4 v;
+      v.x = pack_bf16(o[4 * c + 0][2 * e] * inv, o[4 * c + 0][2 * e + 1] * inv);
+      v.y = pack_bf16(o[4 * c + 1][2 * e] * inv, o[4 * c + 1][2 * e + 1] * inv);
+      v.z = pack_bf16(o[4 * c + 2][2 * e] * inv, o[4 * c + 2][2 * e + 1] * inv);
+      v.w = pack_bf16(o[4 * c + 3][2 * e] * inv, o[4 * c + 3][2 * e + 1] * inv);
+      *reinterpret_cast<uint4*>(op + d) = v;
+    }
+  }
+}
+
+template <int CH>
+static int launch_attention_tile(const AttnParams& P, cudaStream_t stream) {
+  const size_t smem = (size_t)2 * 2 * AT_KEYS * P.head_dim * sizeof(bf16);
+  auto kern = attention_tile_kernel<CH>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 2 * AT_KEYS * 128 * 2);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const dim3 grid(P.n_qblocks, P.n_kv * P.head_groups);
+  return launch_pdl(kern, grid, AT_WARPS * 32, smem, stream, P);
+}
+
+// Prompts and continuations: query tiles of 4 x tokens_per_block tokens (qb_* lists are required).
+// Needs page_tokens == 64.
+STRATUM_EXPORT int stratum_attention_tile(const void* q, int ldq, const void* k_cache, const void* v_cache,
+                                          const int* token_pos, const int* token_seq, const int* block_table,
+                                          int bt_stride, const int* qb_seq, const int* qb_tok0, const int* qb_ntok,
+                                          int n_qblocks, int tokens_per_block, void* out, int ldo, int n_tokens,
+                                          int n_q, int n_kv, int head_dim, int page_tokens, int window, float scale,
+                                          cudaStream_t stream) {
+  if (n_tokens <= 0 || n_qblocks <= 0) return 0;
+  if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 128) return STRATUM_ERR_SHAPE;
+  if (n_kv < 1 || n_q % n_kv != 0 || page_tokens != AT_KEYS) return STRATUM_ERR_SHAPE;
+  if (!qb_seq || !qb_tok0 || !qb_ntok) return STRATUM_ERR_SHAPE;
+  if (ldq % 8 != 0 || ldo % 8 != 0) return STRATUM_ERR_ALIGN;
+  if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return STRATUM_ERR_ALIGN;
+  const int gs = n_q / n_kv;
+  AttnParams P;
+  P.q = (const bf16*)q; P.ldq = ldq;
+  P.k_cache = (const bf16*)k_cache; P.v_cache = (const bf16*)v_cache;
+  P.token_pos = token_pos; P.token_seq = token_seq; P.block_table = block_table; P.bt_stride = bt_stride;
+  P.qb_seq = qb_seq; P.qb_tok0 = qb_tok0; P.qb_ntok = qb_ntok; P.n_qblocks = n_qblocks;
+  P.out = (bf16*)out; P.ldo = ldo; P.part_o = nullptr; P.part_ml = nullptr;
+  P.n_q = n_q; P.n_kv = n_kv; P.head_dim = head_dim; P.page_tokens = page_tokens; P.window = window;
+  P.rows_per_token = gs < 16 ? gs : 16;
+  P.head_groups = (gs + 15) / 16;
+  P.tokens_per_block = tokens_per_block;
+  if (tokens_per_block < 1 || tokens_per_block * P.rows_per_token > 16) return STRATUM_ERR_SHAPE;
+  if ((long long)n_kv * P.head_groups > 65535) return STRATUM_ERR_LIMIT;
+  P.n_splits = 1; P.chunk = 0x40000000;
+  P.scale = scale;
+  switch ((head_dim + 31) / 32) {
+    case 1: return launch_attention_tile<1>(P, stream);
+    case 2: return launch_attention_tile<2>(P, stream);
+    case 3: return launch_attention_tile<3>(P, stream);
+    case 4: return launch_attention_tile<4>(P, stream);
+    default: return STRATUM_ERR_SHAPE;
   }
 }
 

@@ -170,9 +170,11 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ t
                                   int bt_stride, const float* __restrict__ inv_freq, int n_pairs,
                                   int interleaved, float mscale, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                   int n_q, int n_kv, int head_dim, int page_tokens, int write_cache) {
-  // one block per (token, head): q heads, then k heads, then v heads; one thread per pair of dimensions
+  // a block covers one token and blockDim.y heads (q heads, then k heads, then v heads); one thread per pair
+  // of dimensions.  Decode steps use one head per block (many small blocks, shortest latency), prompts several.
   pdl_trigger();
-  const int t = blockIdx.x, h = blockIdx.y;
+  const int t = blockIdx.x, h = blockIdx.y * blockDim.y + threadIdx.y;
+  if (h >= n_q + 2 * n_kv) return;
   const int seq = token_seq[t];
   if (seq < 0) return;
   const int slot = threadIdx.x;                 // pair slot: < n_pairs rotates, the rest pass through
@@ -223,8 +225,13 @@ STRATUM_EXPORT int stratum_rope_store(void* qkv, int dtype, const int* token_pos
   if (n_tokens <= 0) return 0;
   if (head_dim % 2 != 0 || 2 * n_pairs > head_dim || n_pairs < 0 || head_dim > 2048) return STRATUM_ERR_SHAPE;
   if (n_q + 2 * n_kv > 65535) return STRATUM_ERR_LIMIT;
-  const int threads = ((head_dim / 2 + 31) / 32) * 32;
-  const dim3 grid(n_tokens, n_q + 2 * n_kv);
+  const int slots = ((head_dim / 2 + 31) / 32) * 32;
+  const int heads = n_q + 2 * n_kv;
+  int per_block = n_tokens >= 64 ? 256 / slots : 1;
+  if (per_block < 1) per_block = 1;
+  if (per_block > heads) per_block = heads;
+  const dim3 threads(slots, per_block);
+  const dim3 grid(n_tokens, (heads + per_block - 1) / per_block);
   if (dtype == STRATUM_DT_F32)
     return launch_pdl(rope_store_kernel<float>, grid, threads, 0, stream, (float*)qkv, token_pos, token_seq,
                       block_table, bt_stride, inv_freq, n_pairs, interleaved, mscale, (float*)k_cache,

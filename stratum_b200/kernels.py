@@ -309,6 +309,25 @@ def attention_mma(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         count_launches(1)          # the merge kernel
 
 
+def attention_tile(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, token_pos: torch.Tensor,
+                   token_seq: torch.Tensor, block_table: torch.Tensor, qblocks, tokens_per_warp: int,
+                   out: torch.Tensor, n_q: int, n_kv: int, head_dim: int, page_tokens: int, window: int,
+                   scale: float) -> None:
+    """bfloat16 tensor-core attention for prompts: query tiles of 4 * tokens_per_warp tokens share their key
+    tiles through shared memory.  qblocks: (seq, first row, tokens) int32 tensors, tokens <= 4 * tokens_per_warp."""
+    _need(qkv, "qkv", torch.bfloat16); _need(k_cache, "k_cache", torch.bfloat16)
+    _need(v_cache, "v_cache", torch.bfloat16); _need(out, "out", torch.bfloat16)
+    _need(block_table, "block_table", torch.int32)
+    qs, qt, qn = qblocks
+    f = _fn("attention_mma", "stratum_attention_tile",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+             c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(_ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(token_pos), _ptr(token_seq),
+             _ptr(block_table), block_table.stride(0), _ptr(qs), _ptr(qt), _ptr(qn), qs.numel(), tokens_per_warp,
+             _ptr(out), out.stride(0), qkv.shape[0], n_q, n_kv, head_dim, page_tokens, window, c_float(scale),
+             _stream()), "attention_tile")
+
+
 # ------------------------------------------------------------------ sampling
 ARGMAX_SPLITS = 32
 _argmax_scratch = None

@@ -42,7 +42,7 @@ def run(att, qkv: torch.Tensor, cache, step, out: torch.Tensor) -> None:
                         part_o, part_ml, att.n_heads, att.n_kv_heads, hd, PAGE_TOKENS, att.window, att.scale,
                         n_splits, chunk)
     else:
-        per_block = 16 // rows_per_token
-        K.attention_mma(qkv, cache.k, cache.v, step.token_pos, step.token_seq, cache.block_table,
-                        step.query_blocks(per_block), per_block, out, None, None, att.n_heads, att.n_kv_heads, hd,
-                        PAGE_TOKENS, att.window, att.scale, 1, 0)
+        per_warp = 16 // rows_per_token
+        K.attention_tile(qkv, cache.k, cache.v, step.token_pos, step.token_seq, cache.block_table,
+                         step.query_blocks(4 * per_warp), per_warp, out, att.n_heads, att.n_kv_heads, hd,
+                         PAGE_TOKENS, att.window, att.scale)
