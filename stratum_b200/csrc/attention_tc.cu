@@ -1,0 +1,358 @@
+// Causal grouped-query attention for prompts on the 5th-generation tensor cores (TMA + tcgen05 + TMEM).
+//
+// For query head h at position p:  score_t = (q_h . K_t[kv(h)]) * scale over keys t in [lo, p];
+// p_t = softmax;  o_h = sum_t p_t V_t[kv(h)]  (stratum/native/stratum_arch_llama.inc.c:435-514).
+//
+// One CTA owns 128 query rows that share a kv head: 128/gs consecutive new tokens of one sequence times the
+// gs heads of the group (row = token * gs + head).  It walks over the sequence's keys in tiles of 64, which is
+// exactly one page of the cache, so a K or V tile is one contiguous [64][Hd] block fetched by TMA.
+//
+//   warp 0      producer: Q once (3-D box: dims x heads of the group x tokens), then K and V tiles into a ring
+//   warp 1      one lane issues the MMAs:  S = Q K^T  (128 x 64, into one of two TMEM buffers) and, once the
+//               softmax warps have written P,  PV = P V  (128 x Hd, fresh every tile)
+//   warps 2-9   softmax, two threads per row (each owns half of the keys of a tile and half of the output
+//               dimensions): read S from TMEM, mask, running maximum in float32, exponentials, write P as
+//               bfloat16 into shared memory in the swizzled layout the MMA reads, then add PV into the output row
+//               kept in registers, rescaled when the maximum moves.  Nothing is rescaled inside TMEM.
+//
+// V is used as stored, [key][dim]: as the B operand of P V its n index (dim) is the contiguous one
+// ("MN-major"), which the instruction takes directly; no transpose is made anywhere.
+//
+// Every mbarrier wait is bounded (see gemm_tc.cu): on expiry a code goes to the status word and the CTA winds
+// down, freeing its tensor memory.
+#include <math.h>
+
+#include "tc_common.cuh"
+
+#define FA_ROWS 128
+#define FA_KEYS 64
+#define FA_STAGES 2
+#define FA_SOFTMAX_WARPS 8
+#define FA_THREADS (64 + FA_SOFTMAX_WARPS * 32)
+
+struct FaParams {
+  const int* token_pos;
+  const int* block_table; int bt_stride;
+  const int* qb_seq; const int* qb_tok0; const int* qb_ntok;
+  bf16* out; int ldo;
+  int* status;
+  int n_q, n_kv, gs, tokens_per_tile, window;
+  float scale_log2;        // scale * log2(e): exponentials are taken with exp2
+};
+
+template <int HD>
+struct FaSmem {
+  alignas(1024) bf16 q[FA_ROWS * HD];                 // [HD/64 blocks of 64 dims][128 rows][64]
+  alignas(1024) bf16 k[FA_STAGES][FA_KEYS * HD];      // [HD/64][64 keys][64 dims]
+  alignas(1024) bf16 v[FA_STAGES][FA_KEYS * HD];      // [HD/64][64 keys][64 dims]
+  alignas(1024) bf16 p[FA_ROWS * FA_KEYS];            // [128 rows][64 keys]
+  float l_half[FA_ROWS];                              // denominators of the second half of the keys
+  uint64_t q_full, k_full[FA_STAGES], v_full[FA_STAGES], kv_empty[FA_STAGES];
+  uint64_t s_full[2], s_empty[2], p_full, pv_full, pv_empty;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+#define FA_FAIL(code) { atomicCAS(P.status, 0, code); S.abort_flag = 1; }
+
+template <int HD>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, const FaParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  using Smem = FaSmem<HD>;
+  Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int DB = HD / 64;                           // blocks of 64 dims
+  constexpr uint32_t TMEM_COLS = 256;                   // S0 | S1 | PV (Hd columns)
+  constexpr uint32_t COL_PV = 128;
+  pdl_trigger();
+  // heaviest tiles first: the last query tiles of a long prompt see the most keys
+  const int qb = gridDim.x - 1 - blockIdx.x;
+  const int kvh = blockIdx.y;
+  const int seq = P.qb_seq[qb];
+  const int tok0 = P.qb_tok0[qb], ntok = P.qb_ntok[qb];
+  volatile int* abort_flag = &S.abort_flag;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&S.q_full, 1);
+    for (int s = 0; s < FA_STAGES; s++) { mbar_init(&S.k_full[s], 1); mbar_init(&S.v_full[s], 1); mbar_init(&S.kv_empty[s], 1); }
+    for (int b = 0; b < 2; b++) { mbar_init(&S.s_full[b], 1); mbar_init(&S.s_empty[b], FA_SOFTMAX_WARPS); }
+    mbar_init(&S.p_full, FA_SOFTMAX_WARPS);
+    mbar_init(&S.pv_full, 1);
+    mbar_init(&S.pv_empty, FA_SOFTMAX_WARPS);
+    S.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(&S.tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = S.tmem_base;
+
+  const int first_pos = P.token_pos[tok0];
+  const int last_pos = first_pos + ntok - 1;
+  const int lo_tile = (P.window > 0 && first_pos - P.window + 1 > 0) ? (first_pos - P.window + 1) / FA_KEYS : 0;
+  const int n_tiles = (seq < 0) ? 0 : last_pos / FA_KEYS - lo_tile + 1;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0 && n_tiles > 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+      pdl_wait();                                        // q and the newest keys come from the kernel before
+      mbar_expect_tx(&S.q_full, FA_ROWS * HD * sizeof(bf16));
+      for (int db = 0; db < DB; db++)
+        tma_load_3d(&map_q, S.q + db * FA_ROWS * 64, &S.q_full, db * 64, kvh * P.gs, tok0);
+      const int* bt = P.block_table + (size_t)seq * P.bt_stride;
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; j++) {
+        const int s = j % FA_STAGES;
+        if (!mbar_wait(&S.kv_empty[s], ((j / FA_STAGES) & 1) ^ 1, abort_flag)) { FA_FAIL(201); ok = false; break; }
+        const int row = (bt[lo_tile + j] * P.n_kv + kvh) * FA_KEYS;
+        mbar_expect_tx(&S.k_full[s], FA_KEYS * HD * sizeof(bf16));
+        for (int db = 0; db < DB; db++) tma_load_2d(&map_k, S.k[s] + db * FA_KEYS * 64, &S.k_full[s], db * 64, row);
+        mbar_expect_tx(&S.v_full[s], FA_KEYS * HD * sizeof(bf16));
+        for (int db = 0; db < DB; db++) tma_load_2d(&map_v, S.v[s] + db * FA_KEYS * 64, &S.v_full[s], db * 64, row);
+      }
+      if (!ok) {
+        for (int i = 0; i < 2000; i++) __nanosleep(1000);   // let copies already issued land
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0 && n_tiles > 0) {
+      const uint32_t idesc_s = instr_desc_bf16(FA_KEYS);
+      const uint32_t idesc_pv = instr_desc_bf16(HD, true);
+      bool ok = mbar_wait(&S.q_full, 0, abort_flag);
+      if (!ok) FA_FAIL(202);
+      auto issue_scores = [&](int j) -> bool {
+        const int s = j % FA_STAGES, b = j & 1;
+        if (!mbar_wait(&S.k_full[s], (j / FA_STAGES) & 1, abort_flag)) { FA_FAIL(203); return false; }
+        if (!mbar_wait(&S.s_empty[b], ((j >> 1) & 1) ^ 1, abort_flag)) { FA_FAIL(204); return false; }
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(S.q), k_addr = smem_u32(S.k[s]);
+#pragma unroll
+        for (int db = 0; db < DB; db++)
+#pragma unroll
+          for (int kk = 0; kk < 4; kk++)
+            umma_bf16(tmem_base + b * FA_KEYS, smem_desc_sw128(q_addr + db * FA_ROWS * 128 + kk * 32),
+                      smem_desc_sw128(k_addr + db * FA_KEYS * 128 + kk * 32), idesc_s, (db | kk) ? 1u : 0u);
+        umma_commit(&S.s_full[b]);
+        return true;
+      };
+      if (ok) ok = issue_scores(0);
+      for (int j = 0; j < n_tiles && ok; j++) {
+        if (j + 1 < n_tiles) { ok = issue_scores(j + 1); if (!ok) break; }
+        const int s = j % FA_STAGES;
+        if (!mbar_wait(&S.p_full, j & 1, abort_flag)) { FA_FAIL(205); ok = false; break; }
+        if (!mbar_wait(&S.v_full[s], (j / FA_STAGES) & 1, abort_flag)) { FA_FAIL(206); ok = false; break; }
+        if (!mbar_wait(&S.pv_empty, (j & 1) ^ 1, abort_flag)) { FA_FAIL(207); ok = false; break; }
+        tc_fence_after();
+        const uint32_t p_addr = smem_u32(S.p), v_addr = smem_u32(S.v[s]);
+#pragma unroll
+        for (int kk = 0; kk < 4; kk++)          // 16 keys a step: 32 bytes along a row of P, 16 rows of V
+          umma_bf16(tmem_base + COL_PV, smem_desc_sw128(p_addr + kk * 32),
+                    smem_desc_sw128_mn(v_addr + kk * 16 * 128, FA_KEYS * 128), idesc_pv, kk ? 1u : 0u);
+        umma_commit(&S.pv_full);
+        umma_commit(&S.kv_empty[s]);            // K and V of this tile have been read
+      }
+    }
+  } else if (n_tiles > 0) {
+    // ---------------------------------------------------------------- softmax (warps 2..9)
+    const int quarter = warp & 3;                        // TMEM lanes this warp may read
+    const int half = (warp - 2) >> 2;                    // 0: keys 0..31 and dims 0..Hd/2-1;  1: the other halves
+    const int row = quarter * 32 + lane;
+    const int tok = row / P.gs, head = row % P.gs;
+    const bool valid = tok < ntok;
+    const int pos = first_pos + (valid ? tok : 0);
+    const int lo = (P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    constexpr int OD = HD / 2;                           // output dims per thread
+    float o[OD];
+#pragma unroll
+    for (int i = 0; i < OD; i++) o[i] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+
+    auto add_pv = [&](int j) -> bool {                   // o += PV of tile j
+      if (!mbar_wait(&S.pv_full, j & 1, abort_flag)) { if (lane == 0) FA_FAIL(208); return false; }
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < OD; c += 32) {
+        float pv[32];
+        tmem_ld32f(lane_addr + COL_PV + half * OD + c, pv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i++) o[c + i] += pv[i];
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&S.pv_empty);
+      return true;
+    };
+
+    for (int j = 0; j < n_tiles; j++) {
+      const int b = j & 1;
+      if (!mbar_wait(&S.s_full[b], (j >> 1) & 1, abort_flag)) { if (lane == 0) FA_FAIL(209); ok = false; break; }
+      tc_fence_after();
+      float s[FA_KEYS];
+      {
+        float a[32];
+        tmem_ld32f(lane_addr + b * FA_KEYS, a);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i++) s[i] = a[i];
+        tmem_ld32f(lane_addr + b * FA_KEYS + 32, a);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i++) s[32 + i] = a[i];
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&S.s_empty[b]);
+      // mask, scale (in units of log2), maximum over the whole tile
+      const int key0 = (lo_tile + j) * FA_KEYS;
+      float tile_max = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < FA_KEYS; i++) {
+        const int key = key0 + i;
+        s[i] = (valid && key <= pos && key >= lo) ? s[i] * P.scale_log2 : -INFINITY;
+        tile_max = fmaxf(tile_max, s[i]);
+      }
+      const float m_new = fmaxf(m, tile_max);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float corr = exp2f(m - m_use);               // exp2(-inf) = 0 at the first keys
+      // this thread's half of the keys: probabilities, their sum, and P in the layout the MMA reads
+      uint32_t packed[16];
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        // (both indices spelled out so that s[] stays in registers)
+        const float p0 = exp2f((half ? s[32 + i] : s[i]) - m_use), p1 = exp2f((half ? s[33 + i] : s[i + 1]) - m_use);
+        __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
+        // the value sum runs over the rounded probabilities; the denominator does too, so rows sum to one
+        sum += __bfloat162float(pr.x) + __bfloat162float(pr.y);
+        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pr);
+      }
+      if (j > 0) { if (!add_pv(j - 1)) { ok = false; break; } }   // also: P of tile j-1 has been read
+#pragma unroll
+      for (int i = 0; i < OD; i++) o[i] *= corr;
+      l = l * corr + sum;
+      m = m_new;
+      {
+        uint8_t* prow = reinterpret_cast<uint8_t*>(S.p) + row * 128;
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          const int chunk = half * 4 + c;                // 16-byte chunk = 8 keys
+          *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) =
+              make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+        }
+      }
+      fence_async_shared();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&S.p_full);
+    }
+    if (ok) ok = add_pv(n_tiles - 1);
+    // the two halves of the keys kept separate denominators: add them (named barrier among the softmax warps;
+    // reached by all of them or, after a failed wait, by none past this point)
+    if (half == 1) S.l_half[row] = l;
+    asm volatile("bar.sync 1, %0;" ::"n"(FA_SOFTMAX_WARPS * 32) : "memory");
+    if (half == 0) S.l_half[row] += l;
+    asm volatile("bar.sync 1, %0;" ::"n"(FA_SOFTMAX_WARPS * 32) : "memory");
+    if (ok && !S.abort_flag && valid) {
+      const float inv = 1.0f / S.l_half[row];
+      bf16* op = P.out + (size_t)(tok0 + tok) * P.ldo + (size_t)(kvh * P.gs + head) * HD + half * OD;
+#pragma unroll
+      for (int c = 0; c < OD; c += 8) {
+        uint4 w;
+        __nv_bfloat162 a0 = __floats2bfloat162_rn(o[c] * inv, o[c + 1] * inv);
+        __nv_bfloat162 a1 = __floats2bfloat162_rn(o[c + 2] * inv, o[c + 3] * inv);
+        __nv_bfloat162 a2 = __floats2bfloat162_rn(o[c + 4] * inv, o[c + 5] * inv);
+        __nv_bfloat162 a3 = __floats2bfloat162_rn(o[c + 6] * inv, o[c + 7] * inv);
+        w.x = *reinterpret_cast<uint32_t*>(&a0); w.y = *reinterpret_cast<uint32_t*>(&a1);
+        w.z = *reinterpret_cast<uint32_t*>(&a2); w.w = *reinterpret_cast<uint32_t*>(&a3);
+        *reinterpret_cast<uint4*>(op + c) = w;
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+static int make_map_nd(CUtensorMap* map, const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides,
+                       const cuuint32_t* box) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return STRATUM_ERR_LIMIT;
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : STRATUM_ERR_SHAPE;
+}
+
+template <int HD>
+static int launch_attention_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& P,
+                               int n_qblocks, cudaStream_t stream) {
+  const size_t smem = sizeof(FaSmem<HD>) + 1024;
+  auto kern = attention_tc_kernel<HD>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  return launch_pdl(kern, dim3(n_qblocks, P.n_kv), FA_THREADS, smem, stream, mq, mk, mv, P);
+}
+
+// q: bf16 [tokens][ldq], query heads first (n_q * head_dim values per row are used).
+// k_cache / v_cache: bf16 [n_pages][n_kv][64][head_dim].  Query tiles (qb_*): runs of at most 128 / (n_q / n_kv)
+// consecutive new tokens of one sequence.  head_dim 64 or 128; 128 % (n_q / n_kv) == 0; pages of 64 tokens.
+STRATUM_EXPORT int stratum_attention_tc(const void* q, int ldq, const void* k_cache, const void* v_cache,
+                                        long long n_pages, const int* token_pos, const int* block_table,
+                                        int bt_stride, const int* qb_seq, const int* qb_tok0, const int* qb_ntok,
+                                        int n_qblocks, void* out, int ldo, int n_tokens, int n_q, int n_kv,
+                                        int head_dim, int page_tokens, int window, float scale, int* status,
+                                        cudaStream_t stream) {
+  if (n_tokens <= 0 || n_qblocks <= 0) return 0;
+  if (head_dim != 64 && head_dim != 128) return STRATUM_ERR_SHAPE;
+  if (n_kv < 1 || n_q % n_kv != 0 || page_tokens != FA_KEYS) return STRATUM_ERR_SHAPE;
+  const int gs = n_q / n_kv;
+  if (gs > FA_ROWS || FA_ROWS % gs != 0) return STRATUM_ERR_SHAPE;
+  if (ldq % 8 != 0 || ldo % 8 != 0 || !status || !qb_seq || !qb_tok0 || !qb_ntok) return STRATUM_ERR_ALIGN;
+  if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return STRATUM_ERR_ALIGN;
+  if (n_kv > 65535) return STRATUM_ERR_LIMIT;
+  const int R = FA_ROWS / gs;
+  CUtensorMap mq, mk, mv;
+  int st;
+  {  // q as [tokens][n_q heads][head_dim]; a box is 64 dims x gs heads x R tokens: rows token * gs + head
+    cuuint64_t dims[3] = {(cuuint64_t)head_dim, (cuuint64_t)n_q, (cuuint64_t)n_tokens};
+    cuuint64_t strides[2] = {(cuuint64_t)head_dim * sizeof(bf16), (cuuint64_t)ldq * sizeof(bf16)};
+    cuuint32_t box[3] = {64, (cuuint32_t)gs, (cuuint32_t)R};
+    if ((st = make_map_nd(&mq, q, 3, dims, strides, box)) != 0) return st;
+  }
+  {  // the cache as [pages * n_kv * 64 rows][head_dim]; a box is 64 dims x 64 keys
+    cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)n_pages * n_kv * FA_KEYS};
+    cuuint64_t strides[1] = {(cuuint64_t)head_dim * sizeof(bf16)};
+    cuuint32_t box[2] = {64, FA_KEYS};
+    if ((st = make_map_nd(&mk, k_cache, 2, dims, strides, box)) != 0) return st;
+    if ((st = make_map_nd(&mv, v_cache, 2, dims, strides, box)) != 0) return st;
+  }
+  FaParams P;
+  P.token_pos = token_pos; P.block_table = block_table; P.bt_stride = bt_stride;
+  P.qb_seq = qb_seq; P.qb_tok0 = qb_tok0; P.qb_ntok = qb_ntok;
+  P.out = (bf16*)out; P.ldo = ldo; P.status = status;
+  P.n_q = n_q; P.n_kv = n_kv; P.gs = gs; P.tokens_per_tile = R; P.window = window;
+  P.scale_log2 = scale * 1.4426950408889634f;
+  if (head_dim == 64) return launch_attention_tc<64>(mq, mk, mv, P, n_qblocks, stream);
+  return launch_attention_tc<128>(mq, mk, mv, P, n_qblocks, stream);
+}

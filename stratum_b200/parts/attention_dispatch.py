@@ -6,6 +6,8 @@ sequence are cut into splits so that the whole GPU has work, which needs scratch
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import kernels as K
@@ -41,6 +43,10 @@ def run(att, qkv: torch.Tensor, cache, step, out: torch.Tensor) -> None:
         K.attention_mma(qkv, cache.k, cache.v, step.token_pos, step.token_seq, cache.block_table, None, 1, out,
                         part_o, part_ml, att.n_heads, att.n_kv_heads, hd, PAGE_TOKENS, att.window, att.scale,
                         n_splits, chunk)
+    elif hd in (64, 128) and 128 % gs == 0 and os.environ.get("STRATUM_ATTENTION_TC", "1") != "0":
+        # prompts: the tcgen05 kernel, query tiles of 128 rows (128 / gs tokens)
+        K.attention_tc(qkv, cache.k, cache.v, step.token_pos, cache.block_table, step.query_blocks(128 // gs), out,
+                       att.n_heads, att.n_kv_heads, hd, PAGE_TOKENS, att.window, att.scale)
     else:
         per_warp = 16 // rows_per_token
         K.attention_tile(qkv, cache.k, cache.v, step.token_pos, step.token_seq, cache.block_table,
