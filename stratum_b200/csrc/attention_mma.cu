@@ -483,6 +483,172 @@ STRATUM_EXPORT int stratum_attention_tile(const void* q, int ldq, const void* k_
   }
 }
 
+// ---------------------------------------------------------------- decode steps: keys along M
+// One new token per sequence and at most 8 query heads per kv head.  With the query heads along M a 16-row
+// MMA would be three quarters empty, and mma.sync is slow enough on this GPU for that to show next to the
+// time the keys take to arrive.  So the roles are swapped: S^T = K Q^T has the 16 keys of a block along M and the
+// heads along N (8 columns), and O^T = V^T P^T has 16 output dimensions along M; half as many MMAs, half as many
+// accumulator registers.  Fragments still come straight from global memory:
+//   K as the A operand: lane (g,t) holds rows key0+g and key0+8+g, its 8 contiguous dims per 32-dim chunk;
+//   Q^T as the B operand: lane (g,t) holds head g's same 8 dims;
+//   P^T: the accumulator of S^T holds (key g | g+8, heads 2t, 2t+1); packed to bfloat16 and transposed by
+//        movmatrix it is the B operand (keys 2t, 2t+1 | +8; head g);
+//   V^T as the A operand: each 32-bit register of a V load is an 8x8 (key, dim pair) matrix whose movmatrix
+//        transpose gives (dim, keys 2t, 2t+1); registers i and i+1 of a chunk form the 16 rows of one MMA, for the
+//        dims 32c + 8(g/2) + (g%2) + 2i  and  + 2(i+1).
+template <int CH>
+__global__ void __launch_bounds__(AM_WARPS * 32)
+attention_decode_kernel(const AttnParams P) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  pdl_trigger();
+  long long item = (long long)blockIdx.x * AM_WARPS + warp;
+  const long long n_items = (long long)P.n_qblocks * P.n_kv * P.n_splits;
+  if (item >= n_items) return;
+  const int split = (int)(item % P.n_splits); item /= P.n_splits;
+  const int kvh = (int)(item % P.n_kv); item /= P.n_kv;
+  const int tok = (int)item;                            // token = sequence index of the step
+  const int seq = P.token_seq[tok];
+  if (seq < 0) return;                                    // padding
+  const int gs = P.n_q / P.n_kv;
+  const int Hd = P.head_dim;
+  const int pos = P.token_pos[tok];
+  const int lo = (P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
+  int k_begin = split * P.chunk;
+  const int k_end = min((split + 1) * P.chunk, pos + 1);
+  if (k_begin < (lo / 16) * 16) k_begin = (lo / 16) * 16;
+  const int* bt = P.block_table + (size_t)seq * P.bt_stride;
+  const int first_page = (k_begin < k_end) ? bt[k_begin / P.page_tokens] : 0;
+  pdl_wait();
+
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+  uint4 qv[CH];                                           // head g of the group (zero beyond the group)
+#pragma unroll
+  for (int c = 0; c < CH; c++) {
+    const int d = 32 * c + 8 * t;
+    qv[c] = (g < gs && d < Hd) ? ldg16(P.q + (size_t)tok * P.ldq + (size_t)(kvh * gs + g) * Hd + d) : zero4;
+  }
+  float o[2 * CH][4];                                     // [chunk, register pair][dim row g | g+8 x heads 2t, 2t+1]
+#pragma unroll
+  for (int i = 0; i < 2 * CH; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};   // heads 2t, 2t+1 (over this lane's keys only)
+
+  const size_t head_off = (size_t)kvh * P.page_tokens * Hd;
+  const size_t page_stride = (size_t)P.n_kv * P.page_tokens * Hd;
+  auto block_base = [&](int key0) -> size_t {
+    const int page = (key0 == k_begin) ? first_page : bt[key0 / P.page_tokens];
+    return (size_t)page * page_stride + head_off + (size_t)(key0 % P.page_tokens) * Hd;
+  };
+  uint4 ka[CH], kb[CH];
+  size_t base = 0;
+  if (k_begin < k_end) {
+    base = block_base(k_begin);
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+      const int d = 32 * c + 8 * t;
+      ka[c] = d < Hd ? ldg16(P.k_cache + base + (size_t)g * Hd + d) : zero4;
+      kb[c] = d < Hd ? ldg16(P.k_cache + base + (size_t)(g + 8) * Hd + d) : zero4;
+    }
+  }
+  for (int key0 = k_begin; key0 < k_end; key0 += 16) {
+    const bf16* vp = P.v_cache + base;
+    uint4 va[CH], vb[CH], nka[CH], nkb[CH];
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+      const int d = 32 * c + 8 * t;
+      va[c] = d < Hd ? ldg16(vp + (size_t)g * Hd + d) : zero4;
+      vb[c] = d < Hd ? ldg16(vp + (size_t)(g + 8) * Hd + d) : zero4;
+    }
+    const bool more = key0 + 16 < k_end;
+    if (more) base = block_base(key0 + 16);
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+      const int d = 32 * c + 8 * t;
+      nka[c] = (more && d < Hd) ? ldg16(P.k_cache + base + (size_t)g * Hd + d) : zero4;
+      nkb[c] = (more && d < Hd) ? ldg16(P.k_cache + base + (size_t)(g + 8) * Hd + d) : zero4;
+    }
+    // S^T: [0],[1] = (key g, heads 2t, 2t+1); [2],[3] = (key g+8, same heads)
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+      mma16816(s, ka[c].x, kb[c].x, ka[c].y, kb[c].y, qv[c].x, qv[c].y);
+      mma16816(s, ka[c].z, kb[c].z, ka[c].w, kb[c].w, qv[c].z, qv[c].w);
+    }
+    const bool ok0 = key0 + g <= pos && key0 + g >= lo && key0 + g < k_end;
+    const bool ok1 = key0 + g + 8 <= pos && key0 + g + 8 >= lo && key0 + g + 8 < k_end;
+    s[0] = ok0 ? s[0] * P.scale : -INFINITY; s[1] = ok0 ? s[1] * P.scale : -INFINITY;
+    s[2] = ok1 ? s[2] * P.scale : -INFINITY; s[3] = ok1 ? s[3] * P.scale : -INFINITY;
+    // maximum per head over the block's 16 keys: this lane's two keys, then across g (lanes 4, 8, 16 apart)
+    float bm[2] = {fmaxf(s[0], s[2]), fmaxf(s[1], s[3])};
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+      bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 4));
+      bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 8));
+      bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 16));
+      const float m_new = fmaxf(m_run[e], bm[e]);
+      m_use[e] = (m_new == -INFINITY) ? 0.f : m_new;
+      corr[e] = __expf(m_run[e] - m_use[e]);
+      m_run[e] = m_new;
+    }
+    const float p0 = __expf(s[0] - m_use[0]), p1 = __expf(s[1] - m_use[1]);
+    const float p2 = __expf(s[2] - m_use[0]), p3 = __expf(s[3] - m_use[1]);
+    l_run[0] = l_run[0] * corr[0] + p0 + p2;
+    l_run[1] = l_run[1] * corr[1] + p1 + p3;
+#pragma unroll
+    for (int i = 0; i < 2 * CH; i++) {
+      o[i][0] *= corr[0]; o[i][1] *= corr[1]; o[i][2] *= corr[0]; o[i][3] *= corr[1];
+    }
+    // P^T as the B operand: (keys 2t, 2t+1; head g) and (keys 2t+8, 2t+9; head g)
+    const uint32_t pb0 = transpose8x8(pack_bf16(p0, p1)), pb1 = transpose8x8(pack_bf16(p2, p3));
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+#pragma unroll
+      for (int ii = 0; ii < 2; ii++) {
+        const uint32_t a0 = transpose8x8(reg_of(va[c], 2 * ii)), a1 = transpose8x8(reg_of(va[c], 2 * ii + 1));
+        const uint32_t a2 = transpose8x8(reg_of(vb[c], 2 * ii)), a3 = transpose8x8(reg_of(vb[c], 2 * ii + 1));
+        mma16816(o[2 * c + ii], a0, a1, a2, a3, pb0, pb1);
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < CH; c++) { ka[c] = nka[c]; kb[c] = nkb[c]; }
+  }
+  // denominators: this lane summed its own two keys of every block; add across g
+#pragma unroll
+  for (int e = 0; e < 2; e++) {
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 4);
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 8);
+    l_run[e] += __shfl_xor_sync(0xffffffffu, l_run[e], 16);
+  }
+  // o[2c+ii]: [0],[1] = (dim D(2ii), heads 2t, 2t+1); [2],[3] = (dim D(2ii+1), same heads), D(i) = 32c + 8(g/2) + (g%2) + 2i
+#pragma unroll
+  for (int e = 0; e < 2; e++) {
+    const int hq = 2 * t + e;
+    if (hq >= gs) continue;
+    const int head = kvh * gs + hq;
+    const float inv = (P.n_splits == 1) ? 1.0f / l_run[e] : 1.0f;
+    const size_t slot = ((size_t)tok * P.n_q + head) * P.n_splits + split;
+#pragma unroll
+    for (int c = 0; c < CH; c++) {
+#pragma unroll
+      for (int ii = 0; ii < 2; ii++) {
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+          const int d = 32 * c + 8 * (g >> 1) + (g & 1) + 2 * (2 * ii + r);
+          if (d >= Hd) continue;
+          const float v = o[2 * c + ii][2 * r + e] * inv;
+          if (P.n_splits == 1) P.out[(size_t)tok * P.ldo + (size_t)head * Hd + d] = __float2bfloat16_rn(v);
+          else P.part_o[slot * Hd + d] = v;
+        }
+      }
+    }
+    if (P.n_splits > 1 && g == 0) {
+      P.part_ml[slot * 2] = m_run[e];
+      P.part_ml[slot * 2 + 1] = l_run[e];
+    }
+  }
+}
+
 // Merge the splits of one (token, head): one block each, one thread per output dimension, splits in order.
 __global__ void __launch_bounds__(128)
 attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
@@ -543,6 +709,18 @@ STRATUM_EXPORT int stratum_attention_mma(const void* q, int ldq, const void* k_c
   if (blocks > 0x7fffffffLL) return STRATUM_ERR_LIMIT;
   const int ch = (head_dim + 31) / 32;
   int st = 0;
+  if (!qb_seq && tokens_per_block == 1 && gs <= 8) {
+    // decode steps: the kernel with the keys along M
+    const long long d_items = (long long)n_qblocks * n_kv * n_splits;
+    const unsigned d_blocks = (unsigned)((d_items + AM_WARPS - 1) / AM_WARPS);
+    switch (ch) {
+      case 1: st = launch_pdl(attention_decode_kernel<1>, d_blocks, AM_WARPS * 32, 0, stream, P); break;
+      case 2: st = launch_pdl(attention_decode_kernel<2>, d_blocks, AM_WARPS * 32, 0, stream, P); break;
+      case 3: st = launch_pdl(attention_decode_kernel<3>, d_blocks, AM_WARPS * 32, 0, stream, P); break;
+      case 4: st = launch_pdl(attention_decode_kernel<4>, d_blocks, AM_WARPS * 32, 0, stream, P); break;
+      default: return STRATUM_ERR_SHAPE;
+    }
+  } else
   switch (ch) {
     case 1: st = launch_pdl(attention_mma_kernel<1>, (unsigned)blocks, AM_WARPS * 32, 0, stream, P); break;
     case 2: st = launch_pdl(attention_mma_kernel<2>, (unsigned)blocks, AM_WARPS * 32, 0, stream, P); break;

@@ -53,6 +53,12 @@ struct FaSmem {
   int abort_flag;
 };
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 #define FA_FAIL(code) { atomicCAS(P.status, 0, code); S.abort_flag = 1; }
 
 template <int HD>
@@ -215,33 +221,45 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.s_empty[b]);
-      // mask, scale (in units of log2), maximum over the whole tile
+      // maximum over the whole tile; keys beyond a row's own position (or before its window) are masked, which
+      // only tiles on the diagonal (or at the window's edge) need
       const int key0 = (lo_tile + j) * FA_KEYS;
+      const bool needs_mask = (key0 + FA_KEYS - 1 > first_pos) || (P.window > 0) || (ntok < P.tokens_per_tile);
       float tile_max = -INFINITY;
+      if (needs_mask) {
 #pragma unroll
-      for (int i = 0; i < FA_KEYS; i++) {
-        const int key = key0 + i;
-        s[i] = (valid && key <= pos && key >= lo) ? s[i] * P.scale_log2 : -INFINITY;
-        tile_max = fmaxf(tile_max, s[i]);
+        for (int i = 0; i < FA_KEYS; i++) {
+          const int key = key0 + i;
+          s[i] = (valid && key <= pos && key >= lo) ? s[i] : -INFINITY;
+          tile_max = fmaxf(tile_max, s[i]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < FA_KEYS; i++) tile_max = fmaxf(tile_max, s[i]);
       }
+      tile_max *= P.scale_log2;                          // scale > 0: the maximum of the scaled scores
       const float m_new = fmaxf(m, tile_max);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = exp2f(m - m_use);               // exp2(-inf) = 0 at the first keys
-      // this thread's half of the keys: probabilities, their sum, and P in the layout the MMA reads
+      const float corr = fast_exp2(m - m_use);           // exp2(-inf) = 0 at the first keys
+      // this thread's half of the keys: probabilities exp2(s * scale - m), their sum, and P in the layout the
+      // MMA reads
       uint32_t packed[16];
       float sum = 0.f;
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
         // (both indices spelled out so that s[] stays in registers)
-        const float p0 = exp2f((half ? s[32 + i] : s[i]) - m_use), p1 = exp2f((half ? s[33 + i] : s[i + 1]) - m_use);
+        const float p0 = fast_exp2(fmaf(half ? s[32 + i] : s[i], P.scale_log2, -m_use));
+        const float p1 = fast_exp2(fmaf(half ? s[33 + i] : s[i + 1], P.scale_log2, -m_use));
         __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
         // the value sum runs over the rounded probabilities; the denominator does too, so rows sum to one
         sum += __bfloat162float(pr.x) + __bfloat162float(pr.y);
         packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pr);
       }
       if (j > 0) { if (!add_pv(j - 1)) { ok = false; break; } }   // also: P of tile j-1 has been read
+      if (__any_sync(0xffffffffu, corr != 1.0f)) {        // the maximum moved for some row of this warp
 #pragma unroll
-      for (int i = 0; i < OD; i++) o[i] *= corr;
+        for (int i = 0; i < OD; i++) o[i] *= corr;
+      }
       l = l * corr + sum;
       m = m_new;
       {

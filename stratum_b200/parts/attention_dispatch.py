@@ -13,7 +13,8 @@ import torch
 from .. import kernels as K
 from ..cache.pages import PAGE_TOKENS
 
-TARGET_WARPS = 148 * 8          # work items wanted in flight: 148 SMs, 8 warps each
+# work items (warps) wanted in flight on decode steps: 148 SMs times the warps an SM holds of the decode kernel
+TARGET_WARPS = int(os.environ.get("STRATUM_ATTENTION_WARPS", 148 * 8))
 
 
 def plan_splits(n_items: int, max_len: int):

@@ -351,7 +351,7 @@ def test_attention_mma_prompts_and_continuations(n_q, n_kv, hd):
     assert rel_err(as64(out), c["ref"]) < 8e-3
 
 
-@pytest.mark.parametrize("n_q,n_kv,hd", [(8, 2, 128), (4, 4, 64), (40, 2, 32)])
+@pytest.mark.parametrize("n_q,n_kv,hd", [(8, 2, 128), (4, 4, 64), (40, 2, 32), (16, 2, 128), (6, 2, 48), (2, 1, 16)])
 @pytest.mark.parametrize("n_splits,chunk", [(1, 0), (4, 256), (11, 64)])
 def test_attention_mma_decode_with_splits(n_q, n_kv, hd, n_splits, chunk):
     rng = np.random.default_rng(hd)
