@@ -561,6 +561,12 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
   return launch_status();
 }
 
+#ifndef SK_RING_16
+#define SK_RING_16 10
+#define SK_RING_32 9
+#define SK_RING_64 8
+#endif
+
 template <int BN, int STAGES>
 static int launch_streamk(const CUtensorMap& mw, const CUtensorMap& mx, const SkParams& P, int epilogue,
                           cudaStream_t stream) {
@@ -630,7 +636,9 @@ STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bi
   Q.tiles = (N + TC_BM - 1) / TC_BM;
   Q.n_kb = (K + TC_BK - 1) / TC_BK;
   Q.total_kb = Q.tiles * Q.n_kb;
-  if (bn == 16) return launch_streamk<16, 10>(ma, mb, Q, epilogue, stream);
-  if (bn == 32) return launch_streamk<32, 9>(ma, mb, Q, epilogue, stream);
-  return launch_streamk<64, 8>(ma, mb, Q, epilogue, stream);
+  // rings of about 180 KB: what is in flight per SM decides the rate at which weights stream in (rings half
+  // as deep, two CTAs per SM, ran a third slower)
+  if (bn == 16) return launch_streamk<16, SK_RING_16>(ma, mb, Q, epilogue, stream);
+  if (bn == 32) return launch_streamk<32, SK_RING_32>(ma, mb, Q, epilogue, stream);
+  return launch_streamk<64, SK_RING_64>(ma, mb, Q, epilogue, stream);
 }
