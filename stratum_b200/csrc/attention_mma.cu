@@ -649,31 +649,59 @@ attention_decode_kernel(const AttnParams P) {
   }
 }
 
-// Merge the splits of one (token, head): one block each, one thread per output dimension, splits in order.
+// Merge the splits of one (token, head): one block each.  The maxima and denominators of all splits are fetched
+// at once (one thread per split), turned into weights exp(m_s - M) in shared memory, then every thread adds up
+// its output dimension over the splits in split order.
+#define MERGE_MAX_SPLITS 256
 __global__ void __launch_bounds__(128)
 attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                        bf16* __restrict__ out, int ldo, const int* __restrict__ token_seq, int n_tokens, int n_q,
                        int head_dim, int n_splits) {
+  __shared__ float wgt[MERGE_MAX_SPLITS];
+  __shared__ float red[2];
   pdl_trigger();
   const int item = blockIdx.x;
   const int tok = item / n_q, h = item % n_q;
   if (token_seq && token_seq[tok] < 0) return;
   pdl_wait();
   const float* ml = part_ml + (size_t)item * n_splits * 2;
-  float m = -INFINITY;
-  for (int s = 0; s < n_splits; s++) m = fmaxf(m, ld_fresh(ml + 2 * s));
   const float* po = part_o + (size_t)item * n_splits * head_dim;
+  // warp 0: the maximum over splits, then the weights and the denominator
+  if (threadIdx.x < 32) {
+    float ms[MERGE_MAX_SPLITS / 32], ls[MERGE_MAX_SPLITS / 32];
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < MERGE_MAX_SPLITS / 32; j++) {
+      const int sidx = threadIdx.x + 32 * j;
+      ms[j] = sidx < n_splits ? ld_fresh(ml + 2 * sidx) : -INFINITY;
+      ls[j] = sidx < n_splits ? ld_fresh(ml + 2 * sidx + 1) : 0.f;
+      m = fmaxf(m, ms[j]);
+    }
+    m = warp_max(m);
+    float l = 0.f;
+#pragma unroll
+    for (int j = 0; j < MERGE_MAX_SPLITS / 32; j++) {
+      const int sidx = threadIdx.x + 32 * j;
+      const float w = (ms[j] == -INFINITY) ? 0.f : __expf(ms[j] - m);
+      if (sidx < n_splits) wgt[sidx] = w;
+      l += ls[j] * w;
+    }
+    l = warp_sum(l);
+    if (threadIdx.x == 0) red[0] = l;
+  }
+  __syncthreads();
   const int d = threadIdx.x;
   if (d >= head_dim) return;
-  float l = 0.f, acc = 0.f;
-#pragma unroll 4
-  for (int s = 0; s < n_splits; s++) {
-    const float ms = ld_fresh(ml + 2 * s);
-    const float wgt = (ms == -INFINITY) ? 0.f : __expf(ms - m);
-    l += ld_fresh(ml + 2 * s + 1) * wgt;
-    acc += ld_fresh(po + (size_t)s * head_dim + d) * wgt;
+  float acc = 0.f;
+  int sidx = 0;
+  for (; sidx + 4 <= n_splits; sidx += 4) {             // four loads in flight at a time, added in split order
+    const float a0 = ld_fresh(po + (size_t)(sidx + 0) * head_dim + d), a1 = ld_fresh(po + (size_t)(sidx + 1) * head_dim + d);
+    const float a2 = ld_fresh(po + (size_t)(sidx + 2) * head_dim + d), a3 = ld_fresh(po + (size_t)(sidx + 3) * head_dim + d);
+    acc = fmaf(a0, wgt[sidx], acc); acc = fmaf(a1, wgt[sidx + 1], acc);
+    acc = fmaf(a2, wgt[sidx + 2], acc); acc = fmaf(a3, wgt[sidx + 3], acc);
   }
-  out[(size_t)tok * ldo + (size_t)h * head_dim + d] = __float2bfloat16_rn(acc / l);
+  for (; sidx < n_splits; sidx++) acc = fmaf(ld_fresh(po + (size_t)sidx * head_dim + d), wgt[sidx], acc);
+  out[(size_t)tok * ldo + (size_t)h * head_dim + d] = __float2bfloat16_rn(acc / red[0]);
 }
 
 // Scratch needed for n_splits > 1: floats for part_o = tokens*Nq*n_splits*Hd, for part_ml = tokens*Nq*n_splits*2.
@@ -688,6 +716,7 @@ STRATUM_EXPORT int stratum_attention_mma(const void* q, int ldq, const void* k_c
   if (head_dim % 16 != 0 || head_dim < 16 || head_dim > 128) return STRATUM_ERR_SHAPE;
   if (n_kv < 1 || n_q % n_kv != 0 || page_tokens % 16 != 0) return STRATUM_ERR_SHAPE;
   if (n_splits < 1 || (n_splits > 1 && (chunk % page_tokens != 0 || !part_o || !part_ml))) return STRATUM_ERR_SHAPE;
+  if (n_splits > MERGE_MAX_SPLITS) return STRATUM_ERR_LIMIT;
   if (ldq % 8 != 0 || ldo % 8 != 0) return STRATUM_ERR_ALIGN;
   if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return STRATUM_ERR_ALIGN;
   const int gs = n_q / n_kv;

@@ -225,18 +225,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // only tiles on the diagonal (or at the window's edge) need
       const int key0 = (lo_tile + j) * FA_KEYS;
       const bool needs_mask = (key0 + FA_KEYS - 1 > first_pos) || (P.window > 0) || (ntok < P.tokens_per_tile);
-      float tile_max = -INFINITY;
+      // (four running maxima, then combined: one chain of 64 dependent comparisons would cost more time than
+      // everything else a thread does per tile)
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (needs_mask) {
 #pragma unroll
         for (int i = 0; i < FA_KEYS; i++) {
           const int key = key0 + i;
           s[i] = (valid && key <= pos && key >= lo) ? s[i] : -INFINITY;
-          tile_max = fmaxf(tile_max, s[i]);
+          mx[i & 3] = fmaxf(mx[i & 3], s[i]);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < FA_KEYS; i++) tile_max = fmaxf(tile_max, s[i]);
+        for (int i = 0; i < FA_KEYS; i++) mx[i & 3] = fmaxf(mx[i & 3], s[i]);
       }
+      float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       tile_max *= P.scale_log2;                          // scale > 0: the maximum of the scaled scores
       const float m_new = fmaxf(m, tile_max);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
@@ -244,7 +247,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // this thread's half of the keys: probabilities exp2(s * scale - m), their sum, and P in the layout the
       // MMA reads
       uint32_t packed[16];
-      float sum = 0.f;
+      float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
         // (both indices spelled out so that s[] stays in registers)
@@ -252,9 +255,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const float p1 = fast_exp2(fmaf(half ? s[33 + i] : s[i + 1], P.scale_log2, -m_use));
         __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
         // the value sum runs over the rounded probabilities; the denominator does too, so rows sum to one
-        sum += __bfloat162float(pr.x) + __bfloat162float(pr.y);
+        sum0 += __bfloat162float(pr.x);
+        sum1 += __bfloat162float(pr.y);
         packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pr);
       }
+      const float sum = sum0 + sum1;
       if (j > 0) { if (!add_pv(j - 1)) { ok = false; break; } }   // also: P of tile j-1 has been read
       if (__any_sync(0xffffffffu, corr != 1.0f)) {        // the maximum moved for some row of this warp
 #pragma unroll

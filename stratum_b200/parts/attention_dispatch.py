@@ -17,10 +17,13 @@ from ..cache.pages import PAGE_TOKENS
 TARGET_WARPS = int(os.environ.get("STRATUM_ATTENTION_WARPS", 148 * 8))
 
 
+MAX_SPLITS = 256                # what the merge kernel takes
+
+
 def plan_splits(n_items: int, max_len: int):
     """(n_splits, keys per split) for decode steps: enough splits to fill the GPU, whole pages per split."""
     pages = max(1, (max_len + PAGE_TOKENS - 1) // PAGE_TOKENS)
-    want = max(1, min(pages, (TARGET_WARPS + n_items - 1) // n_items))
+    want = max(1, min(pages, MAX_SPLITS, (TARGET_WARPS + n_items - 1) // n_items))
     chunk = ((pages + want - 1) // want) * PAGE_TOKENS
     return (max_len + chunk - 1) // chunk, chunk
 
