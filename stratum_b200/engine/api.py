@@ -39,7 +39,8 @@ class _EngineBackend(Backend):
         if self.graphs is not None and all(len(toks) == 1 for _, toks in work):
             uniforms = None if params.greedy else [st.uniform() for st in streams]
             picked, values, captured = self.graphs.step([s for s, _ in work], [toks[0] for _, toks in work],
-                                                        params.temperature, params.top_k, params.top_p, uniforms)
+                                                        params.temperature, params.top_k, params.top_p, uniforms,
+                                                        trusted=True)     # the loop feeds back ids picked here
             if self.on_logits is not None:
                 self.on_logits(captured.logits[:len(work)], picked)
             return picked, values

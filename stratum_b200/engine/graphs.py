@@ -58,6 +58,9 @@ class _Captured:
         self.out_ids = torch.zeros(B, dtype=torch.int32, device=device)
         self.out_vals = torch.zeros(B, dtype=torch.float32, device=device)
         self.out_host = torch.empty(2 * B, dtype=torch.int32).pin_memory()
+        self.views = {name: self.np[o:o + n] for name, (o, n) in self.off.items()}
+        self.signature = None                         # (slots, pages per sequence) the host buffer was last filled for
+        self.sampling = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.kernels = 0
         self.logits: Optional[torch.Tensor] = None
@@ -78,6 +81,7 @@ class DecodeGraphs:
         self.pool = None
         self.done = torch.cuda.Event()
         self.captures = 0
+        self.h2d_bytes = self.d2h_bytes = 0           # of the last step
 
     # ------------------------------------------------------------------ building blocks
     def _batch(self, c: _Captured) -> StepBatch:
@@ -130,45 +134,58 @@ class DecodeGraphs:
 
     # ------------------------------------------------------------------ one step
     def step(self, slots: Sequence[int], tokens: Sequence[int], temperature: float, top_k: int, top_p: float,
-             uniforms: Optional[Sequence[float]]) -> Tuple[List[int], List[float], _Captured]:
-        """One token for each slot; returns the picked ids and their logits (host lists)."""
+             uniforms: Optional[Sequence[float]], trusted: bool = False) -> Tuple[List[int], List[float], _Captured]:
+        """One token for each slot; returns the picked ids and their logits (host lists).
+        trusted: the tokens are ids this engine picked itself (no range check needed)."""
         eng = self.engine
+        cache = eng.cache
         B = len(slots)
         if B == 0:
             raise StepError("a step needs at least one entry")
-        if len(set(slots)) != B:
-            raise StepError("a slot appears twice in one step")
-        for s, t in zip(slots, tokens):
-            if not eng.cache.slots.is_live(s):
-                raise StepError(f"slot {s} is not held by a sequence")
-            if not (0 <= int(t) < eng.vocab):
-                raise StepError(f"slot {s}: token id {t} outside the vocabulary [0, {eng.vocab})")
-        eng.cache.reserve(slots, [1] * B)
-        before = [eng.cache.length(s) for s in slots]
+        if not trusted:
+            if len(set(slots)) != B:
+                raise StepError("a slot appears twice in one step")
+            for s, t in zip(slots, tokens):
+                if not cache.slots.is_live(s):
+                    raise StepError(f"slot {s} is not held by a sequence")
+                if not (0 <= int(t) < eng.vocab):
+                    raise StepError(f"slot {s}: token id {t} outside the vocabulary [0, {eng.vocab})")
+        cache.reserve(slots, _ONES[:B] if B <= len(_ONES) else [1] * B)
+        before = [cache.length(s) for s in slots]
         c = self._get(padded_rows(B), width_bucket(pages_for(max(before) + 1)), not (temperature > 0.0))
         R, W = c.rows, c.width
-        h = c.np
-        v = lambda name: c.view(name, False)          # noqa: E731
-        v("ids")[:] = 0; v("ids")[:B] = tokens
-        v("pos")[:] = 0; v("pos")[:B] = before
-        v("seq")[:] = -1; v("seq")[:B] = np.arange(B, dtype=np.int32)
-        v("want")[:] = np.arange(R, dtype=np.int32)
-        v("slot")[:] = 0; v("slot")[:B] = slots
-        v("start")[:] = np.arange(R + 1, dtype=np.int32)
-        v("len")[:] = 0; v("len")[:B] = np.asarray(before, dtype=np.int32) + 1
-        o, n = c.off["tables"]
-        tb = h[o:o + n].reshape(len(self.groups), R, W)
-        tb.fill(-1)
-        for j, gi in enumerate(self.groups):
-            for i, row in enumerate(eng.cache.page_table_rows(slots, gi)):
-                tb[j, i, :len(row)] = row
-        v("temperature").view(np.float32)[:] = temperature
-        v("top_k")[:] = top_k
-        v("top_p").view(np.float32)[:] = top_p
-        u = v("uniform").view(np.float32)
-        u[:] = 0.0
+        v = c.views
+        # what a sequence holds changes every step; who is in the batch and which pages they own only now and then
+        signature = (tuple(slots), tuple(len(r) for gi in self.groups for r in cache.page_table_rows(slots, gi)))
+        if signature != c.signature:
+            c.signature = signature
+            v["ids"][:] = 0
+            v["pos"][:] = 0
+            v["seq"][:] = -1; v["seq"][:B] = np.arange(B, dtype=np.int32)
+            v["want"][:] = np.arange(R, dtype=np.int32)
+            v["slot"][:] = 0; v["slot"][:B] = slots
+            v["start"][:] = np.arange(R + 1, dtype=np.int32)
+            v["len"][:] = 0
+            tb = v["tables"].reshape(len(self.groups), R, W)
+            tb.fill(-1)
+            for j, gi in enumerate(self.groups):
+                for i, row in enumerate(cache.page_table_rows(slots, gi)):
+                    tb[j, i, :len(row)] = row
+            v["top_k"][:] = top_k
+            v["temperature"].view(np.float32)[:] = temperature
+            v["top_p"].view(np.float32)[:] = top_p
+            v["uniform"].view(np.float32)[:] = 0.0
+            c.sampling = (temperature, top_k, top_p)
+        elif c.sampling != (temperature, top_k, top_p):
+            v["top_k"][:] = top_k
+            v["temperature"].view(np.float32)[:] = temperature
+            v["top_p"].view(np.float32)[:] = top_p
+            c.sampling = (temperature, top_k, top_p)
+        v["ids"][:B] = tokens
+        v["pos"][:B] = before
+        v["len"][:B] = v["pos"][:B] + 1
         if uniforms is not None:
-            u[:B] = uniforms
+            v["uniform"].view(np.float32)[:B] = uniforms
         c.dev.copy_(c.host, non_blocking=True)
         if c.graph is None:
             self._capture(c)
@@ -178,6 +195,10 @@ class DecodeGraphs:
         c.out_host[R:].copy_(c.out_vals.view(torch.int32), non_blocking=True)
         self.done.record()
         self.done.synchronize()
-        eng.cache.advance(slots, [1] * B)
+        cache.advance(slots, _ONES[:B] if B <= len(_ONES) else [1] * B)
+        self.h2d_bytes, self.d2h_bytes = c.total * 4, 2 * R * 4
         out = c.out_host.numpy()
         return out[:B].tolist(), out[R:R + B].view(np.float32).tolist(), c
+
+
+_ONES = [1] * 1024
