@@ -279,8 +279,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // x 64 k each) form one sequence of tiles*n_kb blocks; CTA c takes the contiguous stretch
 // [c*total/G, (c+1)*total/G).  A stretch covers the end of one tile, some whole tiles and the beginning of
 // another.  Whole tiles go straight from tensor memory through the epilogue.  A tile shared between CTAs is
-// written as float32 partial sums to scratch; a counter per tile tells the CTA that arrives last, which adds
-// the partial sums in the order of k (the order of the CTA numbers) and runs the epilogue.  The split depends
+// written as float32 partial sums to scratch, and a second, small kernel adds the partial sums of every such
+// tile in the order of k (the order of the CTA numbers) and runs the epilogue.  The split depends
 // only on the shapes and the grid, never on the rows of x, so a row's result does not depend on its batch.
 // W tiles do not depend on earlier kernels and are requested before the programmatic-launch wait.
 struct SkParams {
@@ -288,7 +288,7 @@ struct SkParams {
   void* out;
   int* status;
   float* scratch;         // [gridDim.x][2][BN][128] float32 partial tiles (first / last tile of a CTA's stretch)
-  unsigned* counters;     // [tiles], zero before and after every launch
+  unsigned* counters;     // unused (kept for the entry point's signature)
   int M, N, K, ldo;
   int tiles, n_kb, total_kb;
 };
@@ -330,7 +330,6 @@ struct SkSmem {
   uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  int last_flag;
 };
 
 template <int BN, int STAGES, int EPI>
@@ -352,7 +351,6 @@ gemm_tc_streamk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     for (int s = 0; s < STAGES; s++) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
     for (int b = 0; b < 2; b++) { mbar_init(&S.acc_full[b], 1); mbar_init(&S.acc_empty[b], 4); }
     S.abort_flag = 0;
-    S.last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -473,39 +471,6 @@ gemm_tc_streamk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.acc_empty[buf]);
-      if (!whole) {
-        // every epilogue thread's partial sums are written; count this CTA in; the last one to arrive finishes
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (warp == 2 && lane == 0) {
-          const int first_c = sk_owner(tile * P.n_kb, G, P.total_kb);
-          const int last_c = sk_owner((tile + 1) * P.n_kb - 1, G, P.total_kb);
-          const unsigned old = atomicAdd(&P.counters[tile], 1u);
-          const int is_last = (old == (unsigned)(last_c - first_c));
-          if (is_last) P.counters[tile] = 0;       // everyone has arrived: ready for the next launch
-          S.last_flag = is_last;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (S.last_flag) {
-          __threadfence();
-          const int first_c = sk_owner(tile * P.n_kb, G, P.total_kb);
-          const int last_c = sk_owner((tile + 1) * P.n_kb - 1, G, P.total_kb);
-#pragma unroll 1
-          for (int c0 = 0; c0 < BN; c0 += CW) {
-            float v[CW];
-#pragma unroll
-            for (int j = 0; j < CW; j++) v[j] = 0.f;
-            for (int cc = first_c; cc <= last_c; cc++) {       // in the order of k
-              const int slot = (tile == sk_begin(cc, G, P.total_kb) / P.n_kb) ? 0 : 1;
-              const float* src = P.scratch + ((size_t)(cc * 2 + slot) * BN) * TC_BM;
-#pragma unroll
-              for (int j = 0; j < CW; j++) v[j] += ld_fresh(src + (size_t)(c0 + j) * TC_BM + row);
-            }
-            sk_store<EPI, CW>(P, n, c0, v);
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");    // last_flag is reused by the next shared tile
-      }
       g = seg_end;
       seg++;
     }
@@ -561,6 +526,35 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
   return launch_status();
 }
 
+// Second pass of the stream-K form: every tile that was shared between CTAs is put together from the partial
+// sums in scratch, in the order of k (the order of the CTA numbers), and goes through the epilogue.  One block per
+// (tile, 8 rows of x), one thread per weight row; tiles that one CTA computed alone were finished in the first
+// pass and are skipped here.
+template <int BN, int EPI>
+__global__ void __launch_bounds__(TC_BM)
+gemm_tc_fixup_kernel(const SkParams P, int G) {
+  pdl_trigger();
+  const int tile = blockIdx.x, m0 = blockIdx.y * 8;
+  const int first_c = sk_owner(tile * P.n_kb, G, P.total_kb);
+  const int last_c = sk_owner((tile + 1) * P.n_kb - 1, G, P.total_kb);
+  if (first_c == last_c) return;                   // whole tile: done in the first pass
+  pdl_wait();
+  const int row = threadIdx.x;
+  float v[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) v[j] = 0.f;
+  for (int cc = first_c; cc <= last_c; cc++) {
+    const int slot = (tile == sk_begin(cc, G, P.total_kb) / P.n_kb) ? 0 : 1;
+    const float* src = P.scratch + ((size_t)(cc * 2 + slot) * BN + m0) * TC_BM + row;
+    float a[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) a[j] = (m0 + j < P.M) ? ld_fresh(src + (size_t)j * TC_BM) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; j++) v[j] += a[j];
+  }
+  sk_store<EPI, 8>(P, tile * TC_BM + row, m0, v);
+}
+
 #ifndef SK_RING_16
 #define SK_RING_16 10
 #define SK_RING_32 9
@@ -572,6 +566,8 @@ static int launch_streamk(const CUtensorMap& mw, const CUtensorMap& mx, const Sk
                           cudaStream_t stream) {
   const size_t smem = sizeof(SkSmem<BN, STAGES>) + 1024;
   const int grid = P.total_kb < sm_count() ? P.total_kb : sm_count();
+  // no tile is shared between CTAs when every CTA's stretch is a whole number of tiles
+  const bool split_tiles = !(P.tiles % grid == 0);
 #define SK_LAUNCH(E)                                                                                        \
   {                                                                                                         \
     auto kern = gemm_tc_streamk_kernel<BN, STAGES, E>;                                                      \
@@ -581,7 +577,9 @@ static int launch_streamk(const CUtensorMap& mw, const CUtensorMap& mx, const Sk
       if (e != cudaSuccess) return (int)e;                                                                  \
       configured = true;                                                                                    \
     }                                                                                                       \
-    return launch_pdl(kern, grid, TC_THREADS, smem, stream, mw, mx, P);                                     \
+    int st = launch_pdl(kern, grid, TC_THREADS, smem, stream, mw, mx, P);                                   \
+    if (st != 0 || !split_tiles) return st;                                                                 \
+    return launch_pdl(gemm_tc_fixup_kernel<BN, E>, dim3(P.tiles, (P.M + 7) / 8), TC_BM, 0, stream, P, grid); \
   }
   switch (epilogue) {
     case 0: SK_LAUNCH(0)
