@@ -527,32 +527,89 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
 }
 
 // Second pass of the stream-K form: every tile that was shared between CTAs is put together from the partial
-// sums in scratch, in the order of k (the order of the CTA numbers), and goes through the epilogue.  One block per
-// (tile, 8 rows of x), one thread per weight row; tiles that one CTA computed alone were finished in the first
-// pass and are skipped here.
+// sums in scratch, in the order of k (the order of the CTA numbers), and goes through the epilogue.  A shared
+// tile is one that holds the beginning of some CTA's stretch; block x looks at the beginning of CTA x+1 and takes
+// the tile if it is the first beginning inside it.  A block is 4 rows of x (one per warp) by 128 weight rows
+// (four neighbours per lane, so that every load and store is 16 bytes wide); the loads of up to eight partial
+// tiles are in flight together.
+template <int EPI>
+__device__ __forceinline__ void fixup_store(const SkParams& P, int m, int n, float4 v) {
+  float e[4] = {v.x, v.y, v.z, v.w};
+  if (P.bias) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) if (n + j < P.N) e[j] += P.bias[n + j];
+  }
+  if (EPI == 3) {                                   // (gate, up) pairs: n even
+    bf16* o = (bf16*)P.out + (size_t)m * P.ldo + (n >> 1);
+#pragma unroll
+    for (int j = 0; j < 4; j += 2) {
+      if (n + j + 1 < P.N) {
+        const float g = __bfloat162float(__float2bfloat16_rn(e[j])), u = __bfloat162float(__float2bfloat16_rn(e[j + 1]));
+        o[j >> 1] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
+      }
+    }
+    return;
+  }
+  const size_t idx = (size_t)m * P.ldo + n;
+  const bool wide = (n + 3 < P.N) && ((idx & 3) == 0);
+  if (EPI == 0) {
+    bf16* o = (bf16*)P.out + idx;
+    if (wide && ((reinterpret_cast<uintptr_t>(o) & 7) == 0)) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(e[0], e[1]), hi = __floats2bfloat162_rn(e[2], e[3]);
+      uint2 u; u.x = *reinterpret_cast<uint32_t*>(&lo); u.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(o) = u;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; j++) if (n + j < P.N) o[j] = __float2bfloat16_rn(e[j]);
+    }
+  } else {
+    float* o = (float*)P.out + idx;
+    if (wide && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+      float4 r = make_float4(e[0], e[1], e[2], e[3]);
+      if (EPI == 1) { const float4 old = __ldcg(reinterpret_cast<const float4*>(o)); r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w; }
+      *reinterpret_cast<float4*>(o) = r;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; j++)
+        if (n + j < P.N) o[j] = (EPI == 1) ? ld_fresh(o + j) + e[j] : e[j];
+    }
+  }
+}
+
 template <int BN, int EPI>
-__global__ void __launch_bounds__(TC_BM)
+__global__ void __launch_bounds__(128)
 gemm_tc_fixup_kernel(const SkParams P, int G) {
   pdl_trigger();
-  const int tile = blockIdx.x, m0 = blockIdx.y * 8;
-  const int first_c = sk_owner(tile * P.n_kb, G, P.total_kb);
+  const int c1 = blockIdx.x + 1;
+  const int b1 = sk_begin(c1, G, P.total_kb);
+  const int tile = b1 / P.n_kb;
+  if (b1 % P.n_kb == 0) return;                                       // CTA c1 begins with a tile of its own
+  if (c1 > 1 && sk_begin(c1 - 1, G, P.total_kb) > tile * P.n_kb) return;   // an earlier block has this tile
+  const int m = blockIdx.y * 4 + (threadIdx.x >> 5);
+  if (m >= P.M) return;
+  const int first_c = c1 - 1;
   const int last_c = sk_owner((tile + 1) * P.n_kb - 1, G, P.total_kb);
-  if (first_c == last_c) return;                   // whole tile: done in the first pass
+  const int col = (threadIdx.x & 31) * 4;
   pdl_wait();
-  const int row = threadIdx.x;
-  float v[8];
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c0 = first_c; c0 <= last_c; c0 += 8) {
+    float4 a[8];
 #pragma unroll
-  for (int j = 0; j < 8; j++) v[j] = 0.f;
-  for (int cc = first_c; cc <= last_c; cc++) {
-    const int slot = (tile == sk_begin(cc, G, P.total_kb) / P.n_kb) ? 0 : 1;
-    const float* src = P.scratch + ((size_t)(cc * 2 + slot) * BN + m0) * TC_BM + row;
-    float a[8];
+    for (int j = 0; j < 8; j++) {
+      const int cc = c0 + j;
+      if (cc <= last_c) {
+        const int slot = (sk_begin(cc, G, P.total_kb) / P.n_kb == tile) ? 0 : 1;
+        a[j] = __ldcg(reinterpret_cast<const float4*>(P.scratch + ((size_t)(cc * 2 + slot) * BN + m) * TC_BM + col));
+      } else {
+        a[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
 #pragma unroll
-    for (int j = 0; j < 8; j++) a[j] = (m0 + j < P.M) ? ld_fresh(src + (size_t)j * TC_BM) : 0.f;
-#pragma unroll
-    for (int j = 0; j < 8; j++) v[j] += a[j];
+    for (int j = 0; j < 8; j++) {
+      if (c0 + j <= last_c) { v.x += a[j].x; v.y += a[j].y; v.z += a[j].z; v.w += a[j].w; }
+    }
   }
-  sk_store<EPI, 8>(P, tile * TC_BM + row, m0, v);
+  fixup_store<EPI>(P, m, tile * TC_BM + col, v);
 }
 
 #ifndef SK_RING_16
@@ -579,7 +636,7 @@ static int launch_streamk(const CUtensorMap& mw, const CUtensorMap& mx, const Sk
     }                                                                                                       \
     int st = launch_pdl(kern, grid, TC_THREADS, smem, stream, mw, mx, P);                                   \
     if (st != 0 || !split_tiles) return st;                                                                 \
-    return launch_pdl(gemm_tc_fixup_kernel<BN, E>, dim3(P.tiles, (P.M + 7) / 8), TC_BM, 0, stream, P, grid); \
+    return launch_pdl(gemm_tc_fixup_kernel<BN, E>, dim3(grid - 1, (P.M + 3) / 4), 128, 0, stream, P, grid);    \
   }
   switch (epilogue) {
     case 0: SK_LAUNCH(0)

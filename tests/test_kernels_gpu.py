@@ -121,7 +121,7 @@ def test_gemm_skinny(M, N, K_):
 @pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (33, 48, 64), (64, 1000, 200), (100, 256, 4096), (300, 4096 + 16, 512),
                                      (2048, 2 * 177, 96), (129, 6144, 1024), (1, 128, 128), (17, 130, 72),
                                      (8, 4096, 4096), (5, 28672, 1024), (64, 4096 + 64, 14336), (16, 6144, 4096),
-                                     (40, 50000, 512), (8, 128256, 1024)])
+                                     (40, 50000, 512), (8, 128256, 1024), (9, 1002, 1096), (64, 260, 2048)])
 def test_gemm_tc(M, N, K_):
     from stratum_b200 import kernels as K
     rng = np.random.default_rng(M + N + K_)
