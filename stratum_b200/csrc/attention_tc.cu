@@ -9,11 +9,17 @@
 //
 //   warp 0      producer: Q once (3-D box: dims x heads of the group x tokens), then K and V tiles into a ring
 //   warp 1      one lane issues the MMAs:  S = Q K^T  (128 x 64, into one of two TMEM buffers) and, once the
-//               softmax warps have written P,  PV = P V  (128 x Hd, fresh every tile)
+//               softmax warps have written P,  O += P V  (128 x Hd, accumulated in TMEM over all tiles)
 //   warps 2-9   softmax, two threads per row (each owns half of the keys of a tile and half of the output
-//               dimensions): read S from TMEM, mask, running maximum in float32, exponentials, write P as
-//               bfloat16 into shared memory in the swizzled layout the MMA reads, then add PV into the output row
-//               kept in registers, rescaled when the maximum moves.  Nothing is rescaled inside TMEM.
+//               dimensions): read S from TMEM, mask, maximum in float32, exponentials, write P as bfloat16 into
+//               shared memory in the swizzled layout the MMA reads.
+//
+// The exponentials of a row are taken against a reference maximum that is only moved when the row's maximum has
+// grown by more than 2^8 beyond it: exp2(s - ref) then stays below 2^8, exactly representable scaling that the
+// final division by the row's sum (taken against the same reference) removes again.  Moving the reference means
+// multiplying the row of O in TMEM (tcgen05.ld, multiply, tcgen05.st); after the first tiles of a row this is
+// rare, so per tile a softmax thread touches S and P only, and its few registers let two CTAs share an SM: one
+// CTA's MMAs run under the other's softmax.
 //
 // V is used as stored, [key][dim]: as the B operand of P V its n index (dim) is the contiguous one
 // ("MN-major"), which the instruction takes directly; no transpose is made anywhere.
@@ -45,10 +51,9 @@ struct FaSmem {
   alignas(1024) bf16 q[FA_ROWS * HD];                 // [HD/64 blocks of 64 dims][128 rows][64]
   alignas(1024) bf16 k[FA_STAGES][FA_KEYS * HD];      // [HD/64][64 keys][64 dims]
   alignas(1024) bf16 v[FA_STAGES][FA_KEYS * HD];      // [HD/64][64 keys][64 dims]
-  alignas(1024) bf16 p[FA_ROWS * FA_KEYS];            // [128 rows][64 keys]
-  float l_half[FA_ROWS];                              // denominators of the second half of the keys
-  uint64_t q_full, k_full[FA_STAGES], v_full[FA_STAGES], kv_empty[FA_STAGES];
-  uint64_t s_full[2], s_empty[2], p_full, pv_full, pv_empty;
+  alignas(1024) bf16 p[FA_ROWS * FA_KEYS];            // [128 rows][64 keys]; at the end: the rows' two half sums
+  uint64_t q_full, k_full[FA_STAGES], v_full[FA_STAGES], k_empty[FA_STAGES], v_empty[FA_STAGES];
+  uint64_t s_full[2], s_empty[2], p_full, pv_full;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -62,31 +67,38 @@ __device__ __forceinline__ float fast_exp2(float x) {
 #define FA_FAIL(code) { atomicCAS(P.status, 0, code); S.abort_flag = 1; }
 
 template <int HD>
-__global__ void __launch_bounds__(FA_THREADS, 1)
+__global__ void __launch_bounds__(FA_THREADS, 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const FaParams P) {
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   using Smem = FaSmem<HD>;
-  Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  Smem& S = *reinterpret_cast<Smem*>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int DB = HD / 64;                           // blocks of 64 dims
-  constexpr uint32_t TMEM_COLS = 256;                   // S0 | S1 | PV (Hd columns)
+  constexpr uint32_t TMEM_COLS = 256;                   // S0 | S1 | O (Hd columns); two CTAs of an SM fill its 512
   constexpr uint32_t COL_PV = 128;
   pdl_trigger();
-  // heaviest tiles first: the last query tiles of a long prompt see the most keys
-  const int qb = gridDim.x - 1 - blockIdx.x;
-  const int kvh = blockIdx.y;
+  // the swizzled tiles need 1024-byte alignment, and there is no room to round the base up when two CTAs are to
+  // share an SM
+  if (smem_u32(smem_raw) & 1023) {
+    if (threadIdx.x == 0) atomicCAS(P.status, 0, 210);
+    return;
+  }
+  // heaviest tiles first, for all kv heads: the last query tiles of a long prompt see the most keys
+  const int qb = (int)(gridDim.x / P.n_kv) - 1 - (int)(blockIdx.x / P.n_kv);
+  const int kvh = blockIdx.x % P.n_kv;
   const int seq = P.qb_seq[qb];
   const int tok0 = P.qb_tok0[qb], ntok = P.qb_ntok[qb];
   volatile int* abort_flag = &S.abort_flag;
 
   if (threadIdx.x == 0) {
     mbar_init(&S.q_full, 1);
-    for (int s = 0; s < FA_STAGES; s++) { mbar_init(&S.k_full[s], 1); mbar_init(&S.v_full[s], 1); mbar_init(&S.kv_empty[s], 1); }
+    for (int s = 0; s < FA_STAGES; s++) {
+      mbar_init(&S.k_full[s], 1); mbar_init(&S.v_full[s], 1); mbar_init(&S.k_empty[s], 1); mbar_init(&S.v_empty[s], 1);
+    }
     for (int b = 0; b < 2; b++) { mbar_init(&S.s_full[b], 1); mbar_init(&S.s_empty[b], FA_SOFTMAX_WARPS); }
     mbar_init(&S.p_full, FA_SOFTMAX_WARPS);
     mbar_init(&S.pv_full, 1);
-    mbar_init(&S.pv_empty, FA_SOFTMAX_WARPS);
     S.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -115,15 +127,30 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       for (int db = 0; db < DB; db++)
         tma_load_3d(&map_q, S.q + db * FA_ROWS * 64, &S.q_full, db * 64, kvh * P.gs, tok0);
       const int* bt = P.block_table + (size_t)seq * P.bt_stride;
+      // K and V have rings of their own: a K tile is free again as soon as its scores are computed, a whole tile
+      // earlier than the V tile beside it, so the next K is already on its way while P V still runs.  One thread
+      // feeds both rings, polling (never suspended in a wait on one ring while the other has room).
       bool ok = true;
-      for (int j = 0; j < n_tiles && ok; j++) {
-        const int s = j % FA_STAGES;
-        if (!mbar_wait(&S.kv_empty[s], ((j / FA_STAGES) & 1) ^ 1, abort_flag)) { FA_FAIL(201); ok = false; break; }
-        const int row = (bt[lo_tile + j] * P.n_kv + kvh) * FA_KEYS;
-        mbar_expect_tx(&S.k_full[s], FA_KEYS * HD * sizeof(bf16));
-        for (int db = 0; db < DB; db++) tma_load_2d(&map_k, S.k[s] + db * FA_KEYS * 64, &S.k_full[s], db * 64, row);
-        mbar_expect_tx(&S.v_full[s], FA_KEYS * HD * sizeof(bf16));
-        for (int db = 0; db < DB; db++) tma_load_2d(&map_v, S.v[s] + db * FA_KEYS * 64, &S.v_full[s], db * 64, row);
+      int jk = 0, jv = 0;
+      uint32_t idle = 0;
+      while ((jk < n_tiles || jv < n_tiles) && ok) {
+        bool moved = false;
+        if (jk < n_tiles && mbar_test_wait(&S.k_empty[jk % FA_STAGES], ((jk / FA_STAGES) & 1) ^ 1)) {
+          const int s = jk % FA_STAGES;
+          const int row = (bt[lo_tile + jk] * P.n_kv + kvh) * FA_KEYS;
+          mbar_expect_tx(&S.k_full[s], FA_KEYS * HD * sizeof(bf16));
+          for (int db = 0; db < DB; db++) tma_load_2d(&map_k, S.k[s] + db * FA_KEYS * 64, &S.k_full[s], db * 64, row);
+          jk++; moved = true;
+        }
+        if (jv < n_tiles && mbar_test_wait(&S.v_empty[jv % FA_STAGES], ((jv / FA_STAGES) & 1) ^ 1)) {
+          const int s = jv % FA_STAGES;
+          const int row = (bt[lo_tile + jv] * P.n_kv + kvh) * FA_KEYS;
+          mbar_expect_tx(&S.v_full[s], FA_KEYS * HD * sizeof(bf16));
+          for (int db = 0; db < DB; db++) tma_load_2d(&map_v, S.v[s] + db * FA_KEYS * 64, &S.v_full[s], db * 64, row);
+          jv++; moved = true;
+        }
+        if (moved) { idle = 0; continue; }
+        if (++idle >= 64u * TC_SPIN_LIMIT || ((idle & 1023u) == 0 && *abort_flag)) { FA_FAIL(201); ok = false; }
       }
       if (!ok) {
         for (int i = 0; i < 2000; i++) __nanosleep(1000);   // let copies already issued land
@@ -149,6 +176,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             umma_bf16(tmem_base + b * FA_KEYS, smem_desc_sw128(q_addr + db * FA_ROWS * 128 + kk * 32),
                       smem_desc_sw128(k_addr + db * FA_KEYS * 128 + kk * 32), idesc_s, (db | kk) ? 1u : 0u);
         umma_commit(&S.s_full[b]);
+        umma_commit(&S.k_empty[s]);             // K of this tile has been read once these MMAs are done
         return true;
       };
       if (ok) ok = issue_scores(0);
@@ -157,15 +185,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const int s = j % FA_STAGES;
         if (!mbar_wait(&S.p_full, j & 1, abort_flag)) { FA_FAIL(205); ok = false; break; }
         if (!mbar_wait(&S.v_full[s], (j / FA_STAGES) & 1, abort_flag)) { FA_FAIL(206); ok = false; break; }
-        if (!mbar_wait(&S.pv_empty, (j & 1) ^ 1, abort_flag)) { FA_FAIL(207); ok = false; break; }
         tc_fence_after();
         const uint32_t p_addr = smem_u32(S.p), v_addr = smem_u32(S.v[s]);
 #pragma unroll
         for (int kk = 0; kk < 4; kk++)          // 16 keys a step: 32 bytes along a row of P, 16 rows of V
           umma_bf16(tmem_base + COL_PV, smem_desc_sw128(p_addr + kk * 32),
-                    smem_desc_sw128_mn(v_addr + kk * 16 * 128, FA_KEYS * 128), idesc_pv, kk ? 1u : 0u);
+                    smem_desc_sw128_mn(v_addr + kk * 16 * 128, FA_KEYS * 128), idesc_pv, (j | kk) ? 1u : 0u);
         umma_commit(&S.pv_full);
-        umma_commit(&S.kv_empty[s]);            // K and V of this tile have been read
+        umma_commit(&S.v_empty[s]);             // V of this tile has been read
       }
     }
   } else if (n_tiles > 0) {
@@ -179,45 +206,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int lo = (P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     constexpr int OD = HD / 2;                           // output dims per thread
-    float o[OD];
-#pragma unroll
-    for (int i = 0; i < OD; i++) o[i] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    const uint32_t o_addr = lane_addr + COL_PV + half * OD;
+    float m_ref = -INFINITY, l = 0.f;                    // reference maximum (scaled, log2 domain); sum of this half
     bool ok = true;
-
-    auto add_pv = [&](int j) -> bool {                   // o += PV of tile j
-      if (!mbar_wait(&S.pv_full, j & 1, abort_flag)) { if (lane == 0) FA_FAIL(208); return false; }
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < OD; c += 32) {
-        float pv[32];
-        tmem_ld32f(lane_addr + COL_PV + half * OD + c, pv);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i++) o[c + i] += pv[i];
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&S.pv_empty);
-      return true;
-    };
 
     for (int j = 0; j < n_tiles; j++) {
       const int b = j & 1;
       if (!mbar_wait(&S.s_full[b], (j >> 1) & 1, abort_flag)) { if (lane == 0) FA_FAIL(209); ok = false; break; }
       tc_fence_after();
-      float s[FA_KEYS];
-      {
-        float a[32];
-        tmem_ld32f(lane_addr + b * FA_KEYS, a);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i++) s[i] = a[i];
-        tmem_ld32f(lane_addr + b * FA_KEYS + 32, a);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i++) s[32 + i] = a[i];
-      }
+      float s[32], t[32];                                // this thread's half of the keys, and the other half
+      tmem_ld32f(lane_addr + b * FA_KEYS + half * 32, s);
+      tmem_ld32f(lane_addr + b * FA_KEYS + (half ^ 1) * 32, t);
+      tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.s_empty[b]);
@@ -229,44 +229,60 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // everything else a thread does per tile)
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (needs_mask) {
+        const int ks = key0 + half * 32, kt = key0 + (half ^ 1) * 32;
 #pragma unroll
-        for (int i = 0; i < FA_KEYS; i++) {
-          const int key = key0 + i;
-          s[i] = (valid && key <= pos && key >= lo) ? s[i] : -INFINITY;
-          mx[i & 3] = fmaxf(mx[i & 3], s[i]);
+        for (int i = 0; i < 32; i++) {
+          s[i] = (valid && ks + i <= pos && ks + i >= lo) ? s[i] : -INFINITY;
+          t[i] = (valid && kt + i <= pos && kt + i >= lo) ? t[i] : -INFINITY;
+          mx[i & 3] = fmaxf(mx[i & 3], fmaxf(s[i], t[i]));
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < FA_KEYS; i++) mx[i & 3] = fmaxf(mx[i & 3], s[i]);
+        for (int i = 0; i < 32; i++) mx[i & 3] = fmaxf(mx[i & 3], fmaxf(s[i], t[i]));
       }
       float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       tile_max *= P.scale_log2;                          // scale > 0: the maximum of the scaled scores
-      const float m_new = fmaxf(m, tile_max);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float corr = fast_exp2(m - m_use);           // exp2(-inf) = 0 at the first keys
-      // this thread's half of the keys: probabilities exp2(s * scale - m), their sum, and P in the layout the
-      // MMA reads
+      // the reference moves only when the row's maximum has outgrown it by more than 8 (a factor 256); both
+      // threads of a row see the same numbers and decide alike
+      const bool grow = tile_max > m_ref + 8.0f;
+      const float corr = grow ? fast_exp2(m_ref - tile_max) : 1.0f;     // exp2(-inf) = 0 at a row's first keys
+      if (grow) m_ref = tile_max;
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+      // probabilities exp2(s * scale - ref) of this thread's keys, their sum, and P in the layout the MMA reads
       uint32_t packed[16];
       float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
       for (int i = 0; i < 32; i += 2) {
-        // (both indices spelled out so that s[] stays in registers)
-        const float p0 = fast_exp2(fmaf(half ? s[32 + i] : s[i], P.scale_log2, -m_use));
-        const float p1 = fast_exp2(fmaf(half ? s[33 + i] : s[i + 1], P.scale_log2, -m_use));
-        __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
-        // the value sum runs over the rounded probabilities; the denominator does too, so rows sum to one
-        sum0 += __bfloat162float(pr.x);
-        sum1 += __bfloat162float(pr.y);
-        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&pr);
+        const float p0 = fast_exp2(fmaf(s[i], P.scale_log2, -m_use));
+        const float p1 = fast_exp2(fmaf(s[i + 1], P.scale_log2, -m_use));
+        // to bfloat16 by dropping the low mantissa bits (one byte permute for two values; the conversion
+        // instruction shares the exponential's pipe, which is the busiest one here).  The probabilities are
+        // positive, so every one comes out low by a factor in (1 - 2^-7, 1]; the sums below run over the same
+        // shortened values, so the common part of that factor divides out and what stays is as wide as
+        // round-to-nearest's error.
+        const uint32_t u = __byte_perm(__float_as_uint(p0), __float_as_uint(p1), 0x7632);
+        sum0 += __uint_as_float(u << 16);
+        sum1 += __uint_as_float(u & 0xffff0000u);
+        packed[i >> 1] = u;
       }
-      const float sum = sum0 + sum1;
-      if (j > 0) { if (!add_pv(j - 1)) { ok = false; break; } }   // also: P of tile j-1 has been read
-      if (__any_sync(0xffffffffu, corr != 1.0f)) {        // the maximum moved for some row of this warp
+      if (j > 0) {
+        // P V of the tile before has read P and has been added into O
+        if (!mbar_wait(&S.pv_full, (j - 1) & 1, abort_flag)) { if (lane == 0) FA_FAIL(208); ok = false; break; }
+        if (__any_sync(0xffffffffu, grow)) {             // some row of this warp moves its reference: rescale O
+          tc_fence_after();
 #pragma unroll
-        for (int i = 0; i < OD; i++) o[i] *= corr;
+          for (int c = 0; c < OD; c += 32) {
+            uint32_t r[32];
+            tmem_ld32(o_addr + c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+            tmem_st32(o_addr + c, r);
+          }
+          tmem_st_wait();
+        }
       }
-      l = l * corr + sum;
-      m = m_new;
+      l = l * corr + (sum0 + sum1);
       {
         uint8_t* prow = reinterpret_cast<uint8_t*>(S.p) + row * 128;
 #pragma unroll
@@ -277,29 +293,38 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         }
       }
       fence_async_shared();
+      tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.p_full);
     }
-    if (ok) ok = add_pv(n_tiles - 1);
-    // the two halves of the keys kept separate denominators: add them (named barrier among the softmax warps;
-    // reached by all of them or, after a failed wait, by none past this point)
-    if (half == 1) S.l_half[row] = l;
+    if (ok && !mbar_wait(&S.pv_full, (n_tiles - 1) & 1, abort_flag)) { if (lane == 0) FA_FAIL(208); ok = false; }
+    tc_fence_after();
+    // the two halves of the keys kept separate sums: add them (P is no longer read; named barrier among the
+    // softmax warps, reached by all of them)
+    float* l_buf = reinterpret_cast<float*>(S.p);
+    l_buf[half * FA_ROWS + row] = l;
     asm volatile("bar.sync 1, %0;" ::"n"(FA_SOFTMAX_WARPS * 32) : "memory");
-    if (half == 0) S.l_half[row] += l;
-    asm volatile("bar.sync 1, %0;" ::"n"(FA_SOFTMAX_WARPS * 32) : "memory");
-    if (ok && !S.abort_flag && valid) {
-      const float inv = 1.0f / S.l_half[row];
-      bf16* op = P.out + (size_t)(tok0 + tok) * P.ldo + (size_t)(kvh * P.gs + head) * HD + half * OD;
+    if (ok && !S.abort_flag) {
+      const float inv = 1.0f / (l_buf[row] + l_buf[FA_ROWS + row]);
+      bf16* op = P.out + (size_t)(tok0 + (valid ? tok : 0)) * P.ldo + (size_t)(kvh * P.gs + head) * HD + half * OD;
 #pragma unroll
-      for (int c = 0; c < OD; c += 8) {
-        uint4 w;
-        __nv_bfloat162 a0 = __floats2bfloat162_rn(o[c] * inv, o[c + 1] * inv);
-        __nv_bfloat162 a1 = __floats2bfloat162_rn(o[c + 2] * inv, o[c + 3] * inv);
-        __nv_bfloat162 a2 = __floats2bfloat162_rn(o[c + 4] * inv, o[c + 5] * inv);
-        __nv_bfloat162 a3 = __floats2bfloat162_rn(o[c + 6] * inv, o[c + 7] * inv);
-        w.x = *reinterpret_cast<uint32_t*>(&a0); w.y = *reinterpret_cast<uint32_t*>(&a1);
-        w.z = *reinterpret_cast<uint32_t*>(&a2); w.w = *reinterpret_cast<uint32_t*>(&a3);
-        *reinterpret_cast<uint4*>(op + c) = w;
+      for (int c = 0; c < OD; c += 32) {
+        float o[32];
+        tmem_ld32f(o_addr + c, o);                       // (all lanes take part in the load; only valid rows store)
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            __nv_bfloat162 a0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv);
+            __nv_bfloat162 a1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
+            __nv_bfloat162 a2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv);
+            __nv_bfloat162 a3 = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
+            w.x = *reinterpret_cast<uint32_t*>(&a0); w.y = *reinterpret_cast<uint32_t*>(&a1);
+            w.z = *reinterpret_cast<uint32_t*>(&a2); w.w = *reinterpret_cast<uint32_t*>(&a3);
+            *reinterpret_cast<uint4*>(op + c + i) = w;
+          }
+        }
       }
     }
   }
@@ -326,7 +351,7 @@ static int make_map_nd(CUtensorMap* map, const void* base, int rank, const cuuin
 template <int HD>
 static int launch_attention_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& P,
                                int n_qblocks, cudaStream_t stream) {
-  const size_t smem = sizeof(FaSmem<HD>) + 1024;
+  const size_t smem = sizeof(FaSmem<HD>);
   auto kern = attention_tc_kernel<HD>;
   static bool configured = false;
   if (!configured) {
@@ -334,7 +359,7 @@ static int launch_attention_tc(const CUtensorMap& mq, const CUtensorMap& mk, con
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return launch_pdl(kern, dim3(n_qblocks, P.n_kv), FA_THREADS, smem, stream, mq, mk, mv, P);
+  return launch_pdl(kern, dim3((unsigned)n_qblocks * P.n_kv), FA_THREADS, smem, stream, mq, mk, mv, P);
 }
 
 // q: bf16 [tokens][ldq], query heads first (n_q * head_dim values per row are used).
@@ -353,7 +378,7 @@ STRATUM_EXPORT int stratum_attention_tc(const void* q, int ldq, const void* k_ca
   if (gs > FA_ROWS || FA_ROWS % gs != 0) return STRATUM_ERR_SHAPE;
   if (ldq % 8 != 0 || ldo % 8 != 0 || !status || !qb_seq || !qb_tok0 || !qb_ntok) return STRATUM_ERR_ALIGN;
   if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15) return STRATUM_ERR_ALIGN;
-  if (n_kv > 65535) return STRATUM_ERR_LIMIT;
+  if ((long long)n_qblocks * n_kv > 0x7fffffffLL) return STRATUM_ERR_LIMIT;
   const int R = FA_ROWS / gs;
   CUtensorMap mq, mk, mv;
   int st;
