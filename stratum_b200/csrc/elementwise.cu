@@ -106,15 +106,27 @@ __global__ void rmsnorm_vec_kernel(const float* __restrict__ x, const float* __r
   }
 }
 
+template <typename T, int VPT>
+static int launch_rmsnorm_vec(const float* x, const float* gain, const int* rows, T* out, int n_rows, int hidden,
+                              float eps, cudaStream_t stream) {
+  const int threads = (((hidden / 4 + VPT - 1) / VPT + 31) / 32) * 32;
+  return launch_pdl(rmsnorm_vec_kernel<T, VPT>, n_rows, threads, 0, stream, x, gain, rows, out, hidden, eps);
+}
+
 template <typename T>
 static int launch_rmsnorm(const float* x, const float* gain, const int* rows, T* out, int n_rows, int hidden,
                           float eps, cudaStream_t stream) {
   const bool vec = hidden % 4 == 0 && ((((uintptr_t)x | (uintptr_t)gain | (uintptr_t)out) & 15) == 0);
-  if (vec && hidden <= 4 * 1024)
-    return launch_pdl(rmsnorm_vec_kernel<T, 1>, n_rows, ((hidden / 4 + 31) / 32) * 32, 0, stream, x, gain, rows, out,
-                      hidden, eps);
-  if (vec && hidden <= 4 * 4 * 1024)
-    return launch_pdl(rmsnorm_vec_kernel<T, 4>, n_rows, 1024, 0, stream, x, gain, rows, out, hidden, eps);
+  if (vec && hidden <= 4 * 4 * 1024) {
+    // few rows (decode steps): as many threads per row as it has float4s, the shortest path through one row;
+    // many rows (prompts): blocks of about 128 threads, several of which share an SM and hide each other's waits
+    const int n4 = hidden / 4;
+    if (n_rows < 256 && n4 <= 1024) return launch_rmsnorm_vec<T, 1>(x, gain, rows, out, n_rows, hidden, eps, stream);
+    if (n4 <= 256) return launch_rmsnorm_vec<T, 1>(x, gain, rows, out, n_rows, hidden, eps, stream);
+    if (n4 <= 512) return launch_rmsnorm_vec<T, 2>(x, gain, rows, out, n_rows, hidden, eps, stream);
+    if (n4 <= 1024 && n_rows >= 256) return launch_rmsnorm_vec<T, 8>(x, gain, rows, out, n_rows, hidden, eps, stream);
+    return launch_rmsnorm_vec<T, 4>(x, gain, rows, out, n_rows, hidden, eps, stream);
+  }
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   return launch_pdl(rmsnorm_kernel<T>, n_rows, threads, 0, stream, x, gain, rows, out, hidden, eps);
 }
@@ -217,6 +229,82 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ t
   }
 }
 
+// The same for prompts in bfloat16 when every dimension of a head is rotated: one block per token; the sines and
+// cosines of the token's angles are evaluated once (not once per head) into shared memory, then every thread moves
+// 16 bytes at a time: 8 pairs (k, k + n_pairs) from two loads, or 4 pairs (2k, 2k+1) from one when interleaved;
+// the v heads are copied.  Needs head_dim % 16 == 0 and 2 * n_pairs == head_dim.
+template <bool INTERLEAVED>
+__global__ void __launch_bounds__(256)
+rope_store_prompt_kernel(bf16* __restrict__ qkv, const int* __restrict__ token_pos,
+                         const int* __restrict__ token_seq, const int* __restrict__ block_table, int bt_stride,
+                         const float* __restrict__ inv_freq, int n_pairs, float mscale, bf16* __restrict__ k_cache,
+                         bf16* __restrict__ v_cache, int n_q, int n_kv, int head_dim, int page_tokens,
+                         int write_cache) {
+  extern __shared__ float2 cs[];                 // [n_pairs] (cos, sin) * mscale
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int seq = token_seq[t];
+  if (seq < 0) return;
+  const int pos = token_pos[t];
+  for (int k = threadIdx.x; k < n_pairs; k += blockDim.x) {
+    float sn, c;
+    sincosf((float)pos * inv_freq[k], &sn, &c);
+    cs[k] = make_float2(c * mscale, sn * mscale);
+  }
+  const int page = write_cache ? block_table[(size_t)seq * bt_stride + pos / page_tokens] : 0;
+  const size_t cache_row = ((size_t)page * n_kv * page_tokens + (pos % page_tokens)) * (size_t)head_dim;
+  const size_t kv_stride = (size_t)page_tokens * head_dim;
+  bf16* row = qkv + (size_t)t * ((size_t)(n_q + 2 * n_kv) * head_dim);
+  __syncthreads();
+  pdl_wait();
+  const int rot_heads = n_q + (write_cache ? n_kv : 0);
+  if (INTERLEAVED) {
+    const int per_head = head_dim / 8;           // 16-byte pieces of a head: 4 pairs each
+    for (int it = threadIdx.x; it < rot_heads * per_head; it += blockDim.x) {
+      const int h = it / per_head, c8 = it % per_head;
+      bf16* src = row + (size_t)h * head_dim + 8 * c8;
+      bf16* dst = h < n_q ? src : k_cache + cache_row + (size_t)(h - n_q) * kv_stride + 8 * c8;
+      uint4 w = __ldcg(reinterpret_cast<const uint4*>(src));
+      __nv_bfloat162* e = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const float2 f = cs[4 * c8 + j];
+        const float x0 = __bfloat162float(e[j].x), x1 = __bfloat162float(e[j].y);
+        e[j] = __floats2bfloat162_rn(x0 * f.x - x1 * f.y, x0 * f.y + x1 * f.x);
+      }
+      *reinterpret_cast<uint4*>(dst) = w;
+    }
+  } else {
+    const int per_head = n_pairs / 8;            // pieces of 8 pairs: dims 8c..8c+7 and n_pairs + 8c..
+    for (int it = threadIdx.x; it < rot_heads * per_head; it += blockDim.x) {
+      const int h = it / per_head, c8 = it % per_head;
+      bf16* src = row + (size_t)h * head_dim + 8 * c8;
+      bf16* dst = h < n_q ? src : k_cache + cache_row + (size_t)(h - n_q) * kv_stride + 8 * c8;
+      uint4 lo = __ldcg(reinterpret_cast<const uint4*>(src));
+      uint4 hi = __ldcg(reinterpret_cast<const uint4*>(src + n_pairs));
+      bf16* a = reinterpret_cast<bf16*>(&lo);
+      bf16* b = reinterpret_cast<bf16*>(&hi);
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const float2 f = cs[8 * c8 + j];
+        const float x0 = __bfloat162float(a[j]), x1 = __bfloat162float(b[j]);
+        a[j] = __float2bfloat16_rn(x0 * f.x - x1 * f.y);
+        b[j] = __float2bfloat16_rn(x0 * f.y + x1 * f.x);
+      }
+      *reinterpret_cast<uint4*>(dst) = lo;
+      *reinterpret_cast<uint4*>(dst + n_pairs) = hi;
+    }
+  }
+  if (write_cache) {
+    const int per_head = head_dim / 8;
+    for (int it = threadIdx.x; it < n_kv * per_head; it += blockDim.x) {
+      const int h = it / per_head, c8 = it % per_head;
+      const uint4 w = __ldcg(reinterpret_cast<const uint4*>(row + (size_t)(n_q + n_kv + h) * head_dim + 8 * c8));
+      *reinterpret_cast<uint4*>(v_cache + cache_row + (size_t)h * kv_stride + 8 * c8) = w;
+    }
+  }
+}
+
 STRATUM_EXPORT int stratum_rope_store(void* qkv, int dtype, const int* token_pos, const int* token_seq,
                                       const int* block_table, int bt_stride, const float* inv_freq, int n_pairs,
                                       int interleaved, float mscale, void* k_cache, void* v_cache, int n_tokens,
@@ -225,6 +313,17 @@ STRATUM_EXPORT int stratum_rope_store(void* qkv, int dtype, const int* token_pos
   if (n_tokens <= 0) return 0;
   if (head_dim % 2 != 0 || 2 * n_pairs > head_dim || n_pairs < 0 || head_dim > 2048) return STRATUM_ERR_SHAPE;
   if (n_q + 2 * n_kv > 65535) return STRATUM_ERR_LIMIT;
+  if (dtype == STRATUM_DT_BF16 && n_tokens >= 64 && head_dim % 16 == 0 && 2 * n_pairs == head_dim &&
+      ((((uintptr_t)qkv | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15) == 0)) {
+    const size_t smem = (size_t)n_pairs * sizeof(float2);
+    if (interleaved)
+      return launch_pdl(rope_store_prompt_kernel<true>, n_tokens, 256, smem, stream, (bf16*)qkv, token_pos, token_seq,
+                        block_table, bt_stride, inv_freq, n_pairs, mscale, (bf16*)k_cache, (bf16*)v_cache, n_q, n_kv,
+                        head_dim, page_tokens, write_cache);
+    return launch_pdl(rope_store_prompt_kernel<false>, n_tokens, 256, smem, stream, (bf16*)qkv, token_pos, token_seq,
+                      block_table, bt_stride, inv_freq, n_pairs, mscale, (bf16*)k_cache, (bf16*)v_cache, n_q, n_kv,
+                      head_dim, page_tokens, write_cache);
+  }
   const int slots = ((head_dim / 2 + 31) / 32) * 32;
   const int heads = n_q + 2 * n_kv;
   int per_block = n_tokens >= 64 ? 256 / slots : 1;

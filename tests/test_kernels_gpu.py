@@ -41,6 +41,22 @@ def test_rmsnorm(dtype, hidden):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden", [1024, 1544, 4096, 8192])
+def test_rmsnorm_many_rows(dtype, hidden):
+    """Prompts take other block shapes than decode steps (more values per thread)."""
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(hidden + 1)
+    x = dev(rng.standard_normal((300, hidden)) * 2.0)
+    gain = dev(rng.random(hidden) + 0.5)
+    out = torch.empty(300, hidden, dtype=DT[dtype], device="cuda")
+    K.rmsnorm(x, gain, 1e-6, out)
+    assert rel_err(as64(out), P.rms_norm(as64(x), as64(gain), 1e-6)) < (2e-6 if dtype == "float32" else 5e-3)
+    few = torch.empty(5, hidden, dtype=DT[dtype], device="cuda")
+    K.rmsnorm(x[:5], gain, 1e-6, few)
+    assert rel_err(as64(few), as64(out[:5])) < (1e-6 if dtype == "float32" else 5e-3)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_embed_gather(dtype):
     from stratum_b200 import kernels as K
     rng = np.random.default_rng(1)
@@ -209,6 +225,48 @@ def test_rope_store_rotates_and_lands_in_the_right_rows(dtype, interleaved):
     for pg, r in written:
         mask[pg, r] = False
     assert float(kc.float().abs().sum(dim=(1, 3)).cpu()[mask].sum()) == 0.0            # nothing else was touched
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("n_q,n_kv,hd", [(8, 2, 128), (3, 3, 48), (5, 1, 16)])
+def test_rope_store_prompt_kernel(interleaved, n_q, n_kv, hd):
+    """Prompts of 64 tokens or more with fully rotated heads take the 16-byte kernel; a continuation lands beside
+    what the cache already holds, and the same tokens one by one give the same rows up to rounding."""
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(hd + n_q)
+    n0, n1 = 70, 90                                                   # sequence 0 continues at 50; sequence 1 starts
+    pos = list(range(50, 50 + n0)) + list(range(n1))
+    seq = [0] * n0 + [1] * n1
+    table = np.array([[4, 1], [0, 5]], dtype=np.int32)
+    T = n0 + n1
+    qkv = dev(rng.standard_normal((T, (n_q + 2 * n_kv) * hd)), torch.bfloat16)
+    before = as64(qkv)
+    inv = P.rope_inv_freq(hd, 500000.0).astype(np.float32)
+    kc, vc = _paged(rng, 6, n_kv, hd, "bfloat16")
+    single = qkv.clone()
+    kc1, vc1 = _paged(rng, 6, n_kv, hd, "bfloat16")
+    K.rope_store(qkv, dev(pos, torch.int32), dev(seq, torch.int32), dev(table, torch.int32), dev(inv), interleaved,
+                 1.0, kc, vc, n_q, n_kv, hd, 64, True)
+    for t in range(0, T, 40):                                         # fewer than 64 tokens: the general kernel
+        K.rope_store(single[t:t + 40], dev(pos[t:t + 40], torch.int32), dev(seq[t:t + 40], torch.int32),
+                     dev(table, torch.int32), dev(inv), interleaved, 1.0, kc1, vc1, n_q, n_kv, hd, 64, True)
+    heads = before.reshape(T, n_q + 2 * n_kv, hd)
+    q_ref = P.apply_rope(heads[:, :n_q], np.array(pos), inv.astype(np.float64), interleaved)
+    k_ref = P.apply_rope(heads[:, n_q:n_q + n_kv], np.array(pos), inv.astype(np.float64), interleaved)
+    assert rel_err(as64(qkv).reshape(T, -1, hd)[:, :n_q], q_ref) < 5e-3
+    assert np.array_equal(as64(qkv).reshape(T, -1, hd)[:, n_q:], heads[:, n_q:])
+    for t in range(T):
+        page = table[seq[t], pos[t] // 64]
+        assert rel_err(as64(kc[page, :, pos[t] % 64]), k_ref[t]) < 5e-3
+        assert np.array_equal(as64(vc[page, :, pos[t] % 64]), heads[t, n_q + n_kv:])
+    assert rel_err(as64(qkv), as64(single)) < 5e-3 and rel_err(as64(kc), as64(kc1)) < 5e-3
+    assert torch.equal(vc, vc1)
+    # rows nobody wrote stay zero: sequence 0 holds positions 50..119, sequence 1 0..89
+    untouched = kc.clone()
+    for s_, lo, hi in ((0, 50, 120), (1, 0, 90)):
+        for p_ in range(lo, hi):
+            untouched[table[s_, p_ // 64], :, p_ % 64] = 0
+    assert float(untouched.float().abs().sum()) == 0.0
 
 
 def _attention_case(rng, lens_before, n_new, n_q, n_kv, hd, dtype, window=0, spike=None):
