@@ -14,8 +14,8 @@
 //            apply SwiGLU to column pairs.  Two accumulators (2 x BN columns of TMEM) let the
 //            epilogue of one tile overlap the k-loop of the next.
 //
-// With SWAP the roles of x and W are exchanged (the accumulator holds y^T: 128 weight rows by up
-// to 64 rows of x); that form serves decode steps with more rows than the streaming kernel takes.
+// Tiles that would form a last, partly filled wave are cut along k and shared by all CTAs (see TcSchedule).
+// Up to 64 rows of x take the stream-K form further down, with the roles of x and W exchanged.
 //
 // Every wait on an mbarrier is bounded.  If one runs out, the kernel records where in a status
 // word, tells its other warps through shared memory, lets copies in flight land, frees its tensor
@@ -32,6 +32,8 @@ struct TcParams {
   int* status;        // 0, or a code of where a wait ran out
   int M, N, K;        // logical sizes of y = x W^T: x [M][K], W [N][K]
   int ldo;
+  int split;          // 1: the tiles left over after the full waves are cut along k and shared by all CTAs
+  float* scratch;     // [gridDim.x][2][BN][128] float32: up to two partial tiles per CTA (split only)
 };
 
 template <int BN, int STAGES>
@@ -43,9 +45,173 @@ struct TcSmem {
   int abort_flag;
 };
 
+// Output row m, columns col0 .. col0 + CW - 1 (contiguous in memory): bias, then the epilogue.
 // EPI: 0 store bf16, 1 add into float32, 2 store float32, 3 SwiGLU pairs -> bf16.
-// SWAP = false: A tiles come from x (rows m), B tiles from W (rows n).  SWAP = true: A from W, B from x.
-template <int BN, int STAGES, int EPI, bool SWAP>
+template <int EPI, int CW>
+__device__ __forceinline__ void tc_store_chunk(const TcParams& P, int m, int col0, float (&v)[CW]) {
+  if (P.bias) {
+#pragma unroll
+    for (int j = 0; j < CW; j++)
+      if (col0 + j < P.N) v[j] += P.bias[col0 + j];
+  }
+  const bool whole = col0 + CW <= P.N;
+  if (EPI == 3) {
+    bf16* o = (bf16*)P.out + (size_t)m * P.ldo + (col0 >> 1);
+    uint32_t packed[CW / 4];
+#pragma unroll
+    for (int j = 0; j < CW; j += 4) {
+      float a[2];
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        const float gate = __bfloat162float(__float2bfloat16_rn(v[j + 2 * e]));
+        const float up = __bfloat162float(__float2bfloat16_rn(v[j + 2 * e + 1]));
+        a[e] = gate / (1.0f + __expf(-gate)) * up;
+      }
+      __nv_bfloat162 pr = __floats2bfloat162_rn(a[0], a[1]);
+      packed[j / 4] = *reinterpret_cast<uint32_t*>(&pr);
+    }
+    if (whole && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+      for (int q = 0; q < CW / 16; q++)
+        reinterpret_cast<uint4*>(o)[q] = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < CW; j += 2)
+        if (col0 + j + 1 < P.N) {
+          const __nv_bfloat162 pr = *reinterpret_cast<__nv_bfloat162*>(&packed[j / 4]);
+          o[j >> 1] = (j & 2) ? pr.y : pr.x;
+        }
+    }
+  } else if (EPI == 0) {
+    bf16* o = (bf16*)P.out + (size_t)m * P.ldo + col0;
+    if (whole && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+      for (int q = 0; q < CW / 8; q++) {
+        uint32_t w4[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+          __nv_bfloat162 pr = __floats2bfloat162_rn(v[8 * q + 2 * e], v[8 * q + 2 * e + 1]);
+          w4[e] = *reinterpret_cast<uint32_t*>(&pr);
+        }
+        reinterpret_cast<uint4*>(o)[q] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < CW; j++)
+        if (col0 + j < P.N) o[j] = __float2bfloat16_rn(v[j]);
+    }
+  } else {
+    float* o = (float*)P.out + (size_t)m * P.ldo + col0;
+    if (whole && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+      for (int q = 0; q < CW / 4; q++) {
+        float4 w4 = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        if (EPI == 1) {
+          const float4 old = ld_fresh(reinterpret_cast<const float4*>(o) + q);
+          w4.x += old.x; w4.y += old.y; w4.z += old.z; w4.w += old.w;
+        }
+        reinterpret_cast<float4*>(o)[q] = w4;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < CW; j++)
+        if (col0 + j < P.N) o[j] = (EPI == 1) ? ld_fresh(o + j) + v[j] : v[j];
+    }
+  }
+}
+
+// Output row m, columns n .. n+3 (four neighbours of one row): bias, then the epilogue (PT: TcParams or SkParams).
+template <int EPI, typename PT>
+__device__ __forceinline__ void fixup_store(const PT& P, int m, int n, float4 v) {
+  float e[4] = {v.x, v.y, v.z, v.w};
+  if (P.bias) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) if (n + j < P.N) e[j] += P.bias[n + j];
+  }
+  if (EPI == 3) {                                   // (gate, up) pairs: n even
+    bf16* o = (bf16*)P.out + (size_t)m * P.ldo + (n >> 1);
+#pragma unroll
+    for (int j = 0; j < 4; j += 2) {
+      if (n + j + 1 < P.N) {
+        const float g = __bfloat162float(__float2bfloat16_rn(e[j])), u = __bfloat162float(__float2bfloat16_rn(e[j + 1]));
+        o[j >> 1] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
+      }
+    }
+    return;
+  }
+  const size_t idx = (size_t)m * P.ldo + n;
+  const bool wide = (n + 3 < P.N) && ((idx & 3) == 0);
+  if (EPI == 0) {
+    bf16* o = (bf16*)P.out + idx;
+    if (wide && ((reinterpret_cast<uintptr_t>(o) & 7) == 0)) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(e[0], e[1]), hi = __floats2bfloat162_rn(e[2], e[3]);
+      uint2 u; u.x = *reinterpret_cast<uint32_t*>(&lo); u.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(o) = u;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; j++) if (n + j < P.N) o[j] = __float2bfloat16_rn(e[j]);
+    }
+  } else {
+    float* o = (float*)P.out + idx;
+    if (wide && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+      float4 r = make_float4(e[0], e[1], e[2], e[3]);
+      if (EPI == 1) { const float4 old = __ldcg(reinterpret_cast<const float4*>(o)); r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w; }
+      *reinterpret_cast<float4*>(o) = r;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; j++)
+        if (n + j < P.N) o[j] = (EPI == 1) ? ld_fresh(o + j) + e[j] : e[j];
+    }
+  }
+}
+
+// The work of one CTA as a list of items (tile, k-blocks [kb0, kb1)), the same list for its three roles.
+//
+// Whole tiles first: blockIdx.x, blockIdx.x + G, ...  Consecutive CTAs take consecutive x tiles of the same W
+// tile, so that a wave shares W in L2.  With `split`, the R = n_tiles % G tiles that would form a last, partly
+// empty wave are not given to R of the CTAs: their R * n_kb k-blocks are shared evenly, CTA c taking the stretch
+// [c U / G, (c+1) U / G) of them, which is the end of one tile and/or the beginning of the next (or a whole tile).
+// A piece that is not a whole tile is written to scratch as float32 partial sums (slot 0: the tile the stretch
+// begins in; slot 1: the next), and a second kernel adds the pieces of each tile in the order of k and runs the
+// epilogue.  No CTA waits for another.  The split depends on the shapes and the grid only: results are the same
+// from run to run.
+struct TcSchedule {
+  int n_tiles, n_kb, G, c;
+  int R, U, u0, u1, n_seg, n_full, n_whole;
+  __device__ __forceinline__ void init(int n_tiles_, int n_kb_, int split, int G_, int c_) {
+    n_tiles = n_tiles_; n_kb = n_kb_; G = G_; c = c_;
+    R = split ? n_tiles % G : 0;
+    n_full = n_tiles - R;
+    n_whole = (n_full > c) ? (n_full - c + G - 1) / G : 0;       // whole tiles of this CTA
+    U = R * n_kb;
+    u0 = (int)((long long)c * U / G);
+    u1 = (int)((long long)(c + 1) * U / G);
+    n_seg = (u1 > u0) ? ((u1 - 1) / n_kb - u0 / n_kb + 1) : 0;
+  }
+  __device__ __forceinline__ bool item(int i, int& tile, int& kb0, int& kb1, int& slot) const {
+    if (i < n_whole) {
+      tile = c + i * G; kb0 = 0; kb1 = n_kb; slot = -1;
+      return true;
+    }
+    const int j = i - n_whole;
+    if (j >= n_seg) return false;
+    const int r = u0 / n_kb + j;
+    kb0 = (j == 0) ? u0 - r * n_kb : 0;
+    kb1 = min(n_kb, u1 - r * n_kb);
+    tile = n_full + r;
+    slot = (kb0 == 0 && kb1 == n_kb) ? -1 : (j == 0 ? 0 : 1);
+    return true;
+  }
+};
+__device__ __forceinline__ int tc_begin(int c, int G, int U) { return (int)((long long)c * U / G); }
+__device__ __forceinline__ int tc_owner(int u, int G, int U) {
+  int o = (int)(((long long)u * G) / U);
+  while (o + 1 < G && tc_begin(o + 1, G, U) <= u) o++;
+  while (o > 0 && tc_begin(o, G, U) > u) o--;
+  return o;
+}
+
+template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const TcParams P) {
@@ -57,10 +223,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;      // a power of two >= 32
   constexpr uint32_t STAGE_BYTES = (TC_BM + BN) * TC_BK * sizeof(bf16);
 
-  const int rows_a = SWAP ? P.N : P.M, rows_b = SWAP ? P.M : P.N;
-  const int tiles_a = (rows_a + TC_BM - 1) / TC_BM, tiles_b = (rows_b + BN - 1) / BN;
-  const int n_tiles = tiles_a * tiles_b;
-  const int n_kb = (P.K + TC_BK - 1) / TC_BK;
+  const int tiles_a = (P.M + TC_BM - 1) / TC_BM, tiles_b = (P.N + BN - 1) / BN;
+  TcSchedule sched;
+  sched.init(tiles_a * tiles_b, (P.K + TC_BK - 1) / TC_BK, P.split, gridDim.x, blockIdx.x);
   volatile int* abort_flag = &S.abort_flag;
 
   if (threadIdx.x == 0) {
@@ -86,10 +251,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        // consecutive CTAs take consecutive A tiles of the same B tile, so that a wave shares B in L2
+      int tile, kb0, kb1, slot;
+      for (int i = 0; ok && sched.item(i, tile, kb0, kb1, slot); i++) {
         const int ta = tile % tiles_a, tb = tile / tiles_a;
-        for (int kb = 0; kb < n_kb; kb++, it++) {
+        for (int kb = kb0; kb < kb1; kb++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&S.empty[s], ph ^ 1, abort_flag)) {
@@ -109,17 +274,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       const uint32_t idesc = instr_desc_bf16(BN);
-      uint32_t it = 0, t = 0;
+      uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, t++) {
-        const int buf = t & 1;
-        const uint32_t acc_ph = (t >> 1) & 1;
+      int tile, kb0, kb1, slot;
+      for (int i = 0; ok && sched.item(i, tile, kb0, kb1, slot); i++) {
+        const int buf = i & 1;
+        const uint32_t acc_ph = (i >> 1) & 1;
         if (!mbar_wait(&S.acc_empty[buf], acc_ph ^ 1, abort_flag)) {
           atomicCAS(P.status, 0, 102); S.abort_flag = 1; ok = false; break;
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < n_kb; kb++, it++) {
+        for (int kb = kb0; kb < kb1; kb++, it++) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&S.full[s], ph, abort_flag)) {
@@ -131,7 +297,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           for (int k = 0; k < TC_BK / 16; k++) {
             // 16 k-values = 32 bytes further along each 128-byte swizzled row
             umma_bf16(d_tmem, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
-                      (kb > 0 || k > 0) ? 1u : 0u);
+                      (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&S.empty[s]);           // arrives once the MMAs above have read this stage
         }
@@ -141,19 +307,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5)
     const int quarter = warp & 3;                 // the TMEM lanes this warp may read: 32*quarter ..
-    uint32_t t = 0;
+    const int row = quarter * 32 + lane;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, t++) {
+    int tile, kb0, kb1, slot;
+    for (int i = 0; ok && sched.item(i, tile, kb0, kb1, slot); i++) {
       const int ta = tile % tiles_a, tb = tile / tiles_a;
-      const int buf = t & 1;
-      const uint32_t acc_ph = (t >> 1) & 1;
+      const int buf = i & 1;
+      const uint32_t acc_ph = (i >> 1) & 1;
       if (!mbar_wait(&S.acc_full[buf], acc_ph, abort_flag)) {
         if (lane == 0) { atomicCAS(P.status, 0, 104); S.abort_flag = 1; }
         ok = false;
         break;
       }
       tc_fence_after();
-      const int row_a = ta * TC_BM + quarter * 32 + lane;       // row of the A operand this thread holds
+      const int m = ta * TC_BM + row;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
       constexpr int CW = (BN >= 32) ? 32 : 16;                  // columns per tcgen05.ld
 #pragma unroll 1
@@ -161,103 +328,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint32_t r[CW];
         if constexpr (CW == 32) tmem_ld32(taddr + c0, r); else tmem_ld16(taddr + c0, r);
         tmem_ld_wait();
-        const int col_b0 = tb * BN + c0;                        // first row of the B operand in this chunk
-        if (!SWAP) {
-          // thread = output row m, columns n = col_b0 .. col_b0 + CW - 1 (contiguous in memory)
-          const int m = row_a;
-          if (m < P.M) {
-            float v[CW];
+        if (slot >= 0) {
+          // a piece of a shared tile: partial sums, [column][row] so that the lanes of a warp write neighbours
+          float* part = P.scratch + (((size_t)sched.c * 2 + slot) * BN + c0) * TC_BM + row;
 #pragma unroll
-            for (int j = 0; j < CW; j++) {
-              v[j] = __uint_as_float(r[j]);
-              if (P.bias && col_b0 + j < P.N) v[j] += P.bias[col_b0 + j];
-            }
-            const bool whole = col_b0 + CW <= P.N;
-            if (EPI == 3) {
-              bf16* o = (bf16*)P.out + (size_t)m * P.ldo + (col_b0 >> 1);
-              uint32_t packed[CW / 4];
+          for (int j = 0; j < CW; j++) part[(size_t)j * TC_BM] = __uint_as_float(r[j]);
+          continue;
+        }
+        if (m < P.M) {
+          float v[CW];
 #pragma unroll
-              for (int j = 0; j < CW; j += 4) {
-                float a[2];
-#pragma unroll
-                for (int e = 0; e < 2; e++) {
-                  const float gate = __bfloat162float(__float2bfloat16_rn(v[j + 2 * e]));
-                  const float up = __bfloat162float(__float2bfloat16_rn(v[j + 2 * e + 1]));
-                  a[e] = gate / (1.0f + __expf(-gate)) * up;
-                }
-                __nv_bfloat162 pr = __floats2bfloat162_rn(a[0], a[1]);
-                packed[j / 4] = *reinterpret_cast<uint32_t*>(&pr);
-              }
-              if (whole && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
-#pragma unroll
-                for (int q = 0; q < CW / 16; q++)
-                  reinterpret_cast<uint4*>(o)[q] =
-                      make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
-              } else {
-#pragma unroll
-                for (int j = 0; j < CW; j += 2)
-                  if (col_b0 + j + 1 < P.N) {
-                    const __nv_bfloat162 pr = *reinterpret_cast<__nv_bfloat162*>(&packed[j / 4]);
-                    o[j >> 1] = (j & 2) ? pr.y : pr.x;
-                  }
-              }
-            } else if (EPI == 0) {
-              bf16* o = (bf16*)P.out + (size_t)m * P.ldo + col_b0;
-              if (whole && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
-#pragma unroll
-                for (int q = 0; q < CW / 8; q++) {
-                  uint32_t w4[4];
-#pragma unroll
-                  for (int e = 0; e < 4; e++) {
-                    __nv_bfloat162 pr = __floats2bfloat162_rn(v[8 * q + 2 * e], v[8 * q + 2 * e + 1]);
-                    w4[e] = *reinterpret_cast<uint32_t*>(&pr);
-                  }
-                  reinterpret_cast<uint4*>(o)[q] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < CW; j++)
-                  if (col_b0 + j < P.N) o[j] = __float2bfloat16_rn(v[j]);
-              }
-            } else {
-              float* o = (float*)P.out + (size_t)m * P.ldo + col_b0;
-              if (whole && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
-#pragma unroll
-                for (int q = 0; q < CW / 4; q++) {
-                  float4 w4 = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                  if (EPI == 1) {
-                    const float4 old = ld_fresh(reinterpret_cast<const float4*>(o) + q);
-                    w4.x += old.x; w4.y += old.y; w4.z += old.z; w4.w += old.w;
-                  }
-                  reinterpret_cast<float4*>(o)[q] = w4;
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < CW; j++)
-                  if (col_b0 + j < P.N) o[j] = (EPI == 1) ? ld_fresh(o + j) + v[j] : v[j];
-              }
-            }
-          }
-        } else {
-          // thread = weight row n, columns m = col_b0 .. (rows of x): lanes are neighbours in n
-          const int n = row_a;
-#pragma unroll
-          for (int j = 0; j < CW; j++) {
-            const int m = col_b0 + j;
-            float v = __uint_as_float(r[j]);
-            if (P.bias && n < P.N) v += P.bias[n];
-            if (EPI == 3) {
-              v = __bfloat162float(__float2bfloat16_rn(v));
-              const float other = __shfl_xor_sync(0xffffffffu, v, 1);     // gate (even n) <-> up (odd n)
-              if (m < P.M && n + 1 < P.N && (n & 1) == 0)
-                ((bf16*)P.out)[(size_t)m * P.ldo + (n >> 1)] = __float2bfloat16_rn(v / (1.0f + __expf(-v)) * other);
-            } else if (m < P.M && n < P.N) {
-              const size_t idx = (size_t)m * P.ldo + n;
-              if (EPI == 0) ((bf16*)P.out)[idx] = __float2bfloat16_rn(v);
-              else if (EPI == 1) ((float*)P.out)[idx] = ld_fresh((const float*)P.out + idx) + v;
-              else ((float*)P.out)[idx] = v;
-            }
-          }
+          for (int j = 0; j < CW; j++) v[j] = __uint_as_float(r[j]);
+          tc_store_chunk<EPI, CW>(P, m, tb * BN + c0, v);
         }
       }
       tc_fence_before();
@@ -498,22 +580,103 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld,
   return r == CUDA_SUCCESS ? 0 : STRATUM_ERR_SHAPE;
 }
 
-template <int BN, int STAGES, bool SWAP>
-static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& P, int epilogue, int n_tiles,
-                     cudaStream_t stream) {
+// Second pass for tiles shared between CTAs (see TcSchedule).  Block (r, g) takes a 32-row by 64-column part of
+// the r-th shared tile.  The pieces lie [column][row]: a warp reads 32 rows of one column at a time and adds the
+// pieces in the order of k (eight columns per thread, two pieces in flight); the sums go through shared memory so
+// that the epilogue writes rows, four neighbouring columns per thread.
+template <int BN, int EPI>
+__global__ void __launch_bounds__(256)
+gemm_tc_pieces_kernel(const TcParams P, int G, int n_tiles, int n_kb, int tiles_a) {
+  __shared__ float tile_s[32][65];
+  pdl_trigger();
+  const int R = n_tiles % G, U = R * n_kb;
+  const int r = blockIdx.x;
+  const int first_c = tc_owner(r * n_kb, G, U), last_c = tc_owner((r + 1) * n_kb - 1, G, U);
+  if (first_c == last_c) return;                   // one CTA had the whole tile
+  const int tile = n_tiles - R + r;
+  const int ta = tile % tiles_a, tb = tile / tiles_a;
+  const int row0 = (blockIdx.y % 4) * 32, col0 = (blockIdx.y / 4) * 64;
+  if (ta * TC_BM + row0 >= P.M || tb * BN + col0 >= P.N) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  pdl_wait();
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; j++) acc[j] = 0.f;
+  for (int c0 = first_c; c0 <= last_c; c0 += 2) {
+    float a[2][8];
+#pragma unroll
+    for (int e = 0; e < 2; e++) {
+      const int cc = c0 + e;
+      const int slot = (tc_begin(cc < G ? cc : 0, G, U) / n_kb == r) ? 0 : 1;
+      const float* src = P.scratch + (((size_t)cc * 2 + slot) * BN + col0 + warp * 8) * TC_BM + row0 + lane;
+#pragma unroll
+      for (int j = 0; j < 8; j++) a[e][j] = (cc <= last_c) ? __ldcg(src + (size_t)j * TC_BM) : 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < 2; e++)
+#pragma unroll
+      for (int j = 0; j < 8; j++) acc[j] += a[e][j];
+  }
+#pragma unroll
+  for (int j = 0; j < 8; j++) tile_s[lane][warp * 8 + j] = acc[j];
+  __syncthreads();
+#pragma unroll
+  for (int pass = 0; pass < 2; pass++) {
+    const int rr = pass * 16 + (threadIdx.x >> 4), cc4 = (threadIdx.x & 15) * 4;
+    const int m = ta * TC_BM + row0 + rr;
+    if (m < P.M)
+      fixup_store<EPI>(P, m, tb * BN + col0 + cc4,
+                       make_float4(tile_s[rr][cc4], tile_s[rr][cc4 + 1], tile_s[rr][cc4 + 2], tile_s[rr][cc4 + 3]));
+  }
+}
+
+// Whether sharing the left-over tiles pays: a model of both ways in units of one k-block of one tile (about half
+// a microsecond).  Plain: waves * n_kb.  Shared: the k-blocks spread over all SMs, plus writing and reading the
+// pieces (a piece of 128 x 256 float32 per SM costs about as much as 16 k-blocks, measured), plus the second
+// launch (6).  STRATUM_GEMM_SPLIT=0 turns sharing off, =1 forces it where it is possible (measurements).
+static bool split_pays(int n_tiles, int n_kb, int sms, int bn) {
+  static int mode = -1;
+  if (mode < 0) {
+    const char* e = getenv("STRATUM_GEMM_SPLIT");
+    mode = e ? atoi(e) + 1 : 0;                   // 0: model, 1: off, 2: on
+  }
+  const int left = n_tiles % sms, waves = (n_tiles + sms - 1) / sms;
+  if (left == 0 || (long long)left * n_kb < 4LL * sms || mode == 1) return false;
+  if (mode == 2) return true;
+  const float plain = (float)waves * n_kb;
+  const float pieces = (float)(sms + left) / sms;                        // per SM
+  const float shared = (float)n_tiles * n_kb / sms + pieces * 16.0f * bn / 256.0f + 6.0f;
+  return shared < 0.9f * plain;
+}
+
+template <int BN, int STAGES>
+static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TcParams P, int epilogue, int n_tiles, int n_kb,
+                     int tiles_a, float* scratch, cudaStream_t stream) {
   const size_t smem = sizeof(TcSmem<BN, STAGES>) + 1024;
-  const int grid = n_tiles < sm_count() ? n_tiles : sm_count();
+  const int sms = sm_count();
+  int grid = n_tiles < sms ? n_tiles : sms;
+  const int left = n_tiles % sms;
+  P.split = 0; P.scratch = scratch;
+  if (scratch && split_pays(n_tiles, n_kb, sms, BN)) {
+    P.split = 1;
+    grid = sms;
+  }
 #define TC_LAUNCH(E)                                                                                        \
   {                                                                                                         \
-    auto kern = gemm_tc_kernel<BN, STAGES, E, SWAP>;                                                        \
+    auto kern = gemm_tc_kernel<BN, STAGES, E>;                                                              \
     static bool configured = false; /* once per instantiation; not a stream operation */                   \
     if (!configured) {                                                                                      \
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
       if (e != cudaSuccess) return (int)e;                                                                  \
       configured = true;                                                                                    \
     }                                                                                                       \
-    const int st = launch_pdl(kern, grid, TC_THREADS, smem, stream, ma, mb, P);                             \
+    int st = launch_pdl(kern, grid, TC_THREADS, smem, stream, ma, mb, P);                                   \
     if (st != 0) return st;                                                                                 \
+    if (P.split) {                                                                                          \
+      st = launch_pdl(gemm_tc_pieces_kernel<BN, E>, dim3(left, 4 * (BN / 64)), 256, 0, stream, P, grid,              \
+                      n_tiles, n_kb, tiles_a);                                                              \
+      if (st != 0) return st;                                                                               \
+    }                                                                                                       \
   }
   switch (epilogue) {
     case 0: TC_LAUNCH(0) break;
@@ -532,50 +695,6 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
 // the tile if it is the first beginning inside it.  A block is 4 rows of x (one per warp) by 128 weight rows
 // (four neighbours per lane, so that every load and store is 16 bytes wide); the loads of up to eight partial
 // tiles are in flight together.
-template <int EPI>
-__device__ __forceinline__ void fixup_store(const SkParams& P, int m, int n, float4 v) {
-  float e[4] = {v.x, v.y, v.z, v.w};
-  if (P.bias) {
-#pragma unroll
-    for (int j = 0; j < 4; j++) if (n + j < P.N) e[j] += P.bias[n + j];
-  }
-  if (EPI == 3) {                                   // (gate, up) pairs: n even
-    bf16* o = (bf16*)P.out + (size_t)m * P.ldo + (n >> 1);
-#pragma unroll
-    for (int j = 0; j < 4; j += 2) {
-      if (n + j + 1 < P.N) {
-        const float g = __bfloat162float(__float2bfloat16_rn(e[j])), u = __bfloat162float(__float2bfloat16_rn(e[j + 1]));
-        o[j >> 1] = __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
-      }
-    }
-    return;
-  }
-  const size_t idx = (size_t)m * P.ldo + n;
-  const bool wide = (n + 3 < P.N) && ((idx & 3) == 0);
-  if (EPI == 0) {
-    bf16* o = (bf16*)P.out + idx;
-    if (wide && ((reinterpret_cast<uintptr_t>(o) & 7) == 0)) {
-      __nv_bfloat162 lo = __floats2bfloat162_rn(e[0], e[1]), hi = __floats2bfloat162_rn(e[2], e[3]);
-      uint2 u; u.x = *reinterpret_cast<uint32_t*>(&lo); u.y = *reinterpret_cast<uint32_t*>(&hi);
-      *reinterpret_cast<uint2*>(o) = u;
-    } else {
-#pragma unroll
-      for (int j = 0; j < 4; j++) if (n + j < P.N) o[j] = __float2bfloat16_rn(e[j]);
-    }
-  } else {
-    float* o = (float*)P.out + idx;
-    if (wide && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
-      float4 r = make_float4(e[0], e[1], e[2], e[3]);
-      if (EPI == 1) { const float4 old = __ldcg(reinterpret_cast<const float4*>(o)); r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w; }
-      *reinterpret_cast<float4*>(o) = r;
-    } else {
-#pragma unroll
-      for (int j = 0; j < 4; j++)
-        if (n + j < P.N) o[j] = (EPI == 1) ? ld_fresh(o + j) + e[j] : e[j];
-    }
-  }
-}
-
 template <int BN, int EPI>
 __global__ void __launch_bounds__(128)
 gemm_tc_fixup_kernel(const SkParams P, int G) {
@@ -648,13 +767,13 @@ static int launch_streamk(const CUtensorMap& mw, const CUtensorMap& mx, const Sk
 #undef SK_LAUNCH
 }
 
-// Scratch the stream-K form needs: floats for partial tiles, and one counter per tile of 128 weight rows.
-STRATUM_EXPORT long long stratum_gemm_tc_scratch_floats(void) { return (long long)sm_count() * 2 * 64 * TC_BM; }
-STRATUM_EXPORT long long stratum_gemm_tc_counters(int N) { return (long long)(N + TC_BM - 1) / TC_BM; }
+// Scratch for partial tiles (two 128 x 256 float32 tiles per SM cover both forms); the counters are unused.
+STRATUM_EXPORT long long stratum_gemm_tc_scratch_floats(void) { return (long long)sm_count() * 2 * 256 * TC_BM; }
+STRATUM_EXPORT long long stratum_gemm_tc_counters(int N) { (void)N; return (long long)sm_count(); }
 
 // x: bf16 [M][ldx], w: bf16 [N][K], bias float32 [N] or null, out [M][ldo] (SwiGLU: [M][N/2]).
-// scratch / counters: used when M <= 64 (see stratum_gemm_tc_scratch_floats / _counters; the counters must be
-// zero before the first launch, and every launch leaves them zero).
+// scratch: partial tiles of tiles shared between CTAs (see stratum_gemm_tc_scratch_floats).  Without it more than
+// 64 rows of x still work (no tile is shared then); up to 64 rows need it.  counters: unused, kept for callers.
 // status: one int in device memory, 0 before the call; non-zero afterwards means a wait inside the kernel ran out.
 // Needs K % 8 == 0, ldx % 8 == 0, 16-byte aligned x and w (a TMA copy starts on a 16-byte boundary and its
 // row pitch is a multiple of 16 bytes; the k coordinate of every copy here is a multiple of 64).
@@ -668,6 +787,7 @@ STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bi
   if (!status) return STRATUM_ERR_SHAPE;
   TcParams P;
   P.bias = bias; P.out = out; P.status = status; P.M = M; P.N = N; P.K = K; P.ldo = ldo;
+  P.split = 0; P.scratch = nullptr;
   CUtensorMap ma, mb;
   const bool swap = M <= 64;
   int st;
@@ -676,9 +796,9 @@ STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bi
     const bool wide = N >= 2048;
     if ((st = make_map(&ma, x, M, K, ldx, TC_BM)) != 0) return st;
     if ((st = make_map(&mb, w, N, K, K, wide ? 256 : 128)) != 0) return st;
-    const int tiles_m = (M + TC_BM - 1) / TC_BM;
-    if (wide) return launch_tc<256, 4, false>(ma, mb, P, epilogue, tiles_m * ((N + 255) / 256), stream);
-    return launch_tc<128, 6, false>(ma, mb, P, epilogue, tiles_m * ((N + 127) / 128), stream);
+    const int tiles_m = (M + TC_BM - 1) / TC_BM, n_kb = (K + TC_BK - 1) / TC_BK;
+    if (wide) return launch_tc<256, 4>(ma, mb, P, epilogue, tiles_m * ((N + 255) / 256), n_kb, tiles_m, scratch, stream);
+    return launch_tc<128, 6>(ma, mb, P, epilogue, tiles_m * ((N + 127) / 128), n_kb, tiles_m, scratch, stream);
   }
   // few rows of x: tiles of 128 rows of W by all rows of x, k-blocks spread evenly over the SMs
   if (!scratch || !counters) return STRATUM_ERR_SHAPE;

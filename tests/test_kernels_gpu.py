@@ -137,7 +137,13 @@ def test_gemm_skinny(M, N, K_):
 @pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (33, 48, 64), (64, 1000, 200), (100, 256, 4096), (300, 4096 + 16, 512),
                                      (2048, 2 * 177, 96), (129, 6144, 1024), (1, 128, 128), (17, 130, 72),
                                      (8, 4096, 4096), (5, 28672, 1024), (64, 4096 + 64, 14336), (16, 6144, 4096),
-                                     (40, 50000, 512), (8, 128256, 1024), (9, 1002, 1096), (64, 260, 2048)])
+                                     (40, 50000, 512), (8, 128256, 1024), (9, 1002, 1096), (64, 260, 2048),
+                                     # more tiles than SMs with a partly filled last wave: its tiles are shared along k
+                                     (2048, 4096, 512), (1024, 6144, 1280), (4096, 1024, 640), (2000, 4100, 520),
+                                     # fewer tiles than SMs: all of them are shared
+                                     (200, 4096, 4096), (100, 1000, 8192), (65, 2304, 2048),
+                                     # a full wave of whole tiles, then shared ones
+                                     (1280, 4608, 8192)])
 def test_gemm_tc(M, N, K_):
     from stratum_b200 import kernels as K
     rng = np.random.default_rng(M + N + K_)
@@ -161,16 +167,16 @@ def test_gemm_tc(M, N, K_):
     K.check_status()
     r16 = as64(dev(ref, torch.bfloat16))
     assert rel_err(as64(act), P.silu(r16[:, 0::2]) * r16[:, 1::2]) < 2e-2
-    if M <= 64:
-        # the split over SMs depends on the shapes only: a row alone gives the same bits, and so does a second run
+    # the split over SMs depends on the shapes only: a second run gives the same bits
+    again = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    K.gemm_tc(x, w, b, again, K.EPI_STORE_F32)
+    K.check_status()
+    assert torch.equal(again, out32)
+    if M <= 16:
+        # and a row alone gives the same bits as the row in its batch
         one = torch.empty(1, N, dtype=torch.float32, device="cuda")
         K.gemm_tc(x[M - 1:M], w, b, one, K.EPI_STORE_F32)
-        again = torch.empty(M, N, dtype=torch.float32, device="cuda")
-        K.gemm_tc(x, w, b, again, K.EPI_STORE_F32)
-        K.check_status()
-        assert torch.equal(again, out32)
-        if M <= 16:
-            assert torch.equal(one[0], out32[M - 1])
+        assert torch.equal(one[0], out32[M - 1])
 
 
 def test_gemm_skinny_refuses_what_it_cannot_do():
