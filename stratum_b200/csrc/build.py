@@ -26,9 +26,10 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",
                            "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
 SOURCES = ("elementwise", "linear_simple", "attention_simple", "sampling", "gemm_skinny", "attention_mma",
-           "gemm_tc", "attention_tc", "attention_static")
+           "gemm_tc", "attention_tc", "attention_stream", "attention_static")
 HEADERS = ("common.cuh",)
-EXTRA_DEPS = {"attention_static": ("attention_mma.cu", "attention_static.h"),   # files a source includes
+EXTRA_DEPS = {"attention_static": ("attention_mma.cu", "attention_static.h", "mma_common.cuh"),   # files a source includes
+              "attention_mma": ("mma_common.cuh",), "attention_stream": ("mma_common.cuh", "tc_common.cuh"),
               "gemm_tc": ("tc_common.cuh",), "attention_tc": ("tc_common.cuh",)}
 
 _lock = threading.Lock()

@@ -1,8 +1,9 @@
 """Which attention kernel serves a given step.
 
 float32, and head sizes the tensor-core kernel refuses (above 128, or no multiple of 16): the CUDA-core
-kernel with the fixed key order.  bfloat16: the tensor-core kernel; on decode steps the keys of each
-sequence are cut into splits so that the whole GPU has work, which needs scratch for the partial results.
+kernel with the fixed key order.  bfloat16 decode steps: the TMA-fed kernel that spreads all pages evenly over
+the SMs (head size 64 or 128, up to 8 heads per kv head), else the kernel whose keys are cut into splits per
+sequence, which needs scratch for the partial results.  bfloat16 prompts: the tcgen05 kernel, else the tile kernel.
 """
 from __future__ import annotations
 
@@ -37,7 +38,12 @@ def run(att, qkv: torch.Tensor, cache, step, out: torch.Tensor) -> None:
     gs = att.n_heads // att.n_kv_heads
     rows_per_token = min(gs, 16)
     head_groups = (gs + 15) // 16
-    if step.all_single:
+    if (step.all_single and hd in (64, 128) and gs <= 8 and step.n_tokens <= 1024
+            and os.environ.get("STRATUM_ATTENTION_STREAM", "1") != "0"):
+        # decode steps: the pages of all sequences spread evenly over the SMs, streamed by TMA
+        K.attention_stream(qkv, cache.k, cache.v, step.token_pos, step.token_seq, cache.block_table, out,
+                           att.n_heads, att.n_kv_heads, hd, PAGE_TOKENS, att.window, att.scale)
+    elif step.all_single:
         n_splits, chunk = plan_splits(step.n_tokens * att.n_kv_heads * head_groups, step.max_len)
         part_o = part_ml = None
         if n_splits > 1:

@@ -537,6 +537,76 @@ def test_attention_tc_far_key():
     assert rel_err(as64(_run_tc(c, [100, 700], n_q, n_kv, hd)), c["ref"]) < 8e-3
 
 
+def _run_stream(c, n_q, n_kv, hd, window=0, pad_rows=0):
+    """attention_stream on the case's new tokens (one per sequence), optionally with padding rows appended."""
+    from stratum_b200 import kernels as K
+    T = c["T"]
+    qkv, pos, seq = c["qkv"], c["pos"], c["seq"]
+    if pad_rows:
+        qkv = torch.cat([qkv, torch.full((pad_rows, qkv.shape[1]), 7.0, dtype=qkv.dtype, device="cuda")])
+        pos = torch.cat([pos, torch.zeros(pad_rows, dtype=torch.int32, device="cuda")])
+        seq = torch.cat([seq, torch.full((pad_rows,), -1, dtype=torch.int32, device="cuda")])
+    out = torch.zeros(T + pad_rows, n_q * hd, dtype=torch.bfloat16, device="cuda")
+    K.attention_stream(qkv, c["kc"], c["vc"], pos, seq, c["table"], out, n_q, n_kv, hd, 64, window,
+                       1.0 / math.sqrt(hd))
+    K.check_status()
+    return out
+
+
+@pytest.mark.parametrize("n_q,n_kv,hd", [(8, 2, 128), (4, 4, 64), (32, 8, 128), (8, 1, 64), (3, 1, 128), (12, 2, 128)])
+def test_attention_stream_decode_steps(n_q, n_kv, hd):
+    rng = np.random.default_rng(hd + n_q + 3)
+    # unequal sequences: one short of a page end, one just past it, a long one, a single key, a few pages
+    lens = [63, 64, 1500, 0, 300, 129]
+    c = _attention_case(rng, lens, [1] * len(lens), n_q, n_kv, hd, "bfloat16")
+    out = _run_stream(c, n_q, n_kv, hd, pad_rows=2)
+    assert rel_err(as64(out[:c["T"]]), c["ref"]) < 8e-3
+    assert float(out[c["T"]:].float().abs().sum()) == 0.0                 # padding rows are left alone
+    # one long sequence alone: every (sequence, kv head) is shared by many CTAs
+    c = _attention_case(rng, [5000], [1], n_q, n_kv, hd, "bfloat16")
+    assert rel_err(as64(_run_stream(c, n_q, n_kv, hd)), c["ref"]) < 8e-3
+    # many short sequences: many whole (sequence, kv head) runs per CTA
+    lens = [int(x) for x in rng.integers(0, 200, size=70)]
+    c = _attention_case(rng, lens, [1] * len(lens), n_q, n_kv, hd, "bfloat16")
+    assert rel_err(as64(_run_stream(c, n_q, n_kv, hd)), c["ref"]) < 8e-3
+
+
+def test_attention_stream_far_key_and_window_edge():
+    rng = np.random.default_rng(43)
+    n_q, n_kv, hd = 4, 2, 64
+    far = {0: 3, 1: 517}
+
+    def spike(s, q, k, v):
+        d = rng.standard_normal(hd); d /= np.linalg.norm(d)
+        k[far[s], :, :] = d * 12.0
+        q[-1, :, :] = d * 12.0
+
+    c = _attention_case(rng, [699, 600], [1, 1], n_q, n_kv, hd, "bfloat16", spike=spike)
+    out = _run_stream(c, n_q, n_kv, hd)
+    assert rel_err(as64(out), c["ref"]) < 8e-3
+    W, p = 100, 400
+
+    def edge(s, q, k, v):                     # sequence 0: the spiked key is the last one inside the window;
+        d = rng.standard_normal(hd); d /= np.linalg.norm(d)          # sequence 1: the first one outside
+        k[p - W + 1 if s == 0 else p - W, :, :] = d * 12.0
+        q[-1, :, :] = d * 12.0
+
+    c = _attention_case(rng, [p, p], [1, 1], n_q, n_kv, hd, "bfloat16", window=W, spike=edge)
+    out = _run_stream(c, n_q, n_kv, hd, window=W)
+    assert rel_err(as64(out), c["ref"]) < 8e-3
+
+
+def test_attention_stream_refuses_what_it_cannot_do():
+    from stratum_b200 import kernels as K
+    z = lambda *s, dt=torch.bfloat16: torch.zeros(*s, dtype=dt, device="cuda")   # noqa: E731
+    with pytest.raises(K.KernelError, match="shape"):                       # head size 96
+        K.attention_stream(z(1, 3 * 96), z(1, 1, 64, 96), z(1, 1, 64, 96), z(1, dt=torch.int32), z(1, dt=torch.int32),
+                           z(1, 1, dt=torch.int32), z(1, 96), 1, 1, 96, 64, 0, 1.0)
+    with pytest.raises(K.KernelError, match="shape"):                       # 16 heads per kv head
+        K.attention_stream(z(1, 18 * 64), z(1, 1, 64, 64), z(1, 1, 64, 64), z(1, dt=torch.int32),
+                           z(1, dt=torch.int32), z(1, 1, dt=torch.int32), z(1, 16 * 64), 16, 1, 64, 64, 0, 1.0)
+
+
 def test_attention_mma_refuses_head_sizes_it_cannot_do():
     from stratum_b200 import kernels as K
     z = lambda *s, dt=torch.bfloat16: torch.zeros(*s, dtype=dt, device="cuda")   # noqa: E731
