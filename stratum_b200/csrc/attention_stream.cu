@@ -152,11 +152,14 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
       SaCursor cur;
       cur.seek(P, S.pre, u0);
-      pdl_wait();                                // the newest key and value come from the kernel before
+      // Only a sequence's last page holds what the kernel before this one wrote (the newest key and value): the
+      // pages before it are requested at once, up to a ring's worth, and the wait comes with the first last page.
+      bool waited = false;
       uint32_t it = 0;
       bool ok = true;
       for (long long u = u0; u < u1 && ok; u++, it++) {
         const int s = it % STAGES;
+        if (!waited && (it >= (uint32_t)STAGES || cur.page == cur.s.first + cur.s.n - 1)) { pdl_wait(); waited = true; }
         if (!mbar_wait(&S.empty[s], ((it / STAGES) & 1) ^ 1, abort_flag)) {
           atomicCAS(P.status, 0, 301); S.abort_flag = 1; ok = false; break;
         }
@@ -169,6 +172,7 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
         cur.next(P);
       }
+      if (!waited) pdl_wait();
       if (!ok) {
         for (int i = 0; i < 2000; i++) __nanosleep(1000);   // let copies already issued land
       }
