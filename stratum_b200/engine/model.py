@@ -61,6 +61,8 @@ class Model:
         self.layers: List[Layer] = [Layer(ls, runtime) for ls in spec.layers]
         self.final_norm = find_part("norm", spec.final_norm.kind)(spec.final_norm, runtime)
         self.head = find_part("head", spec.head.kind)(spec.head, runtime)
+        self.position = (find_part("position", spec.position.kind)(spec.position, runtime)
+                         if spec.position is not None else None)
         self.schedule = spec.schedule
         self.hidden, self.vocab = spec.hidden, spec.vocab
 
@@ -68,6 +70,8 @@ class Model:
     def tensors(self) -> Dict[str, TensorSpec]:
         out: Dict[str, TensorSpec] = {}
         out.update(self.embedding.tensors())
+        if self.position is not None:
+            out.update(self.position.tensors())
         for layer in self.layers:
             out.update(layer.tensors())
         out.update(self.final_norm.tensors())
@@ -92,6 +96,8 @@ class Model:
     # ------------------------------------------------------------------ weights
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
         self.embedding.bind(weights)
+        if self.position is not None:
+            self.position.bind(weights)
         for layer in self.layers:
             layer.bind(weights)
         self.final_norm.bind(weights)
@@ -101,6 +107,8 @@ class Model:
     def forward(self, step, cache) -> torch.Tensor:
         """Run the tokens of one step through every stop of the schedule; float32 logits at the wanted rows."""
         x = self.embedding.forward(step.token_ids)
+        if self.position is not None:
+            self.position.add_to_embedding(x, step)
         for stop, entry in enumerate(self.schedule):
             layer = self.layers[entry.layer]
             owner = stop if entry.cache_of is None else entry.cache_of

@@ -62,6 +62,7 @@ class ModelSpec:
     schedule: Tuple[ScheduleEntry, ...]
     final_norm: PartSpec
     head: PartSpec
+    position: Optional[PartSpec] = None     # an encoding that acts on the embedded tokens (absolute positions)
 
     def check(self) -> None:
         n = len(self.layers)
