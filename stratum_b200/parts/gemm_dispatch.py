@@ -16,10 +16,11 @@ from .. import kernels as K
 STORE, ADD_TO_F32, STORE_F32, SWIGLU = K.EPI_STORE, K.EPI_ADD_F32, K.EPI_STORE_F32, K.EPI_SWIGLU
 import os
 
-# rows of x up to which the weight-streaming mma.sync kernel is used: at 8 rows it and the stream-K tcgen05
-# kernel take the same time on the Llama-8B layer shapes, below it wins (one kernel, no second pass), above
-# it needs a second 8-row tile and loses.  STRATUM_SKINNY_MAX_ROWS overrides it for measurements.
-SKINNY_MAX_ROWS = int(os.environ.get("STRATUM_SKINNY_MAX_ROWS", 8))
+# rows of x up to which the weight-streaming mma.sync kernel is used.  Measured in whole decode steps on the
+# Llama-8B layer shapes: one and two rows are faster with it (one kernel, no second pass), from four rows on the
+# stream-K tcgen05 kernel wins (3.96 against 4.10 ms at four rows).  STRATUM_SKINNY_MAX_ROWS overrides it for
+# measurements.
+SKINNY_MAX_ROWS = int(os.environ.get("STRATUM_SKINNY_MAX_ROWS", 2))
 # weight matrices of at least this many elements go to the stream-K kernel even for few rows of x: its TMA
 # ring keeps more bytes in flight, which pays once the matrix is large enough to amortise its set-up
 STREAMK_MIN_WEIGHTS = int(os.environ.get("STRATUM_STREAMK_MIN_WEIGHTS", 400_000_000))
