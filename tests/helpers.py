@@ -7,7 +7,7 @@ import torch
 
 from plain import llama_plain as P
 
-# Three tiny Llama configurations that differ in every size and option.
+# Tiny Llama configurations that differ in every size and option.
 TINY_A = {   # grouped heads, untied, no bias, plain rope
     "architectures": ["LlamaForCausalLM"], "model_type": "llama",
     "num_hidden_layers": 2, "hidden_size": 64, "intermediate_size": 176,
@@ -32,7 +32,23 @@ TINY_C = {   # heads*head_dim != hidden, as many kv heads as heads, interleaved 
     "rope_scaling": {"rope_type": "linear", "factor": 2.0}, "max_position_embeddings": 512,
     "tie_word_embeddings": False, "attention_bias": True, "mlp_bias": False, "hidden_act": "silu",
 }
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+TINY_D = {   # head size 64 in groups of two: the TMA / tcgen05 attention and matrix kernels at model level
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 136, "intermediate_size": 200,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64, "vocab_size": 331,
+    "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 1024,
+    "tie_word_embeddings": False, "attention_bias": False, "mlp_bias": False, "hidden_act": "silu",
+}
+TINY_E = {   # head size 128, eight heads on one kv head, llama3 scaling
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 1, "hidden_size": 192, "intermediate_size": 328,
+    "num_attention_heads": 8, "num_key_value_heads": 1, "head_dim": 128, "vocab_size": 517,
+    "rms_norm_eps": 1e-6, "rope_theta": 500000.0, "max_position_embeddings": 1024,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 256},
+    "tie_word_embeddings": True, "attention_bias": False, "mlp_bias": True, "hidden_act": "silu",
+}
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 def make_model_dir(path, cfg_dict, seed, dtype="float32", std=0.02, edit=None):
