@@ -212,7 +212,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
     for (int j = 0; j < n_tiles; j++) {
       const int b = j & 1;
-      if (!mbar_wait(&S.s_full[b], (j >> 1) & 1, abort_flag)) { if (lane == 0) FA_FAIL(209); ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(&S.s_full[b], (j >> 1) & 1, abort_flag))) {   // (a warp gives up as one)
+        if (lane == 0) FA_FAIL(209);
+        ok = false;
+        break;
+      }
       tc_fence_after();
       float s[32], t[32];                                // this thread's half of the keys, and the other half
       tmem_ld32f(lane_addr + b * FA_KEYS + half * 32, s);
@@ -267,7 +271,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       if (j > 0) {
         // P V of the tile before has read P and has been added into O
-        if (!mbar_wait(&S.pv_full, (j - 1) & 1, abort_flag)) { if (lane == 0) FA_FAIL(208); ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&S.pv_full, (j - 1) & 1, abort_flag))) {
+          if (lane == 0) FA_FAIL(208);
+          ok = false;
+          break;
+        }
         if (__any_sync(0xffffffffu, grow)) {             // some row of this warp moves its reference: rescale O
           tc_fence_after();
 #pragma unroll
@@ -297,7 +305,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.p_full);
     }
-    if (ok && !mbar_wait(&S.pv_full, (n_tiles - 1) & 1, abort_flag)) { if (lane == 0) FA_FAIL(208); ok = false; }
+    if (ok && !__all_sync(0xffffffffu, mbar_wait(&S.pv_full, (n_tiles - 1) & 1, abort_flag))) {
+      if (lane == 0) FA_FAIL(208);
+      ok = false;
+    }
     tc_fence_after();
     // the two halves of the keys kept separate sums: add them (P is no longer read; named barrier among the
     // softmax warps, reached by all of them)

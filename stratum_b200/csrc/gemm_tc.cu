@@ -314,7 +314,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int ta = tile % tiles_a, tb = tile / tiles_a;
       const int buf = i & 1;
       const uint32_t acc_ph = (i >> 1) & 1;
-      if (!mbar_wait(&S.acc_full[buf], acc_ph, abort_flag)) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&S.acc_full[buf], acc_ph, abort_flag))) {   // (a warp gives up as one)
         if (lane == 0) { atomicCAS(P.status, 0, 104); S.abort_flag = 1; }
         ok = false;
         break;
@@ -525,7 +525,7 @@ gemm_tc_streamk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
       const int seg_end = min(kb1, (tile + 1) * P.n_kb);
       const bool whole = (g == tile * P.n_kb) && (seg_end == (tile + 1) * P.n_kb);
       const int buf = seg & 1;
-      if (!mbar_wait(&S.acc_full[buf], (seg >> 1) & 1, abort_flag)) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&S.acc_full[buf], (seg >> 1) & 1, abort_flag))) {
         if (lane == 0) { atomicCAS(P.status, 0, 104); S.abort_flag = 1; }
       }
       // the four epilogue warps go on, or give up, together: the barriers below have no limit of their own
