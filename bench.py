@@ -42,6 +42,16 @@ LLAMA_31_8B = {   # the Llama-3.1-8B shape named by the baseline's third configu
     "tie_word_embeddings": False, "attention_bias": False, "mlp_bias": False, "hidden_act": "silu",
     "torch_dtype": "bfloat16",
 }
+# The baseline's other two shapes, for the short --decode-only / --prefill-only lines (the JSON line of the
+# contract is always the Llama-3.1-8B shape).
+OTHER_SHAPES = {
+    "llama2-7b": dict(LLAMA_31_8B, num_key_value_heads=32, intermediate_size=11008, vocab_size=32000,
+                      rope_theta=10000.0, rope_scaling=None, max_position_embeddings=4096),
+    "llama3.2-1b": dict(LLAMA_31_8B, num_hidden_layers=16, hidden_size=2048, intermediate_size=8192, head_dim=64,
+                        tie_word_embeddings=True,
+                        rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                                      "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}),
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 PREFILL_TOKENS = 2048
 
@@ -208,6 +218,8 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--decode-only", action="store_true",
                     help="time the decode steps only and print a short line (for profiler runs)")
+    ap.add_argument("--shape", default="llama3.1-8b", choices=["llama3.1-8b"] + sorted(OTHER_SHAPES),
+                    help="layer sizes for the short lines of --decode-only / --prefill-only")
     ap.add_argument("--prefill-only", action="store_true",
                     help="time the 2,048-token prompt only and print a short line (for profiler runs)")
     args = ap.parse_args()
@@ -228,7 +240,12 @@ def main() -> int:
     from stratum_b200 import Stratum, kernels
     from stratum_b200.config import LlamaConfig
 
-    raw = dict(LLAMA_31_8B)
+    raw = dict(LLAMA_31_8B if args.shape == "llama3.1-8b" else OTHER_SHAPES[args.shape])
+    if raw.get("rope_scaling") is None:
+        raw.pop("rope_scaling", None)
+    if args.shape != "llama3.1-8b" and not (args.decode_only or args.prefill_only):
+        print("bench.py: --shape other than llama3.1-8b goes with --decode-only or --prefill-only")
+        return 2
     n_layers_full = raw["num_hidden_layers"]
     n_layers = args.layers or n_layers_full
     raw["num_hidden_layers"] = n_layers
