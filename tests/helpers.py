@@ -48,7 +48,14 @@ TINY_E = {   # head size 128, eight heads on one kv head, llama3 scaling
                      "high_freq_factor": 4.0, "original_max_position_embeddings": 256},
     "tie_word_embeddings": True, "attention_bias": False, "mlp_bias": True, "hidden_act": "silu",
 }
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
+TINY_F = {   # a width, an inner size and a vocabulary that no vector load divides: the fallback kernels
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 102, "intermediate_size": 150,
+    "num_attention_heads": 6, "num_key_value_heads": 3, "head_dim": 32, "vocab_size": 203,
+    "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 512,
+    "tie_word_embeddings": True, "attention_bias": False, "mlp_bias": False, "hidden_act": "silu",
+}
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F}
 
 
 def make_model_dir(path, cfg_dict, seed, dtype="float32", std=0.02, edit=None):
