@@ -15,7 +15,7 @@
 //            epilogue of one tile overlap the k-loop of the next.
 //
 // Tiles that would form a last, partly filled wave are cut along k and shared by all CTAs (see TcSchedule).
-// Up to 64 rows of x take the stream-K form further down, with the roles of x and W exchanged.
+// Up to 128 rows of x take the stream-K form further down, with the roles of x and W exchanged.
 //
 // Every wait on an mbarrier is bounded.  If one runs out, the kernel records where in a status
 // word, tells its other warps through shared memory, lets copies in flight land, frees its tensor
@@ -735,6 +735,7 @@ gemm_tc_fixup_kernel(const SkParams P, int G) {
 #define SK_RING_16 10
 #define SK_RING_32 9
 #define SK_RING_64 8
+#define SK_RING_128 6
 #endif
 
 template <int BN, int STAGES>
@@ -773,7 +774,7 @@ STRATUM_EXPORT long long stratum_gemm_tc_counters(int N) { (void)N; return (long
 
 // x: bf16 [M][ldx], w: bf16 [N][K], bias float32 [N] or null, out [M][ldo] (SwiGLU: [M][N/2]).
 // scratch: partial tiles of tiles shared between CTAs (see stratum_gemm_tc_scratch_floats).  Without it more than
-// 64 rows of x still work (no tile is shared then); up to 64 rows need it.  counters: unused, kept for callers.
+// 128 rows of x still work (no tile is shared then); up to 128 rows need it.  counters: unused, kept for callers.
 // status: one int in device memory, 0 before the call; non-zero afterwards means a wait inside the kernel ran out.
 // Needs K % 8 == 0, ldx % 8 == 0, 16-byte aligned x and w (a TMA copy starts on a 16-byte boundary and its
 // row pitch is a multiple of 16 bytes; the k coordinate of every copy here is a multiple of 64).
@@ -789,7 +790,10 @@ STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bi
   P.bias = bias; P.out = out; P.status = status; P.M = M; P.N = N; P.K = K; P.ldo = ldo;
   P.split = 0; P.scratch = nullptr;
   CUtensorMap ma, mb;
-  const bool swap = M <= 64;
+  // up to 64 rows always; 65 to 128 rows unless the tile form fills most of the SMs with one wave (measured on the
+  // Llama-8B shapes: 16.7 against 22 us for N = K = 4096, 70 against 53 us for N = 28672)
+  const long long tiles_plain = (long long)((M + TC_BM - 1) / TC_BM) * ((N + (N >= 2048 ? 255 : 127)) / (N >= 2048 ? 256 : 128));
+  const bool swap = M <= 64 || (M <= 128 && scratch && tiles_plain * 10 < (long long)sm_count() * 7);
   int st;
   if (!swap) {
     // prompts: 128 rows of x by 256 (or 128) rows of W per tile
@@ -802,7 +806,7 @@ STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bi
   }
   // few rows of x: tiles of 128 rows of W by all rows of x, k-blocks spread evenly over the SMs
   if (!scratch || !counters) return STRATUM_ERR_SHAPE;
-  const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
   if ((st = make_map(&ma, w, N, K, K, TC_BM)) != 0) return st;
   if ((st = make_map(&mb, x, M, K, ldx, bn)) != 0) return st;
   SkParams Q;
@@ -815,5 +819,6 @@ STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bi
   // as deep, two CTAs per SM, ran a third slower)
   if (bn == 16) return launch_streamk<16, SK_RING_16>(ma, mb, Q, epilogue, stream);
   if (bn == 32) return launch_streamk<32, SK_RING_32>(ma, mb, Q, epilogue, stream);
-  return launch_streamk<64, SK_RING_64>(ma, mb, Q, epilogue, stream);
+  if (bn == 64) return launch_streamk<64, SK_RING_64>(ma, mb, Q, epilogue, stream);
+  return launch_streamk<128, SK_RING_128>(ma, mb, Q, epilogue, stream);
 }

@@ -60,8 +60,19 @@ def _ptr(t: Optional[torch.Tensor]) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)     # the short way to the stream's handle
+_device_index: Optional[int] = None
+
+
 def _stream() -> c_void_p:
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The current stream of the current device (under a graph capture: the capturing stream).  Asked for at
+    every launch, so by the shortest route torch offers."""
+    global _device_index
+    if _raw_stream is None:
+        return c_void_p(torch.cuda.current_stream().cuda_stream)
+    if _device_index is None:
+        _device_index = torch.cuda.current_device()
+    return c_void_p(_raw_stream(_device_index))
 
 
 def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> None:
@@ -248,7 +259,7 @@ def _gemm_tc_scratch(n_out: int, device):
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
             epilogue: int) -> None:
     """bfloat16 tile kernel on the 5th-generation tensor cores (TMA + tcgen05/TMEM); see EPI_*.
-    Up to 64 rows of x run in the stream-K form (every SM reads an equal share of w)."""
+    Up to 128 rows of x run in the stream-K form (every SM reads an equal share of w)."""
     M, N, Kd = _linear_shapes(x, w, bias, out, epilogue, "gemm_tc")
     _need(x, "x", torch.bfloat16, contiguous=False)
     part, counters = _gemm_tc_scratch(N, x.device)

@@ -141,7 +141,7 @@ def test_gemm_skinny(M, N, K_):
                                      # more tiles than SMs with a partly filled last wave: its tiles are shared along k
                                      (2048, 4096, 512), (1024, 6144, 1280), (4096, 1024, 640), (2000, 4100, 520),
                                      # fewer tiles than SMs: all of them are shared
-                                     (200, 4096, 4096), (100, 1000, 8192), (65, 2304, 2048),
+                                     (200, 4096, 4096), (100, 1000, 8192), (65, 2304, 2048), (128, 4096, 1024), (97, 6146, 328),
                                      # a full wave of whole tiles, then shared ones
                                      (1280, 4608, 8192)])
 def test_gemm_tc(M, N, K_):
