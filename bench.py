@@ -218,6 +218,8 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--decode-only", action="store_true",
                     help="time the decode steps only and print a short line (for profiler runs)")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                    help="prompt length of --prefill-only (the JSON line of the contract always uses 2,048)")
     ap.add_argument("--shape", default="llama3.1-8b", choices=["llama3.1-8b"] + sorted(OTHER_SHAPES),
                     help="layer sizes for the short lines of --decode-only / --prefill-only")
     ap.add_argument("--prefill-only", action="store_true",
@@ -254,13 +256,15 @@ def main() -> int:
     rng = np.random.default_rng(0)
     biggest = max(args.batch, 1 if (args.no_points or args.decode_only or args.prefill_only) else 64)
     llm = Stratum.from_random(cfg, seed=0, dtype="bfloat16",
-                              max_tokens=biggest * (args.context + 64), max_seqs=biggest)
+                              max_tokens=max(biggest * (args.context + 64), args.prefill_tokens + 64),
+                              max_seqs=biggest)
     vocab = cfg.vocab
 
     if args.prefill_only:
-        ms = time_prefill(llm, PREFILL_TOKENS, vocab, rng, repeats=2)
-        print(json.dumps({"prefill_only": True, "tokens": PREFILL_TOKENS, "layers": n_layers, "ms": round(ms, 3),
-                          "tflops": round(prefill_flops(cfg, n_layers, PREFILL_TOKENS) / ms / 1e9, 1)}))
+        n_tok = args.prefill_tokens
+        ms = time_prefill(llm, n_tok, vocab, rng, repeats=2)
+        print(json.dumps({"prefill_only": True, "tokens": n_tok, "layers": n_layers, "ms": round(ms, 3),
+                          "tflops": round(prefill_flops(cfg, n_layers, n_tok) / ms / 1e9, 1)}))
         return 0
     with ClockSampler() as clocks:
         ms_step, launches = time_decode(llm, args.batch, args.context, args.steps, args.warmup, vocab, rng)
