@@ -58,6 +58,13 @@ struct FaSmem {
   int abort_flag;
 };
 
+// max(a, b, c) in one instruction (sm_100 has the three-input form)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -150,7 +157,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           jv++; moved = true;
         }
         if (moved) { idle = 0; continue; }
-        if (++idle >= 64u * TC_SPIN_LIMIT || ((idle & 1023u) == 0 && *abort_flag)) { FA_FAIL(201); ok = false; }
+        __nanosleep(64);                       // (a hot poll would take issue slots from the softmax warps beside it)
+        if (++idle >= 4u * TC_SPIN_LIMIT || ((idle & 1023u) == 0 && *abort_flag)) { FA_FAIL(201); ok = false; }
       }
       if (!ok) {
         for (int i = 0; i < 2000; i++) __nanosleep(1000);   // let copies already issued land
@@ -238,11 +246,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         for (int i = 0; i < 32; i++) {
           s[i] = (valid && ks + i <= pos && ks + i >= lo) ? s[i] : -INFINITY;
           t[i] = (valid && kt + i <= pos && kt + i >= lo) ? t[i] : -INFINITY;
-          mx[i & 3] = fmaxf(mx[i & 3], fmaxf(s[i], t[i]));
+          mx[i & 3] = max3(mx[i & 3], s[i], t[i]);
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 32; i++) mx[i & 3] = fmaxf(mx[i & 3], fmaxf(s[i], t[i]));
+        for (int i = 0; i < 32; i++) mx[i & 3] = max3(mx[i & 3], s[i], t[i]);
       }
       float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       tile_max *= P.scale_log2;                          // scale > 0: the maximum of the scaled scores
