@@ -52,8 +52,8 @@ struct FaSmem {
   alignas(1024) bf16 k[FA_STAGES][FA_KEYS * HD];      // [HD/64][64 keys][64 dims]
   alignas(1024) bf16 v[FA_STAGES][FA_KEYS * HD];      // [HD/64][64 keys][64 dims]
   alignas(1024) bf16 p[FA_ROWS * FA_KEYS];            // [128 rows][64 keys]; at the end: the rows' two half sums
-  uint64_t q_full, k_full[FA_STAGES], v_full[FA_STAGES], k_empty[FA_STAGES], v_empty[FA_STAGES];
-  uint64_t s_full[2], s_empty[2], p_full, pv_full;
+  uint64_t q_full, k_full[FA_STAGES], v_full[FA_STAGES];
+  uint64_t s_full[2], p_full, pv_full[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -100,12 +100,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(&S.q_full, 1);
-    for (int s = 0; s < FA_STAGES; s++) {
-      mbar_init(&S.k_full[s], 1); mbar_init(&S.v_full[s], 1); mbar_init(&S.k_empty[s], 1); mbar_init(&S.v_empty[s], 1);
-    }
-    for (int b = 0; b < 2; b++) { mbar_init(&S.s_full[b], 1); mbar_init(&S.s_empty[b], FA_SOFTMAX_WARPS); }
+    for (int s = 0; s < FA_STAGES; s++) { mbar_init(&S.k_full[s], 1); mbar_init(&S.v_full[s], 1); }
+    for (int b = 0; b < 2; b++) { mbar_init(&S.s_full[b], 1); mbar_init(&S.pv_full[b], 1); }
     mbar_init(&S.p_full, FA_SOFTMAX_WARPS);
-    mbar_init(&S.pv_full, 1);
     S.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -134,22 +131,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       for (int db = 0; db < DB; db++)
         tma_load_3d(&map_q, S.q + db * FA_ROWS * 64, &S.q_full, db * 64, kvh * P.gs, tok0);
       const int* bt = P.block_table + (size_t)seq * P.bt_stride;
-      // K and V have rings of their own: a K tile is free again as soon as its scores are computed, a whole tile
-      // earlier than the V tile beside it, so the next K is already on its way while P V still runs.  One thread
-      // feeds both rings, polling (never suspended in a wait on one ring while the other has room).
+      // K and V have rings of their own: a K tile is free again as soon as its scores are computed (s_full), a
+      // whole tile earlier than the V tile beside it (pv_full), so the next K is already on its way while P V still
+      // runs.  One thread feeds both rings, polling (never suspended in a wait on one ring while the other has room).
+      // The MMA thread pays about a hundred cycles for every instruction it issues, commits and waits included,
+      // and is what the kernel's pace hangs on: so no barrier exists only to free a buffer.  (The S buffer of tile
+      // j-1 is free for tile j+1 once P of tile j-1 has arrived, which the MMA thread has waited for by then.)
       bool ok = true;
       int jk = 0, jv = 0;
       uint32_t idle = 0;
       while ((jk < n_tiles || jv < n_tiles) && ok) {
         bool moved = false;
-        if (jk < n_tiles && mbar_test_wait(&S.k_empty[jk % FA_STAGES], ((jk / FA_STAGES) & 1) ^ 1)) {
+        if (jk < n_tiles && (jk < 2 || mbar_test_wait(&S.s_full[jk & 1], ((jk - 2) >> 1) & 1))) {
           const int s = jk % FA_STAGES;
           const int row = (bt[lo_tile + jk] * P.n_kv + kvh) * FA_KEYS;
           mbar_expect_tx(&S.k_full[s], FA_KEYS * HD * sizeof(bf16));
           for (int db = 0; db < DB; db++) tma_load_2d(&map_k, S.k[s] + db * FA_KEYS * 64, &S.k_full[s], db * 64, row);
           jk++; moved = true;
         }
-        if (jv < n_tiles && mbar_test_wait(&S.v_empty[jv % FA_STAGES], ((jv / FA_STAGES) & 1) ^ 1)) {
+        if (jv < n_tiles && (jv < 2 || mbar_test_wait(&S.pv_full[jv & 1], ((jv - 2) >> 1) & 1))) {
           const int s = jv % FA_STAGES;
           const int row = (bt[lo_tile + jv] * P.n_kv + kvh) * FA_KEYS;
           mbar_expect_tx(&S.v_full[s], FA_KEYS * HD * sizeof(bf16));
@@ -174,7 +174,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       auto issue_scores = [&](int j) -> bool {
         const int s = j % FA_STAGES, b = j & 1;
         if (!mbar_wait(&S.k_full[s], (j / FA_STAGES) & 1, abort_flag)) { FA_FAIL(203); return false; }
-        if (!mbar_wait(&S.s_empty[b], ((j >> 1) & 1) ^ 1, abort_flag)) { FA_FAIL(204); return false; }
         tc_fence_after();
         const uint32_t q_addr = smem_u32(S.q), k_addr = smem_u32(S.k[s]);
 #pragma unroll
@@ -183,8 +182,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           for (int kk = 0; kk < 4; kk++)
             umma_bf16(tmem_base + b * FA_KEYS, smem_desc_sw128(q_addr + db * FA_ROWS * 128 + kk * 32),
                       smem_desc_sw128(k_addr + db * FA_KEYS * 128 + kk * 32), idesc_s, (db | kk) ? 1u : 0u);
-        umma_commit(&S.s_full[b]);
-        umma_commit(&S.k_empty[s]);             // K of this tile has been read once these MMAs are done
+        umma_commit(&S.s_full[b]);              // to the softmax warps, and to the producer: K of this tile is read
         return true;
       };
       if (ok) ok = issue_scores(0);
@@ -199,8 +197,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         for (int kk = 0; kk < 4; kk++)          // 16 keys a step: 32 bytes along a row of P, 16 rows of V
           umma_bf16(tmem_base + COL_PV, smem_desc_sw128(p_addr + kk * 32),
                     smem_desc_sw128_mn(v_addr + kk * 16 * 128, FA_KEYS * 128), idesc_pv, (j | kk) ? 1u : 0u);
-        umma_commit(&S.pv_full);
-        umma_commit(&S.v_empty[s]);             // V of this tile has been read
+        umma_commit(&S.pv_full[j & 1]);         // to the softmax warps (P is read, O has the tile), and to the
+                                                // producer: V of this tile is read
       }
     }
   } else if (n_tiles > 0) {
@@ -230,9 +228,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       tmem_ld32f(lane_addr + b * FA_KEYS + half * 32, s);
       tmem_ld32f(lane_addr + b * FA_KEYS + (half ^ 1) * 32, t);
       tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&S.s_empty[b]);
       // maximum over the whole tile; keys beyond a row's own position (or before its window) are masked, which
       // only tiles on the diagonal (or at the window's edge) need
       const int key0 = (lo_tile + j) * FA_KEYS;
@@ -279,7 +274,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       if (j > 0) {
         // P V of the tile before has read P and has been added into O
-        if (!__all_sync(0xffffffffu, mbar_wait(&S.pv_full, (j - 1) & 1, abort_flag))) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&S.pv_full[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag))) {
           if (lane == 0) FA_FAIL(208);
           ok = false;
           break;
@@ -313,7 +308,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.p_full);
     }
-    if (ok && !__all_sync(0xffffffffu, mbar_wait(&S.pv_full, (n_tiles - 1) & 1, abort_flag))) {
+    if (ok && !__all_sync(0xffffffffu, mbar_wait(&S.pv_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag))) {
       if (lane == 0) FA_FAIL(208);
       ok = false;
     }
