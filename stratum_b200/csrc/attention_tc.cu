@@ -166,39 +166,51 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
-    if (lane == 0 && n_tiles > 0) {
+    // The whole warp walks through the waits together and one elected lane issues: with warp-uniform control
+    // flow the operands of the MMAs (descriptors, addresses) stay warp-uniform values.
+    if (n_tiles > 0) {
       const uint32_t idesc_s = instr_desc_bf16(FA_KEYS);
       const uint32_t idesc_pv = instr_desc_bf16(HD, true);
-      bool ok = mbar_wait(&S.q_full, 0, abort_flag);
-      if (!ok) FA_FAIL(202);
+      bool ok = __all_sync(0xffffffffu, mbar_wait(&S.q_full, 0, abort_flag));
+      if (!ok && lane == 0) FA_FAIL(202);
+      const uint32_t q_addr = smem_u32(S.q), p_addr = smem_u32(S.p);
       auto issue_scores = [&](int j) -> bool {
         const int s = j % FA_STAGES, b = j & 1;
-        if (!mbar_wait(&S.k_full[s], (j / FA_STAGES) & 1, abort_flag)) { FA_FAIL(203); return false; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&S.k_full[s], (j / FA_STAGES) & 1, abort_flag))) {
+          if (lane == 0) FA_FAIL(203);
+          return false;
+        }
         tc_fence_after();
-        const uint32_t q_addr = smem_u32(S.q), k_addr = smem_u32(S.k[s]);
+        const uint32_t k_addr = smem_u32(S.k[s]);
+        if (elect_one()) {
 #pragma unroll
-        for (int db = 0; db < DB; db++)
+          for (int db = 0; db < DB; db++)
 #pragma unroll
-          for (int kk = 0; kk < 4; kk++)
-            umma_bf16(tmem_base + b * FA_KEYS, smem_desc_sw128(q_addr + db * FA_ROWS * 128 + kk * 32),
-                      smem_desc_sw128(k_addr + db * FA_KEYS * 128 + kk * 32), idesc_s, (db | kk) ? 1u : 0u);
-        umma_commit(&S.s_full[b]);              // to the softmax warps, and to the producer: K of this tile is read
+            for (int kk = 0; kk < 4; kk++)
+              umma_bf16(tmem_base + b * FA_KEYS, smem_desc_sw128(q_addr + db * FA_ROWS * 128 + kk * 32),
+                        smem_desc_sw128(k_addr + db * FA_KEYS * 128 + kk * 32), idesc_s, (db | kk) ? 1u : 0u);
+          umma_commit(&S.s_full[b]);            // to the softmax warps, and to the producer: K of this tile is read
+        }
+        __syncwarp();
         return true;
       };
       if (ok) ok = issue_scores(0);
       for (int j = 0; j < n_tiles && ok; j++) {
         if (j + 1 < n_tiles) { ok = issue_scores(j + 1); if (!ok) break; }
         const int s = j % FA_STAGES;
-        if (!mbar_wait(&S.p_full, j & 1, abort_flag)) { FA_FAIL(205); ok = false; break; }
-        if (!mbar_wait(&S.v_full[s], (j / FA_STAGES) & 1, abort_flag)) { FA_FAIL(206); ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&S.p_full, j & 1, abort_flag))) { if (lane == 0) FA_FAIL(205); ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&S.v_full[s], (j / FA_STAGES) & 1, abort_flag))) { if (lane == 0) FA_FAIL(206); ok = false; break; }
         tc_fence_after();
-        const uint32_t p_addr = smem_u32(S.p), v_addr = smem_u32(S.v[s]);
+        const uint32_t v_addr = smem_u32(S.v[s]);
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; kk++)          // 16 keys a step: 32 bytes along a row of P, 16 rows of V
-          umma_bf16(tmem_base + COL_PV, smem_desc_sw128(p_addr + kk * 32),
-                    smem_desc_sw128_mn(v_addr + kk * 16 * 128, FA_KEYS * 128), idesc_pv, (j | kk) ? 1u : 0u);
-        umma_commit(&S.pv_full[j & 1]);         // to the softmax warps (P is read, O has the tile), and to the
+          for (int kk = 0; kk < 4; kk++)        // 16 keys a step: 32 bytes along a row of P, 16 rows of V
+            umma_bf16(tmem_base + COL_PV, smem_desc_sw128(p_addr + kk * 32),
+                      smem_desc_sw128_mn(v_addr + kk * 16 * 128, FA_KEYS * 128), idesc_pv, (j | kk) ? 1u : 0u);
+          umma_commit(&S.pv_full[j & 1]);       // to the softmax warps (P is read, O has the tile), and to the
                                                 // producer: V of this tile is read
+        }
+        __syncwarp();
       }
     }
   } else if (n_tiles > 0) {
