@@ -26,6 +26,8 @@
 #define TC_BK 64
 #define TC_THREADS 192
 
+static int g_last_launches = 0;       // kernels the last stratum_gemm_tc call launched (for launch counting)
+
 struct TcParams {
   const float* bias;
   void* out;
@@ -672,6 +674,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TcParams P, i
     }                                                                                                       \
     int st = launch_pdl(kern, grid, TC_THREADS, smem, stream, ma, mb, P);                                   \
     if (st != 0) return st;                                                                                 \
+    g_last_launches = P.split ? 2 : 1;                                                                      \
     if (P.split) {                                                                                          \
       st = launch_pdl(gemm_tc_pieces_kernel<BN, E>, dim3(left, 4 * (BN / 64)), 256, 0, stream, P, grid,              \
                       n_tiles, n_kb, tiles_a);                                                              \
@@ -755,6 +758,7 @@ static int launch_streamk(const CUtensorMap& mw, const CUtensorMap& mx, const Sk
       configured = true;                                                                                    \
     }                                                                                                       \
     int st = launch_pdl(kern, grid, TC_THREADS, smem, stream, mw, mx, P);                                   \
+    g_last_launches = split_tiles ? 2 : 1;                                                                  \
     if (st != 0 || !split_tiles) return st;                                                                 \
     return launch_pdl(gemm_tc_fixup_kernel<BN, E>, dim3(grid - 1, (P.M + 3) / 4), 128, 0, stream, P, grid);    \
   }
@@ -767,6 +771,8 @@ static int launch_streamk(const CUtensorMap& mw, const CUtensorMap& mx, const Sk
   }
 #undef SK_LAUNCH
 }
+
+STRATUM_EXPORT int stratum_gemm_tc_last_launches(void) { return g_last_launches; }
 
 // Scratch for partial tiles (two 128 x 256 float32 tiles per SM cover both forms); the counters are unused.
 STRATUM_EXPORT long long stratum_gemm_tc_scratch_floats(void) { return (long long)sm_count() * 2 * 256 * TC_BM; }

@@ -268,6 +268,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
              c_void_p, c_void_p])
     _check(f(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), epilogue, M, N, Kd, x.stride(0), out.stride(0),
              _ptr(status_word()), _ptr(part), _ptr(counters), _stream()), "gemm_tc")
+    count_launches(build.load("gemm_tc").stratum_gemm_tc_last_launches() - 1)      # a second pass, if there was one
 
 
 # ------------------------------------------------------------------ attention (any sizes, CUDA cores)
