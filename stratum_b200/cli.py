@@ -16,7 +16,8 @@ Switches carry the reference's environment-variable names as well: --temp / STRA
 (stratum/native/stratum_rope.h:55-64), --multiseq / STRATUM_MULTISEQ (B copies of the prompt in
 one batch, stratum/native/stratum_arch_llama.inc.c:1458-1524), --timing / STRATUM_TIMING (:2062-2070),
 --logits-dump / STRATUM_LOGITS_DUMP (stratum/native/stratum_engine.h:489-525), --ppl / STRATUM_PPL
-(stratum/native/stratum_arch_llama.inc.c:1535-1557).
+(stratum/native/stratum_arch_llama.inc.c:1535-1557).  Without a counterpart there: --batch-file FILE, one prompt
+per line, run as one batch of unequal lengths (every request's ids come out on a line of their own).
 """
 from __future__ import annotations
 
@@ -81,7 +82,7 @@ def main(argv=None) -> int:
     if not argv or argv[0] in ("-h", "--help"):
         print(_usage_with_architectures(), file=sys.stderr)
         print("\noptions: --dtype bfloat16|float32  --fp32  --temp T  --top-k K  --top-p P  --seed S  --stop ID\n"
-              "         --max-kv N  --multiseq B  --timing  --logits-dump PATH  --ppl\n"
+              "         --max-kv N  --multiseq B  --timing  --logits-dump PATH  --ppl  --batch-file FILE\n"
               "         --random-weights SEED --config FILE   (write <model_dir> with random weights first)",
               file=sys.stderr)
         return 1
@@ -101,6 +102,8 @@ def main(argv=None) -> int:
     ap.add_argument("--timing", action="store_true", default="STRATUM_TIMING" in env)
     ap.add_argument("--logits-dump", default=env.get("STRATUM_LOGITS_DUMP", ""))
     ap.add_argument("--ppl", action="store_true", default="STRATUM_PPL" in env)
+    ap.add_argument("--batch-file", default=None,
+                    help="one prompt per line (token ids); the prompts run as one batch of unequal lengths")
     ap.add_argument("--random-weights", type=int, default=None, metavar="SEED")
     ap.add_argument("--config", default=None, help="config.json to build random weights for")
     args = ap.parse_args(argv)
@@ -135,7 +138,7 @@ def main(argv=None) -> int:
         print(f"  N_GENERATE must be an integer, got {args.rest[0]!r}", file=sys.stderr)
         return 1
     capacity = resolve_kv_cap(int(getattr(cfg, "max_position", 0) or 0), args.max_kv)
-    prompt = read_prompt(args.rest[1:], capacity)
+    prompt = read_prompt(args.rest[1:], capacity) if not args.batch_file else []
     vocab = cfg.vocab
     for t in prompt:
         if not (0 <= t < vocab):
@@ -145,8 +148,27 @@ def main(argv=None) -> int:
         print(f"  prompt {len(prompt)} + {n_gen} generated exceeds KV capacity {capacity}", file=sys.stderr)
         return 1
 
+    prompts = None
+    if args.batch_file:
+        try:
+            with open(args.batch_file) as f:
+                prompts = [[int(t) for t in line.split()] for line in f if line.strip()]
+        except (OSError, ValueError) as e:
+            print(f"  batch file {args.batch_file}: {e}", file=sys.stderr)
+            return 1
+        if not prompts:
+            print(f"  batch file {args.batch_file}: no prompts", file=sys.stderr)
+            return 1
+        for q in prompts:
+            if any(not (0 <= t < vocab) for t in q):
+                print(f"  batch file: a token id lies outside the vocabulary [0, {vocab})", file=sys.stderr)
+                return 1
+            if len(q) + n_gen > capacity:
+                print(f"  batch file: prompt {len(q)} + {n_gen} generated exceeds KV capacity {capacity}", file=sys.stderr)
+                return 1
+
     from .engine.api import Stratum
-    B = max(1, args.multiseq)
+    B = len(prompts) if prompts else max(1, args.multiseq)
     try:
         llm = Stratum(args.model_dir, dtype=dtype, max_tokens=B * (((capacity + 63) // 64) * 64), max_seqs=B)
     except (WeightError, SafetensorsError, RuntimeError) as e:
@@ -182,6 +204,14 @@ def main(argv=None) -> int:
     if dump is not None:
         # sequence 0 stays first among the live ones until it ends
         on_logits = lambda logits, picked: dump.record(picked[0], logits[0].cpu().numpy())   # noqa: E731
+    if prompts:
+        results = llm.generate(prompts, max_new_tokens=n_gen + 1, stop_ids=args.stop, sampling=params)
+        torch.cuda.synchronize()
+        for i, r in enumerate(results):
+            print(f"  request {i}: prompt {len(prompts[i])} tok, {len(r.tokens)} generated, ended by {r.finish_reason}",
+                  file=sys.stderr)
+            print(" ".join(map(str, r.tokens)), flush=True)
+        return 0
     results = llm.generate([prompt] * B, max_new_tokens=n_gen + 1, stop_ids=args.stop, sampling=params,
                            on_token=on_token, want_values=True, on_logits=on_logits)
     torch.cuda.synchronize()

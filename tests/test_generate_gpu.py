@@ -122,6 +122,21 @@ def test_command_line_prints_the_reference_lines(folders):
     assert r.returncode != 0 and "exceeds KV capacity" in r.stderr
 
 
+def test_command_line_batch_file(folders, tmp_path):
+    """--batch-file: one prompt per line, run as one batch of unequal lengths; every request's ids on its own line."""
+    path = folders["A", "float32"]
+    cfg, w = load_plain(path)
+    prompts = [[1, 2, 3], [9, 8, 7, 6, 5, 4, 3, 2, 1, 0, 11], [42]]
+    bf = tmp_path / "prompts.txt"
+    bf.write_text("\n".join(" ".join(map(str, q)) for q in prompts) + "\n")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "stratum"), path, "3", "--fp32", "--batch-file", str(bf)],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    lines = [ln.split() for ln in r.stdout.strip().splitlines()]
+    assert lines == [[str(t) for t in P.greedy_generate(cfg, w, q, 4)] for q in prompts]
+    assert "request 1: prompt 11 tok, 4 generated, ended by length" in r.stderr
+
+
 def _run_trace(model, dtype, out, max_tokens, steps):
     p = subprocess.Popen([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model, "--dtype", dtype,
                           "--out", out, "--max-tokens", str(max_tokens)], stdin=subprocess.PIPE,
