@@ -218,6 +218,9 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
     ap.add_argument("--decode-only", action="store_true",
                     help="time the decode steps only and print a short line (for profiler runs)")
+    ap.add_argument("--workload", default=None, choices=["unequal8", "batch64"],
+                    help="the baseline's other workloads through Stratum.generate: 8 unequal prompts of 64..2048 "
+                         "tokens + 256 new tokens (Llama-2-7B), or 64 prompts of 512 + 512 new tokens (Llama-3.2-1B)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="prompt length of --prefill-only (the JSON line of the contract always uses 2,048)")
     ap.add_argument("--shape", default="llama3.1-8b", choices=["llama3.1-8b"] + sorted(OTHER_SHAPES),
@@ -245,8 +248,8 @@ def main() -> int:
     raw = dict(LLAMA_31_8B if args.shape == "llama3.1-8b" else OTHER_SHAPES[args.shape])
     if raw.get("rope_scaling") is None:
         raw.pop("rope_scaling", None)
-    if args.shape != "llama3.1-8b" and not (args.decode_only or args.prefill_only):
-        print("bench.py: --shape other than llama3.1-8b goes with --decode-only or --prefill-only")
+    if args.shape != "llama3.1-8b" and not (args.decode_only or args.prefill_only or args.workload):
+        print("bench.py: --shape other than llama3.1-8b goes with --decode-only, --prefill-only or --workload")
         return 2
     n_layers_full = raw["num_hidden_layers"]
     n_layers = args.layers or n_layers_full
@@ -255,11 +258,42 @@ def main() -> int:
     peaks = load_peaks()
     rng = np.random.default_rng(0)
     biggest = max(args.batch, 1 if (args.no_points or args.decode_only or args.prefill_only) else 64)
+    if args.workload:
+        biggest = 64 if args.workload == "batch64" else 8
+        args.context = 1024 if args.workload == "batch64" else 2304
     llm = Stratum.from_random(cfg, seed=0, dtype="bfloat16",
                               max_tokens=max(biggest * (args.context + 64), args.prefill_tokens + 64),
                               max_seqs=biggest)
     vocab = cfg.vocab
 
+    if args.workload:
+        # the baseline's other two workloads, end to end through Stratum.generate (host ids in and out)
+        if args.workload == "unequal8":          # 8 prompts of uniform random lengths in [64, 2048], 256 new tokens each
+            lens = [int(x) for x in rng.integers(64, 2049, size=8)]
+            new = 256
+        else:                                    # 64 prompts of 512 tokens, 512 new tokens each
+            lens = [512] * 64
+            new = 512
+        prompts = [rng.integers(0, vocab, size=n).tolist() for n in lens]
+        marks = {}
+
+        def on_token(req, index, fed, picked, logit):
+            if index == 0 and req == len(lens) - 1:
+                marks["first"] = time.perf_counter()
+
+        llm.generate([p[:8] for p in prompts[:2]], max_new_tokens=2, stop_ids=())     # compile and warm up
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = llm.generate(prompts, max_new_tokens=new, stop_ids=(), on_token=on_token)
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        n_out = sum(len(r.tokens) for r in out)
+        print(json.dumps({"workload": args.workload, "shape": args.shape, "prompt_tokens": sum(lens),
+                          "new_tokens": n_out, "prompt_s": round(marks["first"] - t0, 4),
+                          "prompt_tok_per_s": round(sum(lens) / (marks["first"] - t0), 1),
+                          "decode_s": round(t1 - marks["first"], 4),
+                          "decode_tok_per_s": round((n_out - len(lens)) / (t1 - marks["first"]), 1)}))
+        return 0
     if args.prefill_only:
         n_tok = args.prefill_tokens
         ms = time_prefill(llm, n_tok, vocab, rng, repeats=2)
