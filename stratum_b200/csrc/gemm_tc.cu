@@ -357,6 +357,174 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
+// ---------------------------------------------------------------- many rows of x: pairs of CTAs
+// The tile kernel above is bound by what an SM can pull out of L2: a 128 x 256 tile needs 48 KB of operands per
+// k-block.  Here two CTAs on neighbouring SMs (a cluster of two) compute a 256 x 256 tile together with MMAs that
+// span both SMs (cta_group::2, M = 256): each CTA fetches its own 128 rows of x and only HALF of the W tile (128
+// rows), 32 KB per k-block for the same arithmetic, and holds its own 128 rows of the accumulator in its TMEM.
+//
+//   warp 0   in both CTAs: one lane issues the TMA loads of its CTA's halves; the bytes of both CTAs are counted
+//            on the leader's (rank 0) `full` barrier;
+//   warp 1   both CTAs allocate tensor memory together; the leader's elected lane issues the MMAs for the pair
+//            and commits to `empty` (stage free) and `acc_full` in BOTH CTAs (multicast commit);
+//   warps 2-5 in both CTAs: epilogue of their CTA's 128 rows; they arrive on the LEADER's `acc_empty`.
+//
+// No TMA multicast is used.  Every mbarrier wait is bounded as above; the two cluster-wide barriers (after set-up
+// and before the tensor memory is freed) are reached by every thread of both CTAs on every path.
+template <int STAGES>
+struct Tc2Smem {
+  alignas(1024) bf16 a[STAGES][TC_BM * TC_BK];     // this CTA's 128 rows of x
+  alignas(1024) bf16 b[STAGES][TC_BM * TC_BK];     // this CTA's 128 rows (half) of the W tile
+  uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+#define TC2_STAGES 6
+#define TC2_BN 256
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const TcParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  using Smem = Tc2Smem<TC2_STAGES>;
+  // (the same offset in both CTAs: the dynamic shared memory starts at the same address in every CTA of a kernel)
+  Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  pdl_trigger();
+  constexpr int BN = TC2_BN, STAGES = TC2_STAGES;
+  constexpr uint32_t STAGE_BYTES_PAIR = 2 * 2 * TC_BM * TC_BK * sizeof(bf16);      // both operands, both CTAs
+  const int tiles_m = (P.M + 2 * TC_BM - 1) / (2 * TC_BM), tiles_n = (P.N + BN - 1) / BN;
+  const int n_tiles = tiles_m * tiles_n;
+  const int n_kb = (P.K + TC_BK - 1) / TC_BK;
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  volatile int* abort_flag = &S.abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
+    for (int b = 0; b < 2; b++) { mbar_init(&S.acc_full[b], 1); mbar_init(&S.acc_empty[b], 8); }   // 4 warps x 2 CTAs
+    S.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc_2cta(&S.tmem_base, 2 * BN);
+    tmem_relinquish_2cta();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // the peer's barriers are initialised and its tensor memory is allocated
+  tc_fence_after();
+  const uint32_t tmem_base = S.tmem_base;
+  pdl_wait();
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer (each CTA its halves)
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+        const int tm = tile % tiles_m, tn = tile / tiles_m;
+        for (int kb = 0; kb < n_kb; kb++, it++) {
+          const int s = it % STAGES;
+          if (!mbar_wait(&S.empty[s], ((it / STAGES) & 1) ^ 1, abort_flag)) {
+            atomicCAS(P.status, 0, 111); S.abort_flag = 1; ok = false; break;
+          }
+          const uint32_t full_leader = cluster_map(&S.full[s], 0);
+          if (leader) mbar_expect_tx(&S.full[s], STAGE_BYTES_PAIR);
+          tma_load_2d_2cta(&map_a, S.a[s], full_leader, kb * TC_BK, tm * 2 * TC_BM + (int)rank * TC_BM);
+          tma_load_2d_2cta(&map_b, S.b[s], full_leader, kb * TC_BK, tn * BN + (int)rank * TC_BM);
+        }
+      }
+      if (!ok) {
+        for (int i = 0; i < 2000; i++) __nanosleep(1000);   // let copies already issued land
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer (the leader, for the pair)
+    if (leader) {
+      const uint32_t idesc = instr_desc_bf16_m256(BN);
+      uint32_t it = 0, t = 0;
+      bool ok = true;
+      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, t++) {
+        const int buf = t & 1;
+        if (!__all_sync(0xffffffffu, mbar_wait(&S.acc_empty[buf], ((t >> 1) & 1) ^ 1, abort_flag))) {
+          if (lane == 0) { atomicCAS(P.status, 0, 112); S.abort_flag = 1; }
+          ok = false; break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < n_kb; kb++, it++) {
+          const int s = it % STAGES;
+          if (!__all_sync(0xffffffffu, mbar_wait(&S.full[s], (it / STAGES) & 1, abort_flag))) {
+            if (lane == 0) { atomicCAS(P.status, 0, 113); S.abort_flag = 1; }
+            ok = false; break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(S.a[s]), b_addr = smem_u32(S.b[s]);
+          if (elect_one()) {
+#pragma unroll
+            for (int k = 0; k < TC_BK / 16; k++)
+              umma_bf16_2cta(d_tmem, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
+                             (kb > 0 || k > 0) ? 1u : 0u);
+            umma_commit_2cta(&S.empty[s], 3);             // the stage is free again, in both CTAs
+          }
+          __syncwarp();
+        }
+        if (ok && elect_one()) umma_commit_2cta(&S.acc_full[buf], 3);   // the accumulators of both CTAs are complete
+        __syncwarp();
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5 of both CTAs)
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const uint32_t acc_empty_leader[2] = {cluster_map(&S.acc_empty[0], 0), cluster_map(&S.acc_empty[1], 0)};
+    uint32_t t = 0;
+    bool ok = true;
+    for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, t++) {
+      const int tm = tile % tiles_m, tn = tile / tiles_m;
+      const int buf = t & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&S.acc_full[buf], (t >> 1) & 1, abort_flag))) {
+        if (lane == 0) { atomicCAS(P.status, 0, 114); S.abort_flag = 1; }
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int m = tm * 2 * TC_BM + (int)rank * TC_BM + row;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(taddr + c0, r);
+        tmem_ld_wait();
+        if (m < P.M) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
+          tc_store_chunk<EPI, 32>(P, m, tn * BN + c0, v);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty_leader[buf]);
+    }
+  }
+  // nobody leaves, and nobody frees tensor memory, before both CTAs are through with it and with each other's
+  // barriers
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_2cta(tmem_base, 2 * BN);
+  }
+}
+
 // ---------------------------------------------------------------- few rows of x: stream-K
 // Decode steps multiply a handful of rows of x by all of W, so the time is the time to read W once, and
 // the work must be spread evenly over every SM whatever N is.  The k-blocks of all tiles (128 weight rows
@@ -651,6 +819,50 @@ static bool split_pays(int n_tiles, int n_kb, int sms, int bn) {
   return shared < 0.9f * plain;
 }
 
+// The pair kernel: clusters of two CTAs, as many pairs as can be resident (at most one per two SMs).
+static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, TcParams P, int epilogue, int n_tiles,
+                      cudaStream_t stream) {
+  const size_t smem = sizeof(Tc2Smem<TC2_STAGES>) + 1024;
+  P.split = 0; P.scratch = nullptr;
+#define TC2_LAUNCH(E)                                                                                       \
+  {                                                                                                         \
+    auto kern = gemm_tc2_kernel<E>;                                                                         \
+    static int max_pairs = 0;                                                                               \
+    if (max_pairs == 0) {                                                                                   \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+      if (e != cudaSuccess) return (int)e;                                                                  \
+      cudaLaunchConfig_t q = {};                                                                            \
+      q.gridDim = dim3(sm_count() & ~1); q.blockDim = dim3(TC_THREADS); q.dynamicSmemBytes = smem;          \
+      int n = 0;                                                                                            \
+      e = cudaOccupancyMaxActiveClusters(&n, kern, &q);                                                     \
+      if (e != cudaSuccess || n < 1) { cudaGetLastError(); return STRATUM_ERR_LIMIT; }                     \
+      max_pairs = n < sm_count() / 2 ? n : sm_count() / 2;                                                  \
+    }                                                                                                       \
+    const int pairs = n_tiles < max_pairs ? n_tiles : max_pairs;                                            \
+    const int st = launch_pdl(kern, 2 * pairs, TC_THREADS, smem, stream, ma, mb, P);                        \
+    if (st != 0) return st;                                                                                 \
+    g_last_launches = 1;                                                                                    \
+  }
+  switch (epilogue) {
+    case 0: TC2_LAUNCH(0) break;
+    case 1: TC2_LAUNCH(1) break;
+    case 2: TC2_LAUNCH(2) break;
+    case 3: TC2_LAUNCH(3) break;
+    default: return STRATUM_ERR_SHAPE;
+  }
+#undef TC2_LAUNCH
+  return launch_status();
+}
+
+static bool pair_kernel_wanted() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("STRATUM_GEMM_2CTA");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
 template <int BN, int STAGES>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TcParams P, int epilogue, int n_tiles, int n_kb,
                      int tiles_a, float* scratch, cudaStream_t stream) {
@@ -804,6 +1016,14 @@ STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bi
   if (!swap) {
     // prompts: 128 rows of x by 256 (or 128) rows of W per tile
     const bool wide = N >= 2048;
+    if (wide && M >= 1024 && pair_kernel_wanted()) {
+      // prompts of a thousand tokens and more: 256 x 256 tiles on pairs of CTAs
+      if ((st = make_map(&ma, x, M, K, ldx, TC_BM)) != 0) return st;
+      if ((st = make_map(&mb, w, N, K, K, TC_BM)) != 0) return st;
+      const int n_tiles2 = ((M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((N + TC2_BN - 1) / TC2_BN);
+      st = launch_tc2(ma, mb, P, epilogue, n_tiles2, stream);
+      if (st != STRATUM_ERR_LIMIT) return st;       // (no pair can be resident here: the tile kernel below)
+    }
     if ((st = make_map(&ma, x, M, K, ldx, TC_BM)) != 0) return st;
     if ((st = make_map(&mb, w, N, K, K, wide ? 256 : 128)) != 0) return st;
     const int tiles_m = (M + TC_BM - 1) / TC_BM, n_kb = (K + TC_BK - 1) / TC_BK;
