@@ -854,13 +854,28 @@ static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, TcParams P, 
   return launch_status();
 }
 
-static bool pair_kernel_wanted() {
-  static int on = -1;
-  if (on < 0) {
+// Rows of x from which the pair kernel is used (STRATUM_GEMM_2CTA=0 turns it off, =N sets the number of rows; for
+// measurements).
+static int pair_kernel_min_rows() {
+  static int rows = -1;
+  if (rows < 0) {
     const char* e = getenv("STRATUM_GEMM_2CTA");
-    on = (e && e[0] == '0') ? 0 : 1;
+    rows = e ? atoi(e) : 129;
+    if (e && rows <= 0) rows = 0x7fffffff;
   }
-  return on == 1;
+  return rows;
+}
+
+// Pairs of CTAs that can be resident at once (for reports).
+STRATUM_EXPORT int stratum_gemm_tc_resident_pairs(void) {
+  auto kern = gemm_tc2_kernel<0>;
+  const size_t smem = sizeof(Tc2Smem<TC2_STAGES>) + 1024;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -1;
+  cudaLaunchConfig_t q = {};
+  q.gridDim = dim3(sm_count() & ~1); q.blockDim = dim3(TC_THREADS); q.dynamicSmemBytes = smem;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &q) != cudaSuccess) { cudaGetLastError(); return -1; }
+  return n;
 }
 
 template <int BN, int STAGES>
@@ -1016,11 +1031,14 @@ STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bi
   if (!swap) {
     // prompts: 128 rows of x by 256 (or 128) rows of W per tile
     const bool wide = N >= 2048;
-    if (wide && M >= 1024 && pair_kernel_wanted()) {
-      // prompts of a thousand tokens and more: 256 x 256 tiles on pairs of CTAs
+    // 256 x 256 tiles on pairs of CTAs where they give most pairs of SMs a tile (measured on the Llama-8B shapes:
+    // ahead from a few hundred rows on, except where N is small and the tile kernel can share its tiles along k)
+    const int n_tiles2 = ((M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((N + TC2_BN - 1) / TC2_BN);
+    const int rows1 = ((M + TC_BM - 1) / TC_BM) * TC_BM, rows2 = ((M + 2 * TC_BM - 1) / (2 * TC_BM)) * 2 * TC_BM;
+    if (wide && M >= pair_kernel_min_rows() && n_tiles2 * 10 >= (sm_count() / 2) * 6 &&
+        rows2 * 100 <= rows1 * 115) {               // (not where half of a pair would work on rows beyond M)
       if ((st = make_map(&ma, x, M, K, ldx, TC_BM)) != 0) return st;
       if ((st = make_map(&mb, w, N, K, K, TC_BM)) != 0) return st;
-      const int n_tiles2 = ((M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((N + TC2_BN - 1) / TC2_BN);
       st = launch_tc2(ma, mb, P, epilogue, n_tiles2, stream);
       if (st != STRATUM_ERR_LIMIT) return st;       // (no pair can be resident here: the tile kernel below)
     }

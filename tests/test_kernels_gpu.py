@@ -143,7 +143,10 @@ def test_gemm_skinny(M, N, K_):
                                      # fewer tiles than SMs: all of them are shared
                                      (200, 4096, 4096), (100, 1000, 8192), (65, 2304, 2048), (128, 4096, 1024), (97, 6146, 328),
                                      # a full wave of whole tiles, then shared ones
-                                     (1280, 4608, 8192)])
+                                     (1280, 4608, 8192),
+                                     # pairs of CTAs on 256 x 256 tiles: rows and columns that end inside a tile, more
+                                     # tiles than pairs of SMs, one row of tiles
+                                     (1000, 2100, 264), (256, 28672, 128), (2304, 9000, 72)])
 def test_gemm_tc(M, N, K_):
     from stratum_b200 import kernels as K
     rng = np.random.default_rng(M + N + K_)
