@@ -374,16 +374,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 template <int STAGES>
 struct Tc2Smem {
   alignas(1024) bf16 a[STAGES][TC_BM * TC_BK];     // this CTA's 128 rows of x
-  alignas(1024) bf16 b[STAGES][TC_BM * TC_BK];     // this CTA's 128 rows (half) of the W tile
+  alignas(1024) bf16 b[STAGES][TC_BM * TC_BK];     // this CTA's half of the W tile (up to 128 rows)
   uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
 };
 
 #define TC2_STAGES 6
-#define TC2_BN 256
 
-template <int EPI>
+// BN: columns of a tile (a multiple of 16, at most 256; each CTA fetches BN / 2 rows of W).  The host picks the
+// width whose number of waves times width is least.
+template <int EPI, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const TcParams P) {
@@ -395,8 +396,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
   pdl_trigger();
-  constexpr int BN = TC2_BN, STAGES = TC2_STAGES;
-  constexpr uint32_t STAGE_BYTES_PAIR = 2 * 2 * TC_BM * TC_BK * sizeof(bf16);      // both operands, both CTAs
+  constexpr int STAGES = TC2_STAGES;
+  constexpr uint32_t STAGE_BYTES_PAIR = 2 * (TC_BM + BN / 2) * TC_BK * sizeof(bf16);      // both operands, both CTAs
   const int tiles_m = (P.M + 2 * TC_BM - 1) / (2 * TC_BM), tiles_n = (P.N + BN - 1) / BN;
   const int n_tiles = tiles_m * tiles_n;
   const int n_kb = (P.K + TC_BK - 1) / TC_BK;
@@ -410,7 +411,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    tmem_alloc_2cta(&S.tmem_base, 2 * BN);
+    tmem_alloc_2cta(&S.tmem_base, 512);
     tmem_relinquish_2cta();
   }
   tc_fence_before();
@@ -437,7 +438,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint32_t full_leader = cluster_map(&S.full[s], 0);
           if (leader) mbar_expect_tx(&S.full[s], STAGE_BYTES_PAIR);
           tma_load_2d_2cta(&map_a, S.a[s], full_leader, kb * TC_BK, tm * 2 * TC_BM + (int)rank * TC_BM);
-          tma_load_2d_2cta(&map_b, S.b[s], full_leader, kb * TC_BK, tn * BN + (int)rank * TC_BM);
+          tma_load_2d_2cta(&map_b, S.b[s], full_leader, kb * TC_BK, tn * BN + (int)rank * (BN / 2));
         }
       }
       if (!ok) {
@@ -457,7 +458,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           ok = false; break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * BN;
+        const uint32_t d_tmem = tmem_base + buf * 256;
         for (int kb = 0; kb < n_kb; kb++, it++) {
           const int s = it % STAGES;
           if (!__all_sync(0xffffffffu, mbar_wait(&S.full[s], (it / STAGES) & 1, abort_flag))) {
@@ -496,9 +497,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
       tc_fence_after();
       const int m = tm * 2 * TC_BM + (int)rank * TC_BM + row;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 + 32 <= BN; c0 += 32) {
         uint32_t r[32];
         tmem_ld32(taddr + c0, r);
         tmem_ld_wait();
@@ -507,6 +508,17 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
           for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
           tc_store_chunk<EPI, 32>(P, m, tn * BN + c0, v);
+        }
+      }
+      if constexpr (BN % 32 != 0) {               // the last 16 columns
+        uint32_t r[16];
+        tmem_ld16(taddr + (BN / 32) * 32, r);
+        tmem_ld_wait();
+        if (m < P.M) {
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
+          tc_store_chunk<EPI, 16>(P, m, tn * BN + (BN / 32) * 32, v);
         }
       }
       tc_fence_before();
@@ -521,7 +533,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc_2cta(tmem_base, 2 * BN);
+    tmem_dealloc_2cta(tmem_base, 512);
   }
 }
 
@@ -820,23 +832,36 @@ static bool split_pays(int n_tiles, int n_kb, int sms, int bn) {
 }
 
 // The pair kernel: clusters of two CTAs, as many pairs as can be resident (at most one per two SMs).
+static int resident_pairs() {
+  static int pairs = 0;
+  if (pairs == 0) {
+    auto kern = gemm_tc2_kernel<0, 256>;
+    const size_t smem = sizeof(Tc2Smem<TC2_STAGES>) + 1024;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -1;
+    cudaLaunchConfig_t q = {};
+    q.gridDim = dim3(sm_count() & ~1); q.blockDim = dim3(TC_THREADS); q.dynamicSmemBytes = smem;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &q) != cudaSuccess || n < 1) { cudaGetLastError(); return -1; }
+    pairs = n < sm_count() / 2 ? n : sm_count() / 2;
+  }
+  return pairs;
+}
+
+template <int BN>
 static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, TcParams P, int epilogue, int n_tiles,
                       cudaStream_t stream) {
   const size_t smem = sizeof(Tc2Smem<TC2_STAGES>) + 1024;
   P.split = 0; P.scratch = nullptr;
+  const int max_pairs = resident_pairs();
+  if (max_pairs < 1) return STRATUM_ERR_LIMIT;
 #define TC2_LAUNCH(E)                                                                                       \
   {                                                                                                         \
-    auto kern = gemm_tc2_kernel<E>;                                                                         \
-    static int max_pairs = 0;                                                                               \
-    if (max_pairs == 0) {                                                                                   \
+    auto kern = gemm_tc2_kernel<E, BN>;                                                                     \
+    static bool configured = false;                                                                         \
+    if (!configured) {                                                                                      \
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
       if (e != cudaSuccess) return (int)e;                                                                  \
-      cudaLaunchConfig_t q = {};                                                                            \
-      q.gridDim = dim3(sm_count() & ~1); q.blockDim = dim3(TC_THREADS); q.dynamicSmemBytes = smem;          \
-      int n = 0;                                                                                            \
-      e = cudaOccupancyMaxActiveClusters(&n, kern, &q);                                                     \
-      if (e != cudaSuccess || n < 1) { cudaGetLastError(); return STRATUM_ERR_LIMIT; }                     \
-      max_pairs = n < sm_count() / 2 ? n : sm_count() / 2;                                                  \
+      configured = true;                                                                                    \
     }                                                                                                       \
     const int pairs = n_tiles < max_pairs ? n_tiles : max_pairs;                                            \
     const int st = launch_pdl(kern, 2 * pairs, TC_THREADS, smem, stream, ma, mb, P);                        \
@@ -854,6 +879,22 @@ static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, TcParams P, 
   return launch_status();
 }
 
+// The tile width of the pair kernel for a shape: the one whose waves x width is least (a narrower tile that saves
+// a wave, or fills the same number of waves with less, wins), 256 among equals.
+static int pair_tile_width(int M, int N, int pairs) {
+  const int tiles_m = (M + 2 * TC_BM - 1) / (2 * TC_BM);
+  int best = 256;
+  long long best_cost = -1;
+  const int widths[3] = {256, 240, 224};
+  for (int i = 0; i < 3; i++) {
+    const int bn = widths[i];
+    const long long tiles = (long long)tiles_m * ((N + bn - 1) / bn);
+    const long long cost = ((tiles + pairs - 1) / pairs) * bn;
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+  }
+  return best;
+}
+
 // Rows of x from which the pair kernel is used (STRATUM_GEMM_2CTA=0 turns it off, =N sets the number of rows; for
 // measurements).
 static int pair_kernel_min_rows() {
@@ -867,16 +908,7 @@ static int pair_kernel_min_rows() {
 }
 
 // Pairs of CTAs that can be resident at once (for reports).
-STRATUM_EXPORT int stratum_gemm_tc_resident_pairs(void) {
-  auto kern = gemm_tc2_kernel<0>;
-  const size_t smem = sizeof(Tc2Smem<TC2_STAGES>) + 1024;
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return -1;
-  cudaLaunchConfig_t q = {};
-  q.gridDim = dim3(sm_count() & ~1); q.blockDim = dim3(TC_THREADS); q.dynamicSmemBytes = smem;
-  int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, kern, &q) != cudaSuccess) { cudaGetLastError(); return -1; }
-  return n;
-}
+STRATUM_EXPORT int stratum_gemm_tc_resident_pairs(void) { return resident_pairs(); }
 
 template <int BN, int STAGES>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TcParams P, int epilogue, int n_tiles, int n_kb,
@@ -1033,14 +1065,20 @@ STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bi
     const bool wide = N >= 2048;
     // 256 x 256 tiles on pairs of CTAs where they give most pairs of SMs a tile (measured on the Llama-8B shapes:
     // ahead from a few hundred rows on, except where N is small and the tile kernel can share its tiles along k)
-    const int n_tiles2 = ((M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((N + TC2_BN - 1) / TC2_BN);
+    const int n_tiles2 = ((M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((N + 255) / 256);
     const int rows1 = ((M + TC_BM - 1) / TC_BM) * TC_BM, rows2 = ((M + 2 * TC_BM - 1) / (2 * TC_BM)) * 2 * TC_BM;
     if (wide && M >= pair_kernel_min_rows() && n_tiles2 * 10 >= (sm_count() / 2) * 6 &&
         rows2 * 100 <= rows1 * 115) {               // (not where half of a pair would work on rows beyond M)
-      if ((st = make_map(&ma, x, M, K, ldx, TC_BM)) != 0) return st;
-      if ((st = make_map(&mb, w, N, K, K, TC_BM)) != 0) return st;
-      st = launch_tc2(ma, mb, P, epilogue, n_tiles2, stream);
-      if (st != STRATUM_ERR_LIMIT) return st;       // (no pair can be resident here: the tile kernel below)
+      const int pairs = resident_pairs();
+      if (pairs >= 1) {
+        const int bn = pair_tile_width(M, N, pairs);
+        const int tiles = ((M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((N + bn - 1) / bn);
+        if ((st = make_map(&ma, x, M, K, ldx, TC_BM)) != 0) return st;
+        if ((st = make_map(&mb, w, N, K, K, bn / 2)) != 0) return st;
+        if (bn == 256) return launch_tc2<256>(ma, mb, P, epilogue, tiles, stream);
+        if (bn == 240) return launch_tc2<240>(ma, mb, P, epilogue, tiles, stream);
+        return launch_tc2<224>(ma, mb, P, epilogue, tiles, stream);
+      }                                             // (no pair can be resident here: the tile kernel below)
     }
     if ((st = make_map(&ma, x, M, K, ldx, TC_BM)) != 0) return st;
     if ((st = make_map(&mb, w, N, K, K, wide ? 256 : 128)) != 0) return st;
