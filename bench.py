@@ -143,6 +143,7 @@ def time_decode(llm, batch, context, steps, warmup, vocab, rng):
     """(ms per step, launches per step) for `steps` decode steps ending at `context` tokens per sequence."""
     import torch
     from stratum_b200 import StepEntry, kernels
+    warmup = warmup + SETTLE_STEPS           # (see E2E_EXTRA_WARMUP: the steps right after the prompts run slower)
     slots = [llm.acquire() for _ in range(batch)]
     try:
         fill_to(llm, slots, context - steps - warmup, vocab, rng)
@@ -186,6 +187,7 @@ def time_prefill(llm, tokens, vocab, rng, repeats=3):
 # down in stages, 6.0 -> 5.2 -> 4.4 ms at batch 8, while the GPU's power management settles after the dense
 # prompt), so the end-to-end run decodes this many more untimed tokens than --warmup before its timed ones.
 E2E_EXTRA_WARMUP = 24
+SETTLE_STEPS = 24          # the same for the device-timed decode steps: untimed steps after the cache is filled
 
 
 def time_e2e(llm, batch, context, steps, warmup, vocab, rng):
@@ -337,7 +339,7 @@ def main() -> int:
             "seq_len": args.context, "rope_theta": cfg.rope_theta, "rope_scaling": "llama3 f8 lo1 hi4 orig8192",
             "rms_eps": cfg.rms_eps, "tied": cfg.tie_embeddings, "cache_dtype": "bf16",
             "parallelism": "single GPU", "l2": "weights (GBs) far exceed the 126 MB L2; no flush needed",
-            "peaks": peaks["source"]},
+            "peaks": peaks["source"], "settle_steps": SETTLE_STEPS},
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes,
                 "d2h_bytes_per_step": d2h_bytes, "warmup": args.warmup + E2E_EXTRA_WARMUP},
         "gpu_launches": int(round(launches * args.steps)),
