@@ -2,11 +2,14 @@
 
 float32 always takes the CUDA-core kernel with the fixed summation order (the true 32-bit
 path).  bfloat16: up to SKINNY_MAX_ROWS rows of x take the weight-streaming kernel (decode
-steps), more rows take the tensor-core tile kernel (prompts), and any shape either refuses
-(rows not 16-byte aligned) falls back to the CUDA-core kernel.
+steps of one or two sequences), more rows the tcgen05 kernels of gemm_tc.cu (stream-K for
+decode steps and short prompts, tiles on pairs of CTAs or on single CTAs for prompts; the
+choice among those is made there, from the shapes), and any shape either refuses (rows not
+16-byte aligned) falls back to the CUDA-core kernel.
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -14,7 +17,6 @@ import torch
 from .. import kernels as K
 
 STORE, ADD_TO_F32, STORE_F32, SWIGLU = K.EPI_STORE, K.EPI_ADD_F32, K.EPI_STORE_F32, K.EPI_SWIGLU
-import os
 
 # rows of x up to which the weight-streaming mma.sync kernel is used.  Measured in whole decode steps on the
 # Llama-8B layer shapes: one and two rows are faster with it (one kernel, no second pass), from four rows on the
