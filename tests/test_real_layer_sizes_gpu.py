@@ -1,4 +1,4 @@
-"""The engine against the plain oracle at the layer sizes of Llama-3.1-8B (two layers, a small vocabulary so that
+"""The engine against the plain oracle at the layer sizes of Llama-3.1-8B, Llama-3.2-1B and Llama-2-7B (one or two layers, a small vocabulary so that
 the float64 oracle stays quick): the kernels meet K = 4096 and 14336, 32 heads of 128 in groups of 4, and every
 form of the matrix product (one and two rows, 3 to 16, 17 to 32, 33 to 64, prompts) in both dtypes."""
 import numpy as np
@@ -20,9 +20,19 @@ REAL_LAYERS = {
 }
 
 
-@pytest.fixture(scope="module")
-def model(tmp_path_factory):
-    path = make_model_dir(str(tmp_path_factory.mktemp("real_layers")), REAL_LAYERS, seed=21, dtype="bfloat16")
+# the same for the layer sizes of Llama-3.2-1B (heads of 64, tied head) and Llama-2-7B (as many kv heads as heads)
+REAL_LAYERS_1B = dict(REAL_LAYERS, hidden_size=2048, intermediate_size=8192, head_dim=64, tie_word_embeddings=True,
+                      rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                                    "high_freq_factor": 4.0, "original_max_position_embeddings": 8192})
+REAL_LAYERS_7B = dict(REAL_LAYERS, num_hidden_layers=1, intermediate_size=11008, num_key_value_heads=32,
+                      rope_theta=10000.0, rope_scaling=None, max_position_embeddings=4096)
+SHAPES = {"llama3.1-8b": REAL_LAYERS, "llama3.2-1b": REAL_LAYERS_1B, "llama2-7b": REAL_LAYERS_7B}
+
+
+@pytest.fixture(scope="module", params=sorted(SHAPES))
+def model(request, tmp_path_factory):
+    raw = {k: v for k, v in SHAPES[request.param].items() if v is not None}
+    path = make_model_dir(str(tmp_path_factory.mktemp("real_layers")), raw, seed=21, dtype="bfloat16")
     cfg, w = load_plain(path)
     return path, cfg, w
 
