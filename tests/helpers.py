@@ -55,7 +55,16 @@ TINY_F = {   # a width, an inner size and a vocabulary that no vector load divid
     "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "max_position_embeddings": 512,
     "tie_word_embeddings": True, "attention_bias": False, "mlp_bias": False, "hidden_act": "silu",
 }
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F}
+TINY_G = {   # heads of 80 in groups of three, yarn scaling whose ramp covers pairs 0 to 9 of 40
+    "architectures": ["LlamaForCausalLM"], "model_type": "llama",
+    "num_hidden_layers": 2, "hidden_size": 144, "intermediate_size": 232,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 80, "vocab_size": 411,
+    "rms_norm_eps": 3e-6, "rope_theta": 50000.0, "max_position_embeddings": 1024,
+    "rope_scaling": {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 32,
+                     "beta_fast": 4.0, "beta_slow": 0.5},
+    "tie_word_embeddings": False, "attention_bias": True, "mlp_bias": False, "hidden_act": "silu",
+}
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E, "F": TINY_F, "G": TINY_G}
 
 
 def make_model_dir(path, cfg_dict, seed, dtype="float32", std=0.02, edit=None):

@@ -95,22 +95,51 @@ def rope_inv_freq(rope_dim: int, theta: float, scaling: Optional[dict] = None) -
                 s = (orig / lam - low) / (high - low)
                 out[i] = (1.0 - s) * f / factor + s * f
         return _as_f32(out)
+    if kind == "yarn":
+        # stratum/native/stratum_rope.h:76-106: a ramp over the pair index between the plain frequency (pairs that
+        # turn more than beta_fast times within the original context) and the interpolated one (fewer than beta_slow)
+        if not factor > 1.0:
+            return inv
+        orig = F64(scaling["original_max_position_embeddings"])
+        dim = F64(rope_dim)
+
+        def corr_dim(n_rot):                    # stratum/native/stratum_rope.h:76-79
+            return dim * math.log(orig / (F64(n_rot) * 2.0 * math.pi)) / (2.0 * math.log(F64(theta)))
+
+        low = max(0.0, math.floor(corr_dim(scaling.get("beta_fast", 32.0))))
+        high = min(dim - 1.0, math.ceil(corr_dim(scaling.get("beta_slow", 1.0))))
+        denom = max(high - low, 0.001)
+        out = np.empty_like(inv)
+        for i, f in enumerate(inv):
+            ramp = 1.0 - min(1.0, max(0.0, (i - low) / denom))
+            out[i] = (f / factor) * (1.0 - ramp) + f * ramp
+        return _as_f32(out)
     raise ValueError(f"plain oracle: unknown rope scaling {kind!r}")
 
 
+def rope_magnitude(scaling: Optional[dict]) -> float:
+    """The factor on cos and sin: 1 except for yarn, where it is attention_factor if that is
+    positive and 0.1 ln(factor) + 1 otherwise.  stratum/native/stratum_rope.h:108-112."""
+    if not scaling or scaling.get("rope_type", scaling.get("type")) != "yarn" or not scaling["factor"] > 1.0:
+        return 1.0
+    att = scaling.get("attention_factor", -1.0)
+    return float(att) if att is not None and att > 0 else 0.1 * math.log(float(scaling["factor"])) + 1.0
+
+
 def apply_rope(x: np.ndarray, positions: np.ndarray, inv_freq: np.ndarray,
-               interleaved: bool) -> np.ndarray:
+               interleaved: bool, magnitude: float = 1.0) -> np.ndarray:
     """Rotate pairs of one head vector by angle = pos * inv_k.
     x: [T, n_heads, head_dim]; dims >= 2*len(inv_freq) are left untouched.
     interleaved pairs (2k, 2k+1): stratum/native/stratum_arch_llama.inc.c:149-156;
     half-split pairs (k, k + n_pairs): stratum/native/stratum_arch_llama.inc.c:139-147.
-    (x0, x1) <- (x0*c - x1*s, x0*s + x1*c)."""
+    (x0, x1) <- (x0*c - x1*s, x0*s + x1*c); cos and sin are multiplied by `magnitude`
+    (stratum/native/stratum_arch_llama.inc.c:143, :152), so only rotated components grow."""
     x = np.array(x, dtype=F64, copy=True)
     n_pairs = inv_freq.shape[0]
     # angle = (float)pos * inv_k in float32, as the reference computes it (:141, :151)
     ang = (np.asarray(positions, dtype=np.float32)[:, None] * inv_freq.astype(np.float32)[None, :]).astype(F64)
-    c = np.cos(ang)[:, None, :]
-    s = np.sin(ang)[:, None, :]
+    c = np.cos(ang)[:, None, :] * F64(magnitude)
+    s = np.sin(ang)[:, None, :] * F64(magnitude)
     if interleaved:
         i0 = np.arange(n_pairs) * 2
         i1 = i0 + 1
@@ -175,8 +204,9 @@ def attention_block(xn: np.ndarray, positions: np.ndarray, w: Dict[str, np.ndarr
     k = linear(xn, w[prefix + "k_proj.weight"], w.get(prefix + "k_proj.bias")).reshape(T, Nk, Hd)
     v = linear(xn, w[prefix + "v_proj.weight"], w.get(prefix + "v_proj.bias")).reshape(T, Nk, Hd)
     inter = bool(cfg.get("rope_interleaved", False))
-    q = apply_rope(q, positions, inv_freq, inter)
-    k = apply_rope(k, positions, inv_freq, inter)
+    mag = rope_magnitude(cfg.get("rope_scaling"))
+    q = apply_rope(q, positions, inv_freq, inter, mag)
+    k = apply_rope(k, positions, inv_freq, inter, mag)
     o = causal_gqa_attention(q, k, v).reshape(T, Nq * Hd)
     return linear(o, w[prefix + "o_proj.weight"], w.get(prefix + "o_proj.bias"))
 

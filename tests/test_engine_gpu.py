@@ -16,7 +16,7 @@ def _engine(path, dtype, max_tokens=2048):
     return Engine(model, max_tokens=max_tokens), cfg
 
 
-@pytest.fixture(scope="module", params=[(n, d) for n in "ABCDEF" for d in DTYPES], ids=lambda p: f"{p[0]}-{p[1]}")
+@pytest.fixture(scope="module", params=[(n, d) for n in "ABCDEFG" for d in DTYPES], ids=lambda p: f"{p[0]}-{p[1]}")
 def setup(request, tmp_path_factory):
     name, dtype = request.param
     path = make_model_dir(str(tmp_path_factory.mktemp(f"tiny{name}_{dtype}")), TINY[name], seed=ord(name),
