@@ -41,6 +41,7 @@ struct SaParams {
   int* status;
   int n_seqs, n_q, n_kv, gs, window;
   float scale;
+  int late_trigger;
 };
 
 template <int CH>
@@ -173,6 +174,7 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         cur.next(P);
       }
       if (!waited) pdl_wait();
+      if (P.late_trigger) pdl_trigger();   // this CTA has asked for its last page
       if (!ok) {
         for (int i = 0; i < 2000; i++) __nanosleep(1000);   // let copies already issued land
       }
@@ -446,7 +448,7 @@ STRATUM_EXPORT int stratum_attention_stream(const void* q, int ldq, const void* 
                                             long long n_pages, const int* token_pos, const int* token_seq,
                                             const int* block_table, int bt_stride, void* out, int ldo, int n_seqs,
                                             int n_q, int n_kv, int head_dim, int page_tokens, int window, float scale,
-                                            float* scratch, int* status, cudaStream_t stream) {
+                                            int late_trigger, float* scratch, int* status, cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (head_dim != 64 && head_dim != 128) return STRATUM_ERR_SHAPE;
   if (n_kv < 1 || n_q % n_kv != 0 || n_q / n_kv > SA_MAX_GS || page_tokens != SA_KEYS) return STRATUM_ERR_SHAPE;
@@ -462,6 +464,7 @@ STRATUM_EXPORT int stratum_attention_stream(const void* q, int ldq, const void* 
   P.block_table = block_table; P.bt_stride = bt_stride; P.out = (bf16*)out; P.ldo = ldo;
   P.scratch = scratch; P.status = status;
   P.n_seqs = n_seqs; P.n_q = n_q; P.n_kv = n_kv; P.gs = n_q / n_kv; P.window = window; P.scale = scale;
+  P.late_trigger = late_trigger;
   // one CTA per SM; with fewer pages than SMs the surplus CTAs find an empty stretch and leave
   const int grid = sm_count() < SA_MAX_PIECES ? sm_count() : SA_MAX_PIECES;
   if (head_dim == 64) return launch_stream<2>(mk, mv, P, grid, stream);

@@ -568,6 +568,20 @@ __device__ __forceinline__ int sk_owner(int i, int G, int total) {
 // Final values of weight row n for x rows m0 .. m0+CW-1 (one thread per weight row, lanes are neighbours in n).
 template <int EPI, int CW>
 __device__ __forceinline__ void sk_store(const SkParams& P, int n, int m0, float (&v)[CW]) {
+  if (EPI == 1) {
+    // all loads of the old values first, so that they are in flight together (the compiler may not move a load
+    // above the store of another row: it cannot know that the rows do not overlap)
+    const bool col_ok = n < P.N;
+    const float b = (P.bias && col_ok) ? P.bias[n] : 0.0f;
+    float old[CW];
+#pragma unroll
+    for (int j = 0; j < CW; j++)
+      old[j] = (col_ok && m0 + j < P.M) ? ld_fresh((const float*)P.out + (size_t)(m0 + j) * P.ldo + n) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < CW; j++)
+      if (col_ok && m0 + j < P.M) ((float*)P.out)[(size_t)(m0 + j) * P.ldo + n] = old[j] + (v[j] + b);
+    return;
+  }
 #pragma unroll
   for (int j = 0; j < CW; j++) {
     const int m = m0 + j;
@@ -740,6 +754,162 @@ gemm_tc_streamk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     }
   }
   tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------- few rows of x, N small: k shared inside a cluster
+// Where W has no more tiles of 128 rows than there are SMs, a cluster of CS CTAs takes one tile and cuts k into
+// CS stretches, one per CTA.  Each CTA sums its stretch in tensor memory; the CTAs of ranks 1.. write their float32
+// partial tile into the shared memory of rank 0 (into its ring, idle by then), and rank 0 adds them in the order
+// of the ranks, which is the order of k, and runs the epilogue.  One launch, no scratch in global memory; the cut
+// depends only on the shapes, so a row's result does not depend on its batch.
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+
+template <int BN, int STAGES, int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_clusterk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                        const SkParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  using Smem = SkSmem<BN, STAGES>;
+  Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_trigger();
+  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  constexpr uint32_t A_BYTES = TC_BM * TC_BK * sizeof(bf16), B_BYTES = BN * TC_BK * sizeof(bf16);
+  const int CS = (int)cluster_nctarank(), rank = (int)cluster_ctarank();
+  const int tile = blockIdx.x / CS;
+  const int kb0 = (int)((long long)rank * P.n_kb / CS), kb1 = (int)((long long)(rank + 1) * P.n_kb / CS);
+  volatile int* abort_flag = &S.abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 1); }
+    mbar_init(&S.acc_full[0], 1);
+    S.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    tmem_alloc(&S.tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = S.tmem_base;
+  constexpr int CW = (BN >= 32) ? 32 : 16;
+  float v[BN];                                     // epilogue warps: this thread's weight row, all rows of x
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+      const int count = kb1 - kb0;
+      const int pre = count < STAGES ? count : STAGES;
+      for (int i = 0; i < pre; i++) {               // weights first: the kernel before this one may still be running
+        mbar_expect_tx(&S.full[i], A_BYTES + B_BYTES);
+        tma_load_2d(&map_w, S.a[i], &S.full[i], (kb0 + i) * TC_BK, tile * TC_BM);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; i++) tma_load_2d(&map_x, S.b[i], &S.full[i], (kb0 + i) * TC_BK, 0);
+      bool ok = true;
+      for (int i = pre; i < count; i++) {
+        const int s = i % STAGES;
+        const uint32_t ph = (i / STAGES) & 1;
+        if (!mbar_wait(&S.empty[s], ph ^ 1, abort_flag)) {
+          atomicCAS(P.status, 0, 121); S.abort_flag = 1; ok = false; break;
+        }
+        mbar_expect_tx(&S.full[s], A_BYTES + B_BYTES);
+        tma_load_2d(&map_w, S.a[s], &S.full[s], (kb0 + i) * TC_BK, tile * TC_BM);
+        tma_load_2d(&map_x, S.b[s], &S.full[s], (kb0 + i) * TC_BK, 0);
+      }
+      if (!ok) {
+        for (int i = 0; i < 2000; i++) __nanosleep(1000);   // let copies already issued land
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc_bf16(BN);
+      bool ok = true;
+      for (int i = 0; i < kb1 - kb0; i++) {
+        const int s = i % STAGES;
+        if (!mbar_wait(&S.full[s], (i / STAGES) & 1, abort_flag)) {
+          atomicCAS(P.status, 0, 123); S.abort_flag = 1; ok = false; break;
+        }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(S.a[s]), b_addr = smem_u32(S.b[s]);
+#pragma unroll
+        for (int k = 0; k < TC_BK / 16; k++) {
+          umma_bf16(tmem_base, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
+                    (i == 0 && k == 0) ? 0u : 1u);
+        }
+        umma_commit(&S.empty[s]);
+      }
+      if (ok) umma_commit(&S.acc_full[0]);
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (warps 2..5): this CTA's sums
+    pdl_wait();
+    if (kb1 > kb0) {
+      if (!__all_sync(0xffffffffu, mbar_wait(&S.acc_full[0], 0, abort_flag))) {
+        if (lane == 0) { atomicCAS(P.status, 0, 124); S.abort_flag = 1; }
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+#pragma unroll
+      for (int c0 = 0; c0 < BN; c0 += CW) {
+        uint32_t r[CW];
+        if constexpr (CW == 32) tmem_ld32(taddr + c0, r); else tmem_ld16(taddr + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < CW; j++) v[c0 + j] = __uint_as_float(r[j]);
+      }
+      tc_fence_before();
+    } else {
+#pragma unroll
+      for (int j = 0; j < BN; j++) v[j] = 0.0f;
+    }
+  }
+  // Every thread of the cluster meets here twice, whatever happened above (a wait that ran out leaves its mark in
+  // the status word and the CTA goes on with what it has).  After the first meeting every CTA's products have been
+  // read out of tensor memory and its ring is idle; after the second the partial tiles are in rank 0.
+  __syncwarp();
+  cluster_sync_all();
+  float* part = reinterpret_cast<float*>(S.a);      // rank 0's ring: [rank - 1][BN][128] float32
+  if (warp >= 2 && rank > 0) {
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t dst = cluster_map(part + (size_t)(rank - 1) * BN * TC_BM + row, 0);
+#pragma unroll
+    for (int j = 0; j < BN; j++) st_cluster_f32(dst + (uint32_t)(j * TC_BM * sizeof(float)), v[j]);
+  }
+  cluster_sync_all();
+  if (warp >= 2 && rank == 0) {
+    const int row = (warp & 3) * 32 + lane;
+    for (int r = 1; r < CS; r++) {
+      const float* src = part + (size_t)(r - 1) * BN * TC_BM + row;
+#pragma unroll
+      for (int j = 0; j < BN; j++) v[j] += src[j * TC_BM];
+    }
+    const int n = tile * TC_BM + row;
+#pragma unroll
+    for (int c0 = 0; c0 < BN; c0 += CW) {
+      float o[CW];
+#pragma unroll
+      for (int j = 0; j < CW; j++) o[j] = v[c0 + j];
+      sk_store<EPI, CW>(P, n, c0, o);
+    }
+  }
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
@@ -971,7 +1141,16 @@ gemm_tc_fixup_kernel(const SkParams P, int G) {
   const int first_c = c1 - 1;
   const int last_c = sk_owner((tile + 1) * P.n_kb - 1, G, P.total_kb);
   const int col = (threadIdx.x & 31) * 4;
+  // The tile is the first of every CTA after first_c (slot 0); for first_c it is the first one only if that CTA's
+  // stretch begins exactly with it (it cannot begin later: then an earlier block would have taken the tile).
+  const int slot_first = (sk_begin(first_c, G, P.total_kb) == tile * P.n_kb) ? 0 : 1;
+  const int n = tile * TC_BM + col;
+  const size_t idx = (size_t)m * P.ldo + n;
+  // adding into float32: the old values are asked for together with the partial sums, not after them
+  const bool add_wide = EPI == 1 && n + 3 < P.N && ((reinterpret_cast<uintptr_t>((float*)P.out + idx) & 15) == 0);
   pdl_wait();
+  float4 old = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (add_wide) old = __ldcg(reinterpret_cast<const float4*>((const float*)P.out + idx));
   float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int c0 = first_c; c0 <= last_c; c0 += 8) {
     float4 a[8];
@@ -979,7 +1158,7 @@ gemm_tc_fixup_kernel(const SkParams P, int G) {
     for (int j = 0; j < 8; j++) {
       const int cc = c0 + j;
       if (cc <= last_c) {
-        const int slot = (sk_begin(cc, G, P.total_kb) / P.n_kb == tile) ? 0 : 1;
+        const int slot = cc == first_c ? slot_first : 0;
         a[j] = __ldcg(reinterpret_cast<const float4*>(P.scratch + ((size_t)(cc * 2 + slot) * BN + m) * TC_BM + col));
       } else {
         a[j] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -990,8 +1169,86 @@ gemm_tc_fixup_kernel(const SkParams P, int G) {
       if (c0 + j <= last_c) { v.x += a[j].x; v.y += a[j].y; v.z += a[j].z; v.w += a[j].w; }
     }
   }
-  fixup_store<EPI>(P, m, tile * TC_BM + col, v);
+  if (add_wide) {
+    if (P.bias) { v.x += P.bias[n]; v.y += P.bias[n + 1]; v.z += P.bias[n + 2]; v.w += P.bias[n + 3]; }
+    *reinterpret_cast<float4*>((float*)P.out + idx) = make_float4(old.x + v.x, old.y + v.y, old.z + v.z, old.w + v.w);
+    return;
+  }
+  fixup_store<EPI>(P, m, n, v);
 }
+
+// Clusters of `cs` CTAs of the cluster kernel that can be resident at once (0: none, or the query failed).
+template <int BN, int STAGES, int EPI>
+static int clusterk_resident(int cs) {
+  static int cached[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
+  if (cs < 1 || cs > 8) return 0;
+  if (cached[cs] < 0) {
+    auto kern = gemm_tc_clusterk_kernel<BN, STAGES, EPI>;
+    const size_t smem = sizeof(SkSmem<BN, STAGES>) + 1024;
+    cached[cs] = 0;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess) {
+      cudaLaunchConfig_t q = {};
+      q.gridDim = dim3((sm_count() / cs) * cs); q.blockDim = dim3(TC_THREADS); q.dynamicSmemBytes = smem;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = cs; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+      q.attrs = attr; q.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kern, &q) == cudaSuccess && n > 0) cached[cs] = n;
+      else cudaGetLastError();
+    }
+  }
+  return cached[cs];
+}
+
+// The cluster size with which `tiles` clusters fill most SMs in one wave, or 0 if there is none: the partial tiles
+// must fit into rank 0's ring, every rank needs a k-block, and all clusters must be resident together.
+template <int BN, int STAGES, int EPI>
+static int clusterk_size(int tiles, int n_kb) {
+  const int sms = sm_count();
+  if (tiles > sms) return 0;
+  for (int cs = sms / tiles > 8 ? 8 : sms / tiles; cs >= 1; cs--) {
+    if (tiles * cs * 10 < sms * 8) break;                       // too few SMs at work: the even split is better
+    if (cs > n_kb || (size_t)(cs - 1) * BN * TC_BM * sizeof(float) > (size_t)STAGES * TC_BM * TC_BK * sizeof(bf16)) continue;
+    if (clusterk_resident<BN, STAGES, EPI>(cs) >= tiles) return cs;
+  }
+  return 0;
+}
+
+static int clusterk_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("STRATUM_GEMM_CLUSTERK");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on;
+}
+
+template <int BN, int STAGES, int EPI>
+static int launch_clusterk(const CUtensorMap& mw, const CUtensorMap& mx, const SkParams& P, int cs,
+                           cudaStream_t stream) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(P.tiles * cs);
+  cfg.blockDim = dim3(TC_THREADS);
+  cfg.dynamicSmemBytes = sizeof(SkSmem<BN, STAGES>) + 1024;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = cs; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  g_last_launches = 1;
+  return (int)cudaLaunchKernelEx(&cfg, gemm_tc_clusterk_kernel<BN, STAGES, EPI>, mw, mx, P);
+}
+
+// The cluster form up to this many (padded) rows of x.  Measured in whole decode steps on the Llama-8B shapes: ahead
+// at 16 rows (4.63 against 4.79 ms), behind at 32 and 64 (6.40 against 6.28, 9.48 against 9.19 ms), where rank 0
+// alone adds and stores a tile that is two and four times as wide.
+#ifndef CLUSTERK_MAX_BN
+#define CLUSTERK_MAX_BN 16
+#endif
 
 #ifndef SK_RING_16
 #define SK_RING_16 10
@@ -1009,6 +1266,12 @@ static int launch_streamk(const CUtensorMap& mw, const CUtensorMap& mx, const Sk
   const bool split_tiles = !(P.tiles % grid == 0);
 #define SK_LAUNCH(E)                                                                                        \
   {                                                                                                         \
+    if constexpr (BN <= CLUSTERK_MAX_BN) {                                                                  \
+      if (split_tiles && clusterk_enabled()) {                                                              \
+        const int cs = clusterk_size<BN, STAGES, E>(P.tiles, P.n_kb);                                       \
+        if (cs > 0) return launch_clusterk<BN, STAGES, E>(mw, mx, P, cs, stream);                           \
+      }                                                                                                     \
+    }                                                                                                       \
     auto kern = gemm_tc_streamk_kernel<BN, STAGES, E>;                                                      \
     static bool configured = false;                                                                         \
     if (!configured) {                                                                                      \

@@ -40,9 +40,12 @@ def run(att, qkv: torch.Tensor, cache, step, out: torch.Tensor) -> None:
     head_groups = (gs + 15) // 16
     if (step.all_single and hd in (64, 128) and gs <= 8 and step.n_tokens <= 1024
             and os.environ.get("STRATUM_ATTENTION_STREAM", "1") != "0"):
-        # decode steps: the pages of all sequences spread evenly over the SMs, streamed by TMA
+        # decode steps: the pages of all sequences spread evenly over the SMs, streamed by TMA.  With more than
+        # two sequences the kernels after it get a head start while the last pages stream in (3 % of a step on
+        # the Llama-8B shape at 8 sequences); with one or two it costs more than it gives (measured)
         K.attention_stream(qkv, cache.k, cache.v, step.token_pos, step.token_seq, cache.block_table, out,
-                           att.n_heads, att.n_kv_heads, hd, PAGE_TOKENS, att.window, att.scale)
+                           att.n_heads, att.n_kv_heads, hd, PAGE_TOKENS, att.window, att.scale,
+                           late_trigger=step.n_tokens > 2)
     elif step.all_single:
         n_splits, chunk = plan_splits(step.n_tokens * att.n_kv_heads * head_groups, step.max_len)
         part_o = part_ml = None

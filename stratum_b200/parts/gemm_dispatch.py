@@ -18,14 +18,14 @@ from .. import kernels as K
 
 STORE, ADD_TO_F32, STORE_F32, SWIGLU = K.EPI_STORE, K.EPI_ADD_F32, K.EPI_STORE_F32, K.EPI_SWIGLU
 
-# rows of x up to which the weight-streaming mma.sync kernel is used.  Measured in whole decode steps on the
-# Llama-8B layer shapes: one and two rows are faster with it (one kernel, no second pass), from four rows on the
-# stream-K tcgen05 kernel wins (3.96 against 4.10 ms at four rows).  STRATUM_SKINNY_MAX_ROWS overrides it for
-# measurements.
+# rows of x up to which the weight-streaming mma.sync kernel is used, for weight matrices of fewer than
+# STREAMK_MIN_WEIGHTS elements: larger ones go to the tcgen05 kernels whatever the rows, whose TMA ring keeps more
+# bytes in flight.  Measured in whole decode steps of one sequence: on the Llama-8B shapes 3.36 ms with the
+# threshold at 20 M elements (the output projection alone on the mma.sync kernel), 3.43 ms with every product on
+# tcgen05, 3.61 ms with every product on mma.sync; on the Llama-3.2-1B shapes 0.93, 1.07 and 0.92 ms.  From four
+# rows on the tcgen05 kernels win everywhere.  Both can be set in the environment for measurements.
 SKINNY_MAX_ROWS = int(os.environ.get("STRATUM_SKINNY_MAX_ROWS", 2))
-# weight matrices of at least this many elements go to the stream-K kernel even for few rows of x: its TMA
-# ring keeps more bytes in flight, which pays once the matrix is large enough to amortise its set-up
-STREAMK_MIN_WEIGHTS = int(os.environ.get("STRATUM_STREAMK_MIN_WEIGHTS", 400_000_000))
+STREAMK_MIN_WEIGHTS = int(os.environ.get("STRATUM_STREAMK_MIN_WEIGHTS", 20_000_000))
 
 
 def _aligned(x: torch.Tensor, w: torch.Tensor) -> bool:

@@ -146,7 +146,9 @@ def test_gemm_skinny(M, N, K_):
                                      (1280, 4608, 8192),
                                      # pairs of CTAs on 256 x 256 tiles: rows and columns that end inside a tile, more
                                      # tiles than pairs of SMs, one row of tiles
-                                     (1000, 2100, 264), (256, 28672, 128), (2304, 9000, 72)])
+                                     (1000, 2100, 264), (256, 28672, 128), (2304, 9000, 72),
+                                     # few rows, no more tiles than SMs: k shared inside clusters of 4, 3, 8 and 1 CTAs
+                                     (40, 4096, 2048), (30, 5120, 1000), (3, 2304, 1032), (8, 16000, 520)])
 def test_gemm_tc(M, N, K_):
     from stratum_b200 import kernels as K
     rng = np.random.default_rng(M + N + K_)
@@ -553,6 +555,12 @@ def _run_stream(c, n_q, n_kv, hd, window=0, pad_rows=0):
     K.attention_stream(qkv, c["kc"], c["vc"], pos, seq, c["table"], out, n_q, n_kv, hd, 64, window,
                        1.0 / math.sqrt(hd))
     K.check_status()
+    # when the kernels after it may start changes nothing in the result
+    early = torch.zeros_like(out)
+    K.attention_stream(qkv, c["kc"], c["vc"], pos, seq, c["table"], early, n_q, n_kv, hd, 64, window,
+                       1.0 / math.sqrt(hd), late_trigger=False)
+    K.check_status()
+    assert torch.equal(early, out)
     return out
 
 
