@@ -15,7 +15,10 @@
 //            epilogue of one tile overlap the k-loop of the next.
 //
 // Tiles that would form a last, partly filled wave are cut along k and shared by all CTAs (see TcSchedule).
-// Up to 128 rows of x take the stream-K form further down, with the roles of x and W exchanged.
+// Further down: the same on pairs of CTAs (tcgen05.mma.cta_group::2, 256-row tiles) for prompts; for up to 128
+// rows of x the stream-K form with the roles of x and W exchanged; and for up to 16 rows and few tiles the
+// form that shares k inside a cluster and adds the partial tiles through distributed shared memory.
+// stratum_gemm_tc at the end chooses among them from the shapes.
 //
 // Every wait on an mbarrier is bounded.  If one runs out, the kernel records where in a status
 // word, tells its other warps through shared memory, lets copies in flight land, frees its tensor
@@ -552,7 +555,6 @@ struct SkParams {
   void* out;
   int* status;
   float* scratch;         // [gridDim.x][2][BN][128] float32 partial tiles (first / last tile of a CTA's stretch)
-  unsigned* counters;     // unused (kept for the entry point's signature)
   int M, N, K, ldo;
   int tiles, n_kb, total_kb;
 };
@@ -1296,18 +1298,17 @@ static int launch_streamk(const CUtensorMap& mw, const CUtensorMap& mx, const Sk
 
 STRATUM_EXPORT int stratum_gemm_tc_last_launches(void) { return g_last_launches; }
 
-// Scratch for partial tiles (two 128 x 256 float32 tiles per SM cover both forms); the counters are unused.
+// Scratch for partial tiles (two 128 x 256 float32 tiles per SM cover both forms).
 STRATUM_EXPORT long long stratum_gemm_tc_scratch_floats(void) { return (long long)sm_count() * 2 * 256 * TC_BM; }
-STRATUM_EXPORT long long stratum_gemm_tc_counters(int N) { (void)N; return (long long)sm_count(); }
 
 // x: bf16 [M][ldx], w: bf16 [N][K], bias float32 [N] or null, out [M][ldo] (SwiGLU: [M][N/2]).
 // scratch: partial tiles of tiles shared between CTAs (see stratum_gemm_tc_scratch_floats).  Without it more than
-// 128 rows of x still work (no tile is shared then); up to 128 rows need it.  counters: unused, kept for callers.
+// 128 rows of x still work (no tile is shared then); up to 128 rows need it.
 // status: one int in device memory, 0 before the call; non-zero afterwards means a wait inside the kernel ran out.
 // Needs K % 8 == 0, ldx % 8 == 0, 16-byte aligned x and w (a TMA copy starts on a 16-byte boundary and its
 // row pitch is a multiple of 16 bytes; the k coordinate of every copy here is a multiple of 64).
 STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bias, void* out, int epilogue, int M,
-                                   int N, int K, int ldx, int ldo, int* status, float* scratch, unsigned* counters,
+                                   int N, int K, int ldx, int ldo, int* status, float* scratch,
                                    cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldx < K) return STRATUM_ERR_SHAPE;
@@ -1350,12 +1351,12 @@ STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bi
     return launch_tc<128, 6>(ma, mb, P, epilogue, tiles_m * ((N + 127) / 128), n_kb, tiles_m, scratch, stream);
   }
   // few rows of x: tiles of 128 rows of W by all rows of x, k-blocks spread evenly over the SMs
-  if (!scratch || !counters) return STRATUM_ERR_SHAPE;
+  if (!scratch) return STRATUM_ERR_SHAPE;
   const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
   if ((st = make_map(&ma, w, N, K, K, TC_BM)) != 0) return st;
   if ((st = make_map(&mb, x, M, K, ldx, bn)) != 0) return st;
   SkParams Q;
-  Q.bias = bias; Q.out = out; Q.status = status; Q.scratch = scratch; Q.counters = counters;
+  Q.bias = bias; Q.out = out; Q.status = status; Q.scratch = scratch;
   Q.M = M; Q.N = N; Q.K = K; Q.ldo = ldo;
   Q.tiles = (N + TC_BM - 1) / TC_BM;
   Q.n_kb = (K + TC_BK - 1) / TC_BK;

@@ -242,32 +242,28 @@ def check_status() -> None:
 _gemm_scratch = None
 
 
-def _gemm_tc_scratch(n_out: int, device):
-    """(partial tiles, per-tile counters) of the stream-K form; counters are zero between launches."""
+def _gemm_tc_scratch(device):
+    """float32 scratch for the partial tiles of tiles that several CTAs share."""
     global _gemm_scratch
-    tiles = (n_out + 127) // 128
-    if _gemm_scratch is None or _gemm_scratch[1].numel() < tiles:
+    if _gemm_scratch is None or _gemm_scratch.device != device:
         lib = build.load("gemm_tc")
         lib.stratum_gemm_tc_scratch_floats.restype = ctypes.c_longlong
-        floats = int(lib.stratum_gemm_tc_scratch_floats())
-        part = _gemm_scratch[0] if _gemm_scratch is not None else torch.empty(floats, dtype=torch.float32,
-                                                                                device=device)
-        _gemm_scratch = (part, torch.zeros(max(tiles, 2048), dtype=torch.int32, device=device))
+        _gemm_scratch = torch.empty(int(lib.stratum_gemm_tc_scratch_floats()), dtype=torch.float32, device=device)
     return _gemm_scratch
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
             epilogue: int) -> None:
-    """bfloat16 tile kernel on the 5th-generation tensor cores (TMA + tcgen05/TMEM); see EPI_*.
-    Up to 128 rows of x run in the stream-K form (every SM reads an equal share of w)."""
+    """bfloat16 matrix product on the 5th-generation tensor cores (TMA + tcgen05/TMEM); see EPI_*.  The form
+    (k shared inside clusters, stream-K, tiles, tiles on pairs of CTAs) is chosen from the shapes in gemm_tc.cu."""
     M, N, Kd = _linear_shapes(x, w, bias, out, epilogue, "gemm_tc")
     _need(x, "x", torch.bfloat16, contiguous=False)
-    part, counters = _gemm_tc_scratch(N, x.device)
+    part = _gemm_tc_scratch(x.device)
     f = _fn("gemm_tc", "stratum_gemm_tc",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-             c_void_p, c_void_p])
+             c_void_p])
     _check(f(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), epilogue, M, N, Kd, x.stride(0), out.stride(0),
-             _ptr(status_word()), _ptr(part), _ptr(counters), _stream()), "gemm_tc")
+             _ptr(status_word()), _ptr(part), _stream()), "gemm_tc")
     count_launches(build.load("gemm_tc").stratum_gemm_tc_last_launches() - 1)      # a second pass, if there was one
 
 
