@@ -17,6 +17,7 @@
 
 #define SAMPLE_THREADS 1024
 #define SAMPLE_CAND_MAX 512
+static_assert(SAMPLE_THREADS == 1024 && SAMPLE_CAND_MAX % 32 == 0, "the sampling kernel counts on 32 warps");
 
 struct MaxIdx { float v; int i; };
 
@@ -52,12 +53,37 @@ __device__ __forceinline__ MaxIdx block_argmax(MaxIdx mine, MaxIdx* scratch /* 3
   return scratch[32];
 }
 
+// f(i, logit) for every logit of the row, 16 bytes per load where the row allows it.  A thread meets its ids in
+// ascending order; which thread meets which id depends on the row's alignment, so only order-free work goes here.
+template <typename F>
+__device__ __forceinline__ void for_each_logit(const float* __restrict__ row, int vocab, F f) {
+  if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const int n4 = vocab >> 2;
+    // four loads in flight per thread before the first is used (one block reads a whole row: latency bounds it)
+    for (int q0 = threadIdx.x; q0 < n4; q0 += 4 * blockDim.x) {
+      float4 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int q = q0 + j * blockDim.x;
+        if (q < n4) v[j] = ld_fresh(reinterpret_cast<const float4*>(row) + q);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int q = q0 + j * blockDim.x;
+        if (q < n4) { f(4 * q, v[j].x); f(4 * q + 1, v[j].y); f(4 * q + 2, v[j].z); f(4 * q + 3, v[j].w); }
+      }
+    }
+    for (int i = 4 * n4 + threadIdx.x; i < vocab; i += blockDim.x) f(i, ld_fresh(row + i));
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) f(i, ld_fresh(row + i));
+  }
+}
+
 __device__ __forceinline__ MaxIdx row_argmax(const float* __restrict__ row, int vocab, MaxIdx* scratch) {
   MaxIdx mine{-INFINITY, 0x7fffffff};
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    const float v = ld_fresh(row + (i));
+  for_each_logit(row, vocab, [&](int i, float v) {
     if (v > mine.v) { mine.v = v; mine.i = i; }      // ascending i per thread: first of equals is kept
-  }
+  });
   MaxIdx r = block_argmax(mine, scratch);
   if (r.i == 0x7fffffff) { r.i = 0; r.v = ld_fresh(row + (0)); }  // every logit is -inf or NaN: index 0, as a scalar scan would give
   return r;
@@ -145,6 +171,7 @@ STRATUM_EXPORT int stratum_argmax(const float* logits, int ld, int n_rows, int v
 // ---------------------------------------------------------------- temperature sampling
 // Per-row parameters (so one launch serves sequences with different settings):
 //   temperature[r] <= 0 -> greedy;  top_k[r] <= 0 -> off;  top_p[r] >= 1 -> off;  uniform[r] in [0,1).
+// Every sum is taken in an order that depends on the sizes only, so a row's pick is the same in every batch and run.
 
 // order-preserving map float -> uint32 (larger float, larger key)
 __device__ __forceinline__ uint32_t float_key(float f) {
@@ -152,20 +179,68 @@ __device__ __forceinline__ uint32_t float_key(float f) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+// Inclusive prefix sum over the lanes of a warp (lane 0 first).
+template <typename T>
+__device__ __forceinline__ T warp_incl_scan(T v) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const T t = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += t;
+  }
+  return v;
+}
+
+template <typename T>
+__device__ __forceinline__ T warp_sum(T v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ int warp_min(int v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Exclusive prefix sum of one value per thread over the block (thread 0 first); *total gets the sum of all.
+// scratch: 33 values.  Every thread of the block calls it.
+template <typename T>
+__device__ __forceinline__ T block_excl_scan(T v, T* scratch, T* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  const T incl = warp_incl_scan(v);
+  __syncthreads();
+  if (lane == 31) scratch[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    const T w = lane < n_warps ? scratch[lane] : T(0);
+    const T wi = warp_incl_scan(w);
+    scratch[lane] = wi - w;
+    if (lane == 31) scratch[32] = wi;
+  }
+  __syncthreads();
+  *total = scratch[32];
+  return scratch[warp] + incl - v;
+}
+
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ uniform,
               int* __restrict__ ids, float* __restrict__ values) {
   __shared__ MaxIdx mi_scratch[33];
-  __shared__ float partial[SAMPLE_THREADS];
+  __shared__ float f_scratch[33];
+  __shared__ unsigned u_scratch[33];
+  __shared__ float cand_e[SAMPLE_CAND_MAX];
   __shared__ unsigned hist[256];
   __shared__ float cand_v[SAMPLE_CAND_MAX];
   __shared__ int cand_i[SAMPLE_CAND_MAX];
   __shared__ unsigned sh_prefix, sh_remaining, sh_count, sh_equal_total;
+  __shared__ int sh_owner;
 
   pdl_trigger();
   pdl_wait();
-  const int r = blockIdx.x, tid = threadIdx.x;
+  const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* row = logits + (size_t)r * ld;
   const float temp = temperature[r];
   const MaxIdx best = row_argmax(row, vocab, mi_scratch);
@@ -180,43 +255,69 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
   const bool filtered = (k > 0) || (tp < 1.0f);
 
   if (!filtered) {
-    // every id in id order: thread i owns the contiguous ids [i*chunk, (i+1)*chunk)
-    const int chunk = (vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
-    const int b = tid * chunk, e = min(vocab, b + chunk);
+    // Every id in id order.  Warp w owns the contiguous ids [w*seg, (w+1)*seg) and reads them 32 at a time; the
+    // warps' sums are added in warp order, which gives the warp that holds the draw; that warp then walks its
+    // stretch again, 32 ids at a time, until the running sum passes the draw.
+    const int n_warps = SAMPLE_THREADS / 32;
+    const int seg = (((vocab + n_warps - 1) / n_warps) + 31) & ~31;
+    const int b = min(vocab, warp * seg), e = min(vocab, b + seg);
     float s = 0.f;
-    for (int i = b; i < e; i++) s += expf((ld_fresh(row + (i)) - best.v) * inv_t);
-    partial[tid] = s;
+    for (int i = b + lane; i < e; i += 32) s += expf((ld_fresh(row + i) - best.v) * inv_t);
+    s = warp_sum(s);
     __syncthreads();
-    if (tid == 0) {
-      // serial over 1024 partial sums: fixed order, exact same total for the same row every time
-      float total = 0.f;
-      for (int i = 0; i < SAMPLE_THREADS; i++) total += partial[i];
+    if (lane == 0) f_scratch[warp] = s;
+    if (tid == 0) sh_owner = -1;
+    __syncthreads();
+    if (warp == 0) {
+      const float w = f_scratch[lane];                 // n_warps == 32
+      const float incl = warp_incl_scan(w);
+      const float total = __shfl_sync(0xffffffffu, incl, 31);
       const float target = u * total;
-      float cum = 0.f;
-      int owner = -1;
-      for (int i = 0; i < SAMPLE_THREADS; i++) {
-        if (target < cum + partial[i]) { owner = i; break; }
-        cum += partial[i];
+      const unsigned hit = __ballot_sync(0xffffffffu, target < incl);
+      if (lane == 0) {
+        sh_owner = hit ? (__ffs(hit) - 1) : -1;
+        f_scratch[32] = target;
       }
-      int pick = vocab - 1;
-      if (owner >= 0) {
-        const int ob = owner * chunk, oe = min(vocab, ob + chunk);
-        pick = oe - 1;
-        for (int i = ob; i < oe; i++) {
-          cum += expf((ld_fresh(row + (i)) - best.v) * inv_t);
-          if (target < cum) { pick = i; break; }
+      f_scratch[lane] = incl - w;                      // the sum of the warps before
+    }
+    __syncthreads();
+    const int owner = sh_owner;
+    if (owner < 0) {                                   // rounding left no warp: the last id
+      if (tid == 0) { ids[r] = vocab - 1; if (values) values[r] = ld_fresh(row + (vocab - 1)); }
+      return;
+    }
+    if (warp != owner) return;
+    const float target = f_scratch[32];
+    float carry = f_scratch[owner];
+    int pick = e - 1;                                  // rounding left no id in the stretch: its last
+    for (int base = b; base < e; base += 4 * 32) {
+      float x[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const int i = base + 32 * j + lane;
+        x[j] = i < e ? expf((ld_fresh(row + i) - best.v) * inv_t) : 0.f;
+      }
+      bool found = false;
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        if (!found) {
+          const float incl = carry + warp_incl_scan(x[j]);
+          const unsigned hit = __ballot_sync(0xffffffffu, target < incl && base + 32 * j + lane < e);
+          if (hit) { pick = base + 32 * j + __ffs(hit) - 1; found = true; }
+          carry = __shfl_sync(0xffffffffu, incl, 31);
         }
       }
-      ids[r] = pick;
-      if (values) values[r] = ld_fresh(row + (pick));
+      if (found) break;
     }
+    if (lane == 0) { ids[r] = pick; if (values) values[r] = ld_fresh(row + pick); }
     return;
   }
 
   // ---- filtered: the k largest logits, k <= SAMPLE_CAND_MAX
   if (k <= 0 || k > SAMPLE_CAND_MAX) k = SAMPLE_CAND_MAX;
   if (k > vocab) k = vocab;
-  // radix select, 8 bits a pass from the top: find the key of the k-th largest
+  // radix select, 8 bits a pass from the top: find the key of the k-th largest.  Lanes that meet the same bucket
+  // add to it once (the first pass sees nearly every logit in two or three buckets).
   if (tid == 0) { sh_prefix = 0; sh_remaining = (unsigned)k; }
   __syncthreads();
   for (int pass = 0; pass < 4; pass++) {
@@ -225,10 +326,14 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
     __syncthreads();
     const unsigned prefix = sh_prefix;
     const unsigned mask = pass == 0 ? 0u : (0xFFFFFFFFu << (shift + 8));
-    for (int i = tid; i < vocab; i += blockDim.x) {
-      const uint32_t key = float_key(ld_fresh(row + (i)));
-      if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
-    }
+    for_each_logit(row, vocab, [&](int, float v) {
+      const uint32_t key = float_key(v);
+      if ((key & mask) == prefix) {
+        const unsigned bucket = (key >> shift) & 255u;
+        const unsigned peers = __match_any_sync(__activemask(), bucket);
+        if (__ffs(peers) - 1 == lane) atomicAdd(&hist[bucket], (unsigned)__popc(peers));
+      }
+    });
     __syncthreads();
     if (tid == 0) {
       unsigned remaining = sh_remaining;
@@ -246,27 +351,37 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
   const uint32_t kth_key = sh_prefix;       // key of the k-th largest logit
   const unsigned n_equal_wanted = sh_remaining;
   // gather: everything above the k-th key, then the lowest ids among those equal to it.  When all
-  // the equal ones are wanted (no tie straddles the cut) they are gathered in the same parallel pass.
+  // the equal ones are wanted (no tie straddles the cut) they are gathered in the same pass.
   const bool take_all_equal = sh_equal_total == n_equal_wanted;
   if (tid == 0) sh_count = 0;
   __syncthreads();
-  for (int i = tid; i < vocab; i += blockDim.x) {
-    const uint32_t key = float_key(ld_fresh(row + (i)));
+  for_each_logit(row, vocab, [&](int i, float v) {
+    const uint32_t key = float_key(v);
     if (key > kth_key || (take_all_equal && key == kth_key)) {
       const unsigned slot = atomicAdd(&sh_count, 1u);
-      cand_v[slot] = ld_fresh(row + (i));
+      cand_v[slot] = v;
       cand_i[slot] = i;
     }
-  }
+  });
   __syncthreads();
-  if (tid == 0 && !take_all_equal) {
-    unsigned slot = sh_count, taken = 0;
-    for (int i = 0; i < vocab && taken < n_equal_wanted; i++) {
-      if (float_key(ld_fresh(row + (i))) == kth_key) { cand_v[slot] = ld_fresh(row + (i)); cand_i[slot] = i; slot++; taken++; }
+  if (!take_all_equal) {
+    // a tie straddles the cut: thread t counts the equal ones among its contiguous ids, the counts are summed in
+    // thread order, and the first n_equal_wanted of them in id order are taken
+    const unsigned above = sh_count;
+    const int chunk = (vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
+    const int b = min(vocab, tid * chunk), e = min(vocab, b + chunk);
+    unsigned mine = 0;
+    for (int i = b; i < e; i++) mine += float_key(ld_fresh(row + i)) == kth_key;
+    unsigned all;
+    unsigned rank = block_excl_scan(mine, u_scratch, &all);
+    for (int i = b; i < e && rank < n_equal_wanted; i++) {
+      const float v = ld_fresh(row + i);
+      if (float_key(v) == kth_key) { cand_v[above + rank] = v; cand_i[above + rank] = i; rank++; }
     }
-    sh_count = slot;
+    __syncthreads();
+    if (tid == 0) sh_count = above + n_equal_wanted;
+    __syncthreads();
   }
-  __syncthreads();
   const int n_cand = (int)sh_count;        // == k
   // pad to a power of two and sort: descending logit, ascending id among equals (bitonic, in shared memory)
   int n_sort = 1;
@@ -289,28 +404,50 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
       __syncthreads();
     }
   }
-  if (tid == 0) {
-    // probabilities over the candidates, top-p cut, renormalised draw: all serial over <= 512 entries
-    const float top = cand_v[0];
-    double sum = 0.0;
-    for (int i = 0; i < n_cand; i++) sum += (double)expf((cand_v[i] - top) * inv_t);
-    int keep = n_cand;
-    if (tp < 1.0f) {
-      double cum = 0.0;
-      for (int i = 0; i < n_cand; i++) {
-        cum += (double)(float)((double)expf((cand_v[i] - top) * inv_t) / sum);
-        if (cum >= (double)tp) { keep = i + 1; break; }
-      }
+  // weights of the candidates, then (one warp, lane l holding the 16 consecutive candidates from 16 l on, sums
+  // in float64): their total, the top-p cut over the normalised weights, and the draw among what is kept
+  const float top = cand_v[0];
+  for (int i = tid; i < SAMPLE_CAND_MAX; i += blockDim.x) cand_e[i] = i < n_cand ? expf((cand_v[i] - top) * inv_t) : 0.f;
+  __syncthreads();
+  if (warp != 0) return;
+  constexpr int PER = SAMPLE_CAND_MAX / 32;
+  const int c0 = lane * PER;
+  double own = 0.0;
+#pragma unroll
+  for (int j = 0; j < PER; j++) own += (double)cand_e[c0 + j];
+  const double sum = warp_sum(own);
+  int keep = n_cand;
+  if (tp < 1.0f) {
+    double q[PER], own_q = 0.0;
+#pragma unroll
+    for (int j = 0; j < PER; j++) { q[j] = (double)(float)((double)cand_e[c0 + j] / sum); own_q += q[j]; }
+    double cum = warp_incl_scan(own_q) - own_q;
+    int first = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+      cum += q[j];
+      if (first == 0x7fffffff && c0 + j < n_cand && cum >= (double)tp) first = c0 + j;
     }
-    double kept = 0.0;
-    for (int i = 0; i < keep; i++) kept += (double)expf((cand_v[i] - top) * inv_t);
-    const double target = (double)u * kept;
-    double cum = 0.0;
-    int pick = keep - 1;
-    for (int i = 0; i < keep; i++) {
-      cum += (double)expf((cand_v[i] - top) * inv_t);
-      if (target < cum) { pick = i; break; }
+    first = warp_min(first);
+    if (first != 0x7fffffff) keep = first + 1;
+  }
+  double own_kept = 0.0;
+#pragma unroll
+  for (int j = 0; j < PER; j++) own_kept += (c0 + j < keep) ? (double)cand_e[c0 + j] : 0.0;
+  const double kept = warp_sum(own_kept);
+  const double target = (double)u * kept;
+  double cum = warp_incl_scan(own_kept) - own_kept;
+  int first = 0x7fffffff;
+#pragma unroll
+  for (int j = 0; j < PER; j++) {
+    if (c0 + j < keep) {
+      cum += (double)cand_e[c0 + j];
+      if (first == 0x7fffffff && target < cum) first = c0 + j;
     }
+  }
+  first = warp_min(first);
+  const int pick = first == 0x7fffffff ? keep - 1 : first;
+  if (lane == 0) {
     ids[r] = cand_i[pick];
     if (values) values[r] = cand_v[pick];
   }
