@@ -14,7 +14,7 @@ and writes tests/golden/tiny_llama_reference.npz holding
     every position the oracle processed.
 tests/test_plain_reference.py compares the plain oracle with these files.
 
-Usage:  python tests/golden/make_golden.py [--reference /path/to/reference/checkout]
+Usage:  python tests/golden/make_golden.py --reference /path/to/reference/checkout
 """
 import argparse
 import importlib.util
@@ -57,9 +57,12 @@ def load_module(path, name):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("STRATUM_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("STRATUM_REFERENCE"),
+                    help="checkout of shiaho777/stratum (or set STRATUM_REFERENCE)")
     ap.add_argument("--layers", type=int, default=4)
     args = ap.parse_args()
+    if not args.reference:
+        ap.error("give --reference DIR (a checkout of shiaho777/stratum) or set STRATUM_REFERENCE")
     tools = os.path.join(args.reference, "stratum", "tools")
     tmp = tempfile.mkdtemp(prefix="golden_")
     gguf = os.path.join(tmp, "tiny.gguf")
