@@ -1,8 +1,8 @@
 """Which matrix-product kernel serves a given call.
 
 float32 always takes the CUDA-core kernel with the fixed summation order (the true 32-bit
-path).  bfloat16: up to SKINNY_MAX_ROWS rows of x take the weight-streaming kernel (decode
-steps of one or two sequences), more rows the tcgen05 kernels of gemm_tc.cu (stream-K for
+path).  bfloat16: up to SKINNY_MAX_ROWS rows of x and a small weight matrix take the weight-streaming kernel
+(decode steps of a few sequences), more rows the tcgen05 kernels of gemm_tc.cu (stream-K for
 decode steps and short prompts, tiles on pairs of CTAs or on single CTAs for prompts; the
 choice among those is made there, from the shapes), and any shape either refuses (rows not
 16-byte aligned) falls back to the CUDA-core kernel.
@@ -22,9 +22,10 @@ STORE, ADD_TO_F32, STORE_F32, SWIGLU = K.EPI_STORE, K.EPI_ADD_F32, K.EPI_STORE_F
 # STREAMK_MIN_WEIGHTS elements: larger ones go to the tcgen05 kernels whatever the rows, whose TMA ring keeps more
 # bytes in flight.  Measured in whole decode steps of one sequence: on the Llama-8B shapes 3.36 ms with the
 # threshold at 20 M elements (the output projection alone on the mma.sync kernel), 3.43 ms with every product on
-# tcgen05, 3.61 ms with every product on mma.sync; on the Llama-3.2-1B shapes 0.93, 1.07 and 0.92 ms.  From four
-# rows on the tcgen05 kernels win everywhere.  Both can be set in the environment for measurements.
-SKINNY_MAX_ROWS = int(os.environ.get("STRATUM_SKINNY_MAX_ROWS", 2))
+# tcgen05, 3.61 ms with every product on mma.sync; on the Llama-3.2-1B shapes 0.93, 1.07 and 0.92 ms.  With four
+# rows the output projection is still ahead on mma.sync (3.64 against 3.69 ms a step), with eight it is not (4.00
+# against 3.99).  Both can be set in the environment for measurements.
+SKINNY_MAX_ROWS = int(os.environ.get("STRATUM_SKINNY_MAX_ROWS", 4))
 STREAMK_MIN_WEIGHTS = int(os.environ.get("STRATUM_STREAMK_MIN_WEIGHTS", 20_000_000))
 
 
