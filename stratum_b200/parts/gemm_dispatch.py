@@ -23,9 +23,11 @@ STORE, ADD_TO_F32, STORE_F32, SWIGLU = K.EPI_STORE, K.EPI_ADD_F32, K.EPI_STORE_F
 # bytes in flight.  Measured in whole decode steps of one sequence: on the Llama-8B shapes 3.36 ms with the
 # threshold at 20 M elements (the output projection alone on the mma.sync kernel), 3.43 ms with every product on
 # tcgen05, 3.61 ms with every product on mma.sync; on the Llama-3.2-1B shapes 0.93, 1.07 and 0.92 ms.  With four
-# rows the output projection is still ahead on mma.sync (3.64 against 3.69 ms a step), with eight it is not (4.00
-# against 3.99).  Both can be set in the environment for measurements.
-SKINNY_MAX_ROWS = int(os.environ.get("STRATUM_SKINNY_MAX_ROWS", 4))
+# rows the output projection is still ahead on mma.sync (3.64 against 3.69 ms a step), with eight it makes no
+# difference (4.00 against 3.99); on the Llama-3.2-1B shapes, where all but gate|up are that small, the step is
+# 8 to 11 % shorter with three to eight rows (1.20 against 1.29 ms at eight) and the same with sixteen.  Both can
+# be set in the environment for measurements.
+SKINNY_MAX_ROWS = int(os.environ.get("STRATUM_SKINNY_MAX_ROWS", 8))
 STREAMK_MIN_WEIGHTS = int(os.environ.get("STRATUM_STREAMK_MIN_WEIGHTS", 20_000_000))
 
 
