@@ -136,7 +136,9 @@ class SequencePages:
     def reserve(self, n_new: int) -> None:
         self.table.extend(self.pool.take(self.pages_needed(n_new)))
 
-    def advance(self, n_new: int) -> None:
+    def advance(self, n_new: int) -> bool:
+        """The sequence now holds n_new more positions.  True if that changed the page table (a windowed
+        group handed pages back)."""
         self.length += n_new
         if self.length > len(self.table) * PAGE_TOKENS:
             raise CacheMisuse("sequence advanced beyond its reserved pages")
@@ -147,6 +149,8 @@ class SequencePages:
                 self.pool.give(drop)
                 for i in range(first_needed):
                     self.table[i] = -1
+                return True
+        return False
 
     def release(self) -> None:
         self.pool.give([p for p in self.table if p >= 0])

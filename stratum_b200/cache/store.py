@@ -94,6 +94,7 @@ class SequenceCache:
                 g.pool = PagePool(self.n_pages)
         self._seq: Dict[int, List[Optional[SequencePages]]] = {}
         self._len: Dict[int, int] = {}
+        self.epoch = 0          # grows whenever a slot or a page changes hands: page tables copied earlier are stale
         if allocate:
             self._allocate()
 
@@ -107,7 +108,9 @@ class SequenceCache:
                 g.v = torch.zeros(shape, dtype=self.dtype, device=self.device)
             else:
                 dt = torch.float32 if g.spec.dtype == "float32" else self.dtype
-                g.state = torch.zeros((n, self.max_seqs) + tuple(g.spec.shape), dtype=dt, device=self.device)
+                # one row more than there are slots: row `max_seqs` belongs to no sequence; the padding rows of a
+                # step point there, so a mixer may update "their" state without harm to anyone's
+                g.state = torch.zeros((n, self.max_seqs + 1) + tuple(g.spec.shape), dtype=dt, device=self.device)
 
     def storage_bytes(self) -> int:
         total = 0
@@ -126,6 +129,7 @@ class SequenceCache:
             if g.state is not None:
                 g.state[:, slot].zero_()
         self._len[slot] = 0
+        self.epoch += 1
         return slot
 
     def length(self, slot: int) -> int:
@@ -154,14 +158,17 @@ class SequenceCache:
             if g.pool is None:
                 continue
             for s, n in zip(slots, n_new):
-                self._seq[s][gi].reserve(n)
+                sp = self._seq[s][gi]
+                if sp.pages_needed(n):
+                    sp.reserve(n)
+                    self.epoch += 1
 
     def advance(self, slots: Sequence[int], n_new: Sequence[int]) -> None:
         for s, n in zip(slots, n_new):
             self._need(s)
             for sp in self._seq[s]:
-                if sp is not None:
-                    sp.advance(n)
+                if sp is not None and sp.advance(n):
+                    self.epoch += 1
             self._len[s] += n
 
     def release(self, slot: int) -> None:
@@ -171,6 +178,7 @@ class SequenceCache:
                 sp.release()
         del self._len[slot]
         self.slots.release(slot)
+        self.epoch += 1
 
     def release_all(self) -> None:
         for s in self.slots.live():

@@ -92,27 +92,37 @@ class Stratum:
         return self.engine.step(entries)
 
     def decode_step(self, slots: Sequence[int], tokens: Sequence[int],
-                    sampling: SamplingParams = SamplingParams(), streams: Optional[Sequence[Pcg32]] = None):
+                    sampling: SamplingParams = SamplingParams(), streams: Optional[Sequence[Pcg32]] = None,
+                    with_logits: bool = False):
         """One token for each slot, picked on the device: (ids, logits of the ids) as host lists.  The step
-        runs as a replayed CUDA graph (or launch by launch when graphs are off)."""
+        runs as a replayed CUDA graph (or launch by launch when graphs are off).  with_logits: a third value,
+        the step's float32 logits [slots, vocab] on the device (valid until the next step)."""
         if self.graphs is None:
-            return self._backend.step_and_pick([(s, [t]) for s, t in zip(slots, tokens)], streams, sampling)
+            kept = []
+            self._backend.on_logits = (lambda lg, ids: kept.append(lg)) if with_logits else None
+            try:
+                ids, vals = self._backend.step_and_pick([(s, [t]) for s, t in zip(slots, tokens)], streams, sampling)
+            finally:
+                self._backend.on_logits = None
+            return (ids, vals, kept[0]) if with_logits else (ids, vals)
         uniforms = None if sampling.greedy else [st.uniform() for st in streams]
-        ids, vals, _ = self.graphs.step(slots, tokens, sampling.temperature, sampling.top_k, sampling.top_p, uniforms)
-        return ids, vals
+        ids, vals, c = self.graphs.step(slots, tokens, sampling.temperature, sampling.top_k, sampling.top_p, uniforms)
+        return (ids, vals, c.logits[:len(ids)]) if with_logits else (ids, vals)
 
     # -- generation ---------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens=16, stop_ids: Optional[Sequence[int]] = None,
                  sampling: SamplingParams = SamplingParams(), max_batch: Optional[int] = None,
                  on_token: Optional[Callable] = None, want_values: bool = False,
-                 on_logits: Optional[Callable] = None) -> List[GenerationResult]:
+                 on_logits: Optional[Callable] = None,
+                 stream_ids: Optional[Sequence[int]] = None) -> List[GenerationResult]:
         """stop_ids None: the configuration's eos ids; () : none.
-        on_logits(logits on the device [live sequences, vocab], picked ids) is called after every step."""
+        on_logits(logits on the device [live sequences, vocab], picked ids) is called after every step.
+        stream_ids: the random stream each request draws from (default: its index in this call)."""
         if stop_ids is None:
             stop_ids = tuple(getattr(self.config, "eos_token_ids", ()) or ())
         self._backend.on_logits = on_logits
         try:
             return generate(self._backend, prompts, max_new_tokens, stop_ids, sampling, max_batch, on_token,
-                            want_values)
+                            want_values, stream_ids)
         finally:
             self._backend.on_logits = None

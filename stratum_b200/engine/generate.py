@@ -76,16 +76,24 @@ def generate(backend: Backend, prompts: Sequence[Sequence[int]], max_new_tokens,
              stop_ids: Sequence[int] = (), params: SamplingParams = SamplingParams(),
              max_batch: Optional[int] = None,
              on_token: Optional[Callable[[int, int, int, int, float], None]] = None,
-             want_values: bool = False) -> List[GenerationResult]:
+             want_values: bool = False, stream_ids: Optional[Sequence[int]] = None) -> List[GenerationResult]:
     """Generate for every prompt.  max_new_tokens: one int or one per request.
-    on_token(request, index of the new token, token fed in, token picked, its logit)."""
+    on_token(request, index of the new token, token fed in, token picked, its logit).
+    stream_ids: which random stream of the seed each request draws from (default: its index in this call).
+    A request keeps its draws when it is given the same stream in another call, whatever else is in the
+    batch (the reference seeds stream s with seed + s * 0x9E3779B97F4A7C15,
+    stratum/native/stratum_arch_qwen35.inc.c:14010-14018)."""
     n_req = len(prompts)
     budgets = [int(max_new_tokens)] * n_req if isinstance(max_new_tokens, int) else [int(m) for m in max_new_tokens]
     if len(budgets) != n_req:
         raise ValueError("max_new_tokens: one value, or one per prompt")
     stop = set(int(s) for s in stop_ids)
     results = [GenerationResult(prompt_len=len(p)) for p in prompts]
-    streams = [Pcg32(params.seed, i) for i in range(n_req)]
+    if stream_ids is None:
+        stream_ids = range(n_req)
+    elif len(stream_ids) != n_req:
+        raise ValueError("stream_ids: one per prompt")
+    streams = [Pcg32(params.seed, int(i)) for i in stream_ids]
     for batch in plan_batches([len(p) for p in prompts], budgets, backend.n_pages, backend.max_seqs, max_batch):
         live = [i for i in batch if budgets[i] > 0]
         for i in batch:

@@ -19,6 +19,7 @@ import numpy as np
 import torch
 
 from ..cache.pages import PAGE_TOKENS, pages_for
+from .. import kernels as K
 from ..cache.store import KVSpec, SequenceCache
 from .model import Model
 
@@ -68,6 +69,129 @@ class StepBatch:
         return self._qblocks[tokens_per_block]
 
 
+class StepDescription:
+    """A step's description as one int32 buffer on the host and its copy on the device.
+
+    Both ways of running a step use this one builder: `Engine.step` makes a description of exactly the
+    step's size, a captured decode graph keeps one of a fixed size (rows padded, page tables of a fixed width)
+    and rewrites it before every replay.  A field that a new part needs is added here once.
+
+    Fields, in order: ids | pos | seq | want | slot | start | len | one page table per key/value group | extras.
+    Rows beyond the real tokens are padding: each is a sequence of its own with sequence index -1 (every kernel
+    that touches the cache skips it), position 0, length 0, an empty page table, and the slot number `max_seqs`,
+    which is a row of fixed-size state that belongs to no sequence.
+    """
+
+    def __init__(self, engine: "Engine", n_tokens: int, n_seqs: int, n_want: int, width: int,
+                 extras: Sequence = (), pinned: bool = False):
+        self.engine = engine
+        self.n_tokens, self.n_seqs, self.n_want, self.width = n_tokens, n_seqs, n_want, width
+        self.groups = engine.kv_groups
+        self.off: Dict[str, tuple] = {}
+        o = 0
+        for name, n in (("ids", n_tokens), ("pos", n_tokens), ("seq", n_tokens), ("want", n_want),
+                        ("slot", n_seqs), ("start", n_seqs + 1), ("len", n_seqs),
+                        ("tables", len(self.groups) * n_seqs * width)) + tuple(extras):
+            self.off[name] = (o, n)
+            o += n
+        self.total = o
+        self.host = torch.empty(o, dtype=torch.int32)
+        if pinned:
+            self.host = self.host.pin_memory()
+        self.np = self.host.numpy()
+        self.dev: Optional[torch.Tensor] = None
+        self.views = {name: self.np[a:a + n] for name, (a, n) in self.off.items()}
+        self.n_new: List[int] = []
+        self.single = True
+        self.before: Optional[List[int]] = None
+
+    def write_membership(self, slots: Sequence[int], n_new: Sequence[int], wants: Optional[Sequence[Sequence[int]]]):
+        """Who is in the step, with how many tokens each, whose logits are wanted and which pages they hold:
+        what stays the same from one decode step to the next until a sequence leaves or a page is taken.
+        wants None: every row's logits (the rows of a decode step)."""
+        v = self.views
+        B, T = len(slots), sum(n_new)
+        pad = self.n_tokens - T
+        if B + pad != self.n_seqs:
+            raise StepError(f"step description for {self.n_seqs} sequences given {B} and {pad} padding rows")
+        cache = self.engine.cache
+        seq, start, slot = v["seq"], v["start"], v["slot"]
+        if all(n == 1 for n in n_new):
+            seq[:B] = np.arange(B, dtype=np.int32)
+            start[:B + 1] = np.arange(B + 1, dtype=np.int32)
+        else:
+            r = 0
+            for i, n in enumerate(n_new):
+                seq[r:r + n] = i
+                start[i] = r
+                r += n
+            start[B] = T
+        seq[T:] = -1
+        start[B:] = np.arange(T, T + pad + 1, dtype=np.int32)
+        slot[:B] = slots
+        slot[B:] = cache.max_seqs
+        if wants is None:
+            v["want"][:] = np.arange(self.n_want, dtype=np.int32)
+        else:
+            w = 0
+            for i, ws in enumerate(wants):
+                for p in ws:
+                    v["want"][w] = start[i] + int(p)
+                    w += 1
+        if self.groups:
+            tb = v["tables"].reshape(len(self.groups), self.n_seqs, self.width)
+            tb.fill(-1)
+            for j, gi in enumerate(self.groups):
+                for i, row in enumerate(cache.page_table_rows(slots, gi)):
+                    tb[j, i, :len(row)] = row
+        self.n_new = list(n_new) + [1] * pad
+        self.single = all(n == 1 for n in n_new)
+
+    def write_tokens(self, token_lists: Sequence[Sequence[int]], before: Sequence[int]) -> None:
+        """The tokens themselves, their positions, and each sequence's length once they are appended."""
+        v = self.views
+        B = len(before)
+        ids, pos, slen = v["ids"], v["pos"], v["len"]
+        T = 0
+        if self.single:
+            ids[:B] = [t[0] for t in token_lists]
+            pos[:B] = before
+            slen[:B] = pos[:B] + 1
+            T = B
+        else:
+            for i, toks in enumerate(token_lists):
+                n = len(toks)
+                ids[T:T + n] = np.asarray(toks, dtype=np.int32)
+                pos[T:T + n] = np.arange(before[i], before[i] + n, dtype=np.int32)
+                slen[i] = before[i] + n
+                T += n
+        ids[T:] = 0
+        pos[T:] = 0
+        slen[B:] = 0
+        self.before = list(before)
+
+    def upload(self) -> None:
+        dev = self.engine.runtime.device
+        if self.dev is None:
+            self.dev = torch.empty(self.total, dtype=torch.int32, device=dev)
+        self.dev.copy_(self.host, non_blocking=True)
+
+    def field(self, name: str) -> torch.Tensor:
+        a, n = self.off[name]
+        return self.dev[a:a + n]
+
+    def batch(self, max_len: int) -> StepBatch:
+        """The device copy's fields as a StepBatch (views; the buffer may be rewritten and uploaded again)."""
+        R, W = self.n_seqs, self.width
+        a, _ = self.off["tables"]
+        tables = {gi: self.dev[a + j * R * W: a + (j + 1) * R * W].view(R, W) for j, gi in enumerate(self.groups)}
+        return StepBatch(n_tokens=self.n_tokens, n_seqs=R, token_ids=self.field("ids"), token_pos=self.field("pos"),
+                         token_seq=self.field("seq"), want_rows=self.field("want"), seq_slot=self.field("slot"),
+                         seq_start=self.field("start"), seq_len=self.field("len"), block_tables=tables,
+                         max_new=max(self.n_new), max_len=max_len, all_single=self.single,
+                         host={"n_new": list(self.n_new), "before": self.before})
+
+
 class Engine:
     """A model, its cache and the step function over them."""
 
@@ -78,6 +202,7 @@ class Engine:
         self.cache = SequenceCache(model.cache_specs(), max_tokens,
                                    max_seqs if max_seqs is not None else min(n_pages, 1024),
                                    self.runtime.dtype, self.runtime.device)
+        self.kv_groups = [gi for gi, g in enumerate(self.cache.groups) if isinstance(g.spec, KVSpec)]
         self.vocab = model.vocab
 
     # ------------------------------------------------------------------ sequences
@@ -91,92 +216,56 @@ class Engine:
         return self.cache.length(slot)
 
     # ------------------------------------------------------------------ the step
-    def _validate(self, entries: Sequence[StepEntry]) -> None:
-        if not entries:
+    def validate(self, slots: Sequence[int], token_lists: Sequence[Sequence[int]],
+                 wants: Optional[Sequence[Sequence[int]]] = None, trusted_tokens: bool = False) -> None:
+        """Refuse a step before anything runs.  trusted_tokens: the ids were picked by this engine itself."""
+        if not slots:
             raise StepError("a step needs at least one entry")
-        seen = set()
-        for e in entries:
-            if e.slot in seen:
-                raise StepError(f"slot {e.slot} appears twice in one step")
-            seen.add(e.slot)
-            if not self.cache.slots.is_live(e.slot):
-                raise StepError(f"slot {e.slot} is not held by a sequence")
-            if len(e.tokens) == 0:
-                raise StepError(f"slot {e.slot}: a step entry needs at least one token")
-            for t in e.tokens:
-                if not (0 <= int(t) < self.vocab):
-                    raise StepError(f"slot {e.slot}: token id {t} outside the vocabulary [0, {self.vocab})")
-            for w in e.want:
-                if not (0 <= int(w) < len(e.tokens)):
-                    raise StepError(f"slot {e.slot}: wanted place {w} outside its {len(e.tokens)} tokens")
+        if len(set(slots)) != len(slots):
+            dup = next(s for i, s in enumerate(slots) if s in slots[:i])
+            raise StepError(f"slot {dup} appears twice in one step")
+        for i, (s, toks) in enumerate(zip(slots, token_lists)):
+            if not self.cache.slots.is_live(s):
+                raise StepError(f"slot {s} is not held by a sequence")
+            if len(toks) == 0:
+                raise StepError(f"slot {s}: a step entry needs at least one token")
+            if not trusted_tokens:
+                for t in toks:
+                    if not (0 <= int(t) < self.vocab):
+                        raise StepError(f"slot {s}: token id {t} outside the vocabulary [0, {self.vocab})")
+            if wants is not None:
+                for w in wants[i]:
+                    if not (0 <= int(w) < len(toks)):
+                        raise StepError(f"slot {s}: wanted place {w} outside its {len(toks)} tokens")
 
     def build_batch(self, entries: Sequence[StepEntry]) -> StepBatch:
         """Pack the entries and copy their description to the device (one copy)."""
-        B = len(entries)
+        slots = [e.slot for e in entries]
         n_new = [len(e.tokens) for e in entries]
-        T = sum(n_new)
-        before = [self.cache.length(e.slot) for e in entries]
-        n_want = sum(len(e.want) for e in entries)
-        groups = [gi for gi, g in enumerate(self.cache.groups) if isinstance(g.spec, KVSpec)]
+        before = [self.cache.length(s) for s in slots]
         max_len = max(b + n for b, n in zip(before, n_new))
-        width = max(1, pages_for(max_len))
-        # one int32 array: ids | pos | seq | want | slot | start | len | tables...
-        total = 3 * T + n_want + B + (B + 1) + B + len(groups) * B * width
-        buf = np.empty(total, dtype=np.int32)
-        o = 0
-        ids = buf[o:o + T]; o += T
-        pos = buf[o:o + T]; o += T
-        seq = buf[o:o + T]; o += T
-        want = buf[o:o + n_want]; o += n_want
-        slot = buf[o:o + B]; o += B
-        start = buf[o:o + B + 1]; o += B + 1
-        slen = buf[o:o + B]; o += B
-        r = w = 0
-        for i, e in enumerate(entries):
-            n = n_new[i]
-            ids[r:r + n] = np.asarray(e.tokens, dtype=np.int32)
-            pos[r:r + n] = np.arange(before[i], before[i] + n, dtype=np.int32)
-            seq[r:r + n] = i
-            for p in e.want:
-                want[w] = r + int(p); w += 1
-            slot[i] = e.slot
-            start[i] = r
-            slen[i] = before[i] + n
-            r += n
-        start[B] = T
-        tables = {}
-        for gi in groups:
-            tb = buf[o:o + B * width].reshape(B, width); o += B * width
-            tb.fill(-1)
-            for i, row in enumerate(self.cache.page_table_rows([e.slot for e in entries], gi)):
-                tb[i, :len(row)] = row
-            tables[gi] = tb
-        dev = torch.from_numpy(buf).to(self.runtime.device)
-        o = 0
+        d = StepDescription(self, sum(n_new), len(entries), sum(len(e.want) for e in entries),
+                            max(1, pages_for(max_len)))
+        d.write_membership(slots, n_new, [e.want for e in entries])
+        d.write_tokens([e.tokens for e in entries], before)
+        d.upload()
+        return d.batch(max_len)
 
-        def take(n):
-            nonlocal o
-            t = dev[o:o + n]
-            o += n
-            return t
-
-        d_ids, d_pos, d_seq = take(T), take(T), take(T)
-        d_want, d_slot, d_start, d_len = take(n_want), take(B), take(B + 1), take(B)
-        d_tables = {gi: take(B * width).view(B, width) for gi in groups}
-        return StepBatch(n_tokens=T, n_seqs=B, token_ids=d_ids, token_pos=d_pos, token_seq=d_seq,
-                         want_rows=d_want, seq_slot=d_slot, seq_start=d_start, seq_len=d_len,
-                         block_tables=d_tables, max_new=max(n_new), max_len=max_len,
-                         all_single=all(n == 1 for n in n_new),
-                         host={"n_new": n_new, "before": before})
+    def check_kernels(self) -> None:
+        """Raise if a kernel gave up a bounded wait since the last check (synchronises)."""
+        K.check_status()
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run the entries' tokens; return float32 logits [wanted places, vocab] on the device,
-        in the order of the entries and of each entry's `want`.  On error nothing has changed."""
-        self._validate(entries)
+        in the order of the entries and of each entry's `want`.  On error nothing has changed:
+        a refused step launches nothing, and a step in which a kernel gave up a wait leaves
+        every sequence at the length it had."""
         slots = [e.slot for e in entries]
+        self.validate(slots, [e.tokens for e in entries], [e.want for e in entries])
         n_new = [len(e.tokens) for e in entries]
         self.cache.reserve(slots, n_new)          # raises CacheFull before anything is launched
         batch = self.build_batch(entries)
         logits = self.model.forward(batch, self.cache)
+        self.check_kernels()
         self.cache.advance(slots, n_new)
         return logits

@@ -216,6 +216,21 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
            "gemm_skinny")
 
 
+_scratch_epoch = 0
+
+
+def scratch_epoch() -> int:
+    """Grows whenever a scratch buffer that kernels are given is replaced by a larger one (the old one is freed).
+    A captured CUDA graph recorded the old address: whoever replays graphs compares this number with the one
+    at capture and captures again when it has moved."""
+    return _scratch_epoch
+
+
+def scratch_regrown() -> None:
+    global _scratch_epoch
+    _scratch_epoch += 1
+
+
 _status_word: Optional[torch.Tensor] = None
 
 
@@ -249,6 +264,7 @@ def _gemm_tc_scratch(device):
         lib = build.load("gemm_tc")
         lib.stratum_gemm_tc_scratch_floats.restype = ctypes.c_longlong
         _gemm_scratch = torch.empty(int(lib.stratum_gemm_tc_scratch_floats()), dtype=torch.float32, device=device)
+        scratch_regrown()
     return _gemm_scratch
 
 
@@ -375,6 +391,7 @@ def attention_stream(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
         floats = int(lib.stratum_attention_stream_scratch_floats(max(gs, 8), max(head_dim, 128)))
         _stream_scratch = (max(gs, 8) * (max(head_dim, 128) + 2),
                            torch.empty(floats, dtype=torch.float32, device=qkv.device))
+        scratch_regrown()
     f = _fn("attention_stream", "stratum_attention_stream",
             [c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p])
@@ -400,6 +417,7 @@ def _argmax_scratch_for(rows: int, device):
         _argmax_scratch = (torch.empty(n * ARGMAX_SPLITS, dtype=torch.float32, device=device),
                            torch.empty(n * ARGMAX_SPLITS, dtype=torch.int32, device=device),
                            torch.zeros(n, dtype=torch.int32, device=device))
+        scratch_regrown()
     return _argmax_scratch
 
 

@@ -42,6 +42,8 @@ class Runtime:
         if t is None or t.numel() < numel or t.dtype != dtype:
             t = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
             self._scratch[name] = t
+            from .. import kernels
+            kernels.scratch_regrown()
         return t
 
 

@@ -116,7 +116,7 @@ def test_groups_have_storage_of_their_own():
     assert len(c.groups) == 3
     assert c.layer_group == {0: (0, 0), 1: (1, 0), 3: (2, 0), 4: (0, 1)}
     assert c.groups[0].k.shape == (2, 6, 2, PAGE_TOKENS, 16) and c.groups[1].k.shape == (1, 6, 2, PAGE_TOKENS, 16)
-    assert c.groups[2].state.shape == (1, 3, 4, 8)
+    assert c.groups[2].state.shape == (1, 3 + 1, 4, 8)          # a spare row for the padding rows of a step
     s = c.acquire()
     c.reserve([s], [300]); c.advance([s], [300])
     full = c.page_table_rows([s], 0)[0]
@@ -132,6 +132,6 @@ def test_groups_have_storage_of_their_own():
     s2 = c.acquire()
     assert s2 == s and float(c.groups[2].state[0, s2].abs().sum()) == 0.0
     v = c.layer_view(3, True, {})
-    assert v.state.shape == (3, 4, 8) and v.k is None
+    assert v.state.shape == (3 + 1, 4, 8) and v.k is None
     v = c.layer_view(2, True, {})
     assert v.spec is None

@@ -51,6 +51,27 @@ def _define_toy():
                 if cache.writes:
                     cache.state[slot] = s
 
+    @register_part("mixer", "toy_decay_state_on_device", replace=True)
+    class DecayStateOnDevice(DecayState):
+        """The same mixer written so that a decode step can be captured in a CUDA graph: device operators on
+        the current stream only, nothing copied to or from the host, loop counts from the step's host numbers.  Padding
+        rows of a captured step carry the spare state row (slot number = max_seqs), so they need no mask."""
+
+        def forward(self, xn, residual, step, cache):
+            u = xn.float() @ self.w_in.T
+            slot = step.seq_slot.long()
+            s = cache.state.index_select(0, slot)                                  # [sequences, width]
+            first = step.seq_start[:-1].long()
+            n_new = step.seq_start[1:] - step.seq_start[:-1]                       # stays on the device
+            last_row = xn.shape[0] - 1
+            for t in range(step.max_new):
+                live = (n_new > t).unsqueeze(1)
+                rows = (first + t).clamp(max=last_row)
+                s = torch.where(live, self.decay * s + u.index_select(0, rows), s)
+                residual.index_add_(0, rows, (s @ self.w_out.T) * live)
+            if cache.writes:
+                cache.state.index_copy_(0, slot, s)
+
     @dataclass(frozen=True)
     class ToyConfig(ModelConfig):
         n_layers: int
@@ -59,6 +80,7 @@ def _define_toy():
         decay: float
         vocab: int
         eps: float
+        mixer: str = "toy_decay_state"
         torch_dtype: str = "float32"
         architecture = "ToyStateForCausalLM"
 
@@ -66,20 +88,21 @@ def _define_toy():
         def from_dict(cls, raw: Dict[str, Any]):
             r = KeyReader(raw)
             out = cls(r.integer("layers"), r.integer("hidden"), r.integer("width"), r.number("decay"),
-                      r.integer("vocab"), r.number("eps", 1e-5))
+                      r.integer("vocab"), r.number("eps", 1e-5), r.string("mixer", "toy_decay_state"))
             r.finish()
             return out
 
         def to_dict(self):
             return {"architectures": [self.architecture], "layers": self.n_layers, "hidden": self.hidden,
-                    "width": self.width, "decay": self.decay, "vocab": self.vocab, "eps": self.eps}
+                    "width": self.width, "decay": self.decay, "vocab": self.vocab, "eps": self.eps,
+                    "mixer": self.mixer}
 
     def describe(cfg):
         norm = lambda p: PartSpec("rmsnorm", {"size": cfg.hidden, "eps": cfg.eps, "prefix": p})   # noqa: E731
         layers = []
         for i in range(cfg.n_layers):
             # odd layers mix with the toy state, even layers with attention: one model, two kinds of mixer
-            mixer = PartSpec("toy_decay_state", {"hidden": cfg.hidden, "width": cfg.width, "decay": cfg.decay,
+            mixer = PartSpec(cfg.mixer, {"hidden": cfg.hidden, "width": cfg.width, "decay": cfg.decay,
                                                  "prefix": "mix."}) if i % 2 else \
                 PartSpec("gqa_attention", {"hidden": cfg.hidden, "n_heads": 2, "n_kv_heads": 1, "head_dim": 16,
                                            "bias": False, "window": 0, "scale": None, "position": None,
@@ -136,7 +159,7 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     llm = Stratum(path, dtype="float32", max_tokens=1024)                                        # chosen by config.json
     groups = llm.engine.cache.groups
     assert len(groups) == 2 and sum(isinstance(g.spec, StateSpec) for g in groups) == 1
-    assert [g.state.shape for g in groups if g.state is not None] == [(2, llm.engine.cache.max_seqs, 24)]
+    assert [g.state.shape for g in groups if g.state is not None] == [(2, llm.engine.cache.max_seqs + 1, 24)]
     c, w = load_plain(path)
     rng = np.random.default_rng(0)
     seqs = [rng.integers(0, 120, size=n).tolist() for n in (40, 7, 70)]
@@ -158,8 +181,8 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
                 if cut[i] + k >= len(seqs[i]):
                     llm.release(slots[i]); live.remove(i)
     llm.engine.cache.check()
-    # and through the generation loop (graphs are captured around the toy mixer's host loop? no: it reads
-    # tensors on the host, so this model steps launch by launch)
+    # and through the generation loop (this mixer reads tensors on the host, which a graph capture refuses, so
+    # the model steps launch by launch; the next test has the capturable form)
     plain_llm = Stratum(path, dtype="float32", max_tokens=1024, use_graphs=False)
     res = plain_llm.generate([seqs[1]], max_new_tokens=5, stop_ids=())
     seq = list(seqs[1])
@@ -167,3 +190,38 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
         ref = _plain_toy(c, w, seq)[-1]
         assert ref[tok] >= ref.max() - 1e-4 * np.max(np.abs(ref))
         seq.append(tok)
+
+
+def test_toy_state_under_replayed_graphs(tmp_path):
+    """Generation with graphs on (the default) over a mixer with fixed-size state: the state must be updated
+    exactly once per step, also in the step that captures a new graph, and a slot taken again starts from zero.
+    Tokens and every step's logits against graphs off and against the plain restatement, in two rounds."""
+    from helpers import load_plain
+    from stratum_b200 import Stratum
+    from stratum_b200.weights import write_random_model
+    ToyConfig = _define_toy()
+    raw = {"architectures": ["ToyStateForCausalLM"], "layers": 4, "hidden": 48, "width": 24, "decay": 0.9,
+           "vocab": 120, "eps": 1e-5, "mixer": "toy_decay_state_on_device"}
+    path = write_random_model(str(tmp_path / "toy"), ToyConfig.from_dict(raw), seed=6, std=0.1, dtype="float32")
+    c, w = load_plain(path)
+    graphed = Stratum(path, dtype="float32", max_tokens=2048)
+    assert graphed.graphs is not None
+    eager = Stratum(path, dtype="float32", max_tokens=2048, use_graphs=False)
+    rng = np.random.default_rng(2)
+    for rnd in range(2):
+        lens, budgets = ((5, 17, 3), (9, 4, 12)) if rnd == 0 else ((8, 2, 30, 6), (6, 14, 3, 9))
+        prompts = [rng.integers(0, 120, size=n).tolist() for n in lens]
+        seen = []
+        out = graphed.generate(prompts, max_new_tokens=list(budgets), stop_ids=(),
+                               on_logits=lambda lg, ids: seen.append(lg.cpu().numpy().copy()))
+        ref = eager.generate(prompts, max_new_tokens=list(budgets), stop_ids=())
+        assert [r.tokens for r in out] == [r.tokens for r in ref]
+        plain = [_plain_toy(c, w, p + r.tokens) for p, r in zip(prompts, out)]
+        live = list(range(len(prompts)))
+        for step, lg in enumerate(seen):
+            for row, i in enumerate(live):
+                want = plain[i][len(prompts[i]) - 1 + step]
+                assert np.max(np.abs(lg[row] - want)) < 3e-5 * np.max(np.abs(want)), (rnd, step, i)
+            live = [i for i in live if step + 1 < budgets[i]]
+    assert graphed.graphs.captures >= 3
+    graphed.engine.cache.check()
