@@ -25,16 +25,17 @@ def describe_llama(cfg: LlamaConfig) -> ModelSpec:
     for i in range(cfg.n_layers):
         layers.append(LayerSpec(
             arrangement="prenorm_residual",
-            mixer=PartSpec("gqa_attention", {
-                "hidden": cfg.hidden, "n_heads": cfg.n_heads, "n_kv_heads": cfg.n_kv_heads,
-                "head_dim": cfg.head_dim, "bias": cfg.attention_bias, "window": 0, "scale": None,
-                "position": rope, "prefix": "self_attn."}),
-            mixer_norm=PartSpec("rmsnorm", {"size": cfg.hidden, "eps": cfg.rms_eps,
-                                            "prefix": "input_layernorm."}),
-            feed_forward=PartSpec("swiglu", {"hidden": cfg.hidden, "intermediate": cfg.intermediate,
-                                             "bias": cfg.mlp_bias, "prefix": "mlp."}),
-            feed_forward_norm=PartSpec("rmsnorm", {"size": cfg.hidden, "eps": cfg.rms_eps,
-                                                   "prefix": "post_attention_layernorm."}),
+            parts={
+                "mixer_norm": PartSpec("rmsnorm", {"size": cfg.hidden, "eps": cfg.rms_eps,
+                                                   "prefix": "input_layernorm."}),
+                "mixer": PartSpec("gqa_attention", {
+                    "hidden": cfg.hidden, "n_heads": cfg.n_heads, "n_kv_heads": cfg.n_kv_heads,
+                    "head_dim": cfg.head_dim, "bias": cfg.attention_bias, "window": 0, "scale": None,
+                    "position": rope, "q_norm": None, "k_norm": None, "prefix": "self_attn."}),
+                "feed_forward_norm": PartSpec("rmsnorm", {"size": cfg.hidden, "eps": cfg.rms_eps,
+                                                          "prefix": "post_attention_layernorm."}),
+                "feed_forward": PartSpec("swiglu", {"hidden": cfg.hidden, "intermediate": cfg.intermediate,
+                                                    "bias": cfg.mlp_bias, "prefix": "mlp."})},
             prefix=f"model.layers.{i}."))
     return ModelSpec(
         hidden=cfg.hidden, vocab=cfg.vocab,

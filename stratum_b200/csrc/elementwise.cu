@@ -139,6 +139,44 @@ STRATUM_EXPORT int stratum_rmsnorm(const float* x, const float* gain, const int*
   return STRATUM_ERR_DTYPE;
 }
 
+// The same per head, in place: row r of x holds n_heads stretches of head_dim values from column first_col on,
+// and each becomes stretch * (1/sqrt(mean(stretch^2) + eps)) * gain (the optional per-head norm of queries and
+// keys, stratum/native/stratum_arch_llama.inc.c:403-420).  One warp per (row, head); the sum runs over the
+// lane's values in order and then across lanes, whatever else is in the step.
+template <typename T>
+__global__ void rmsnorm_heads_kernel(T* x, int n_rows, int stride, int first_col, int n_heads, int head_dim,
+                                     const float* __restrict__ gain, float eps) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= n_rows * n_heads) return;
+  T* p = x + (size_t)(item / n_heads) * stride + first_col + (size_t)(item % n_heads) * head_dim;
+  float ss = 0.f;
+  for (int d = lane; d < head_dim; d += 32) {
+    const float v = ld_fresh(p + d);
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  const float scale = 1.0f / sqrtf(ss / (float)head_dim + eps);
+  for (int d = lane; d < head_dim; d += 32) p[d] = from_float<T>(ld_fresh(p + d) * scale * gain[d]);
+}
+
+STRATUM_EXPORT int stratum_rmsnorm_heads(void* x, int dtype, int n_rows, int stride, int first_col, int n_heads,
+                                         int head_dim, const float* gain, float eps, cudaStream_t stream) {
+  if (n_rows <= 0 || n_heads <= 0) return 0;
+  if (head_dim <= 0 || first_col < 0 || first_col + (long long)n_heads * head_dim > stride) return STRATUM_ERR_SHAPE;
+  const int warps = 4;
+  const int blocks = (int)(((long long)n_rows * n_heads + warps - 1) / warps);
+  if (dtype == STRATUM_DT_F32)
+    return launch_pdl(rmsnorm_heads_kernel<float>, blocks, warps * 32, 0, stream, (float*)x, n_rows, stride,
+                      first_col, n_heads, head_dim, gain, eps);
+  if (dtype == STRATUM_DT_BF16)
+    return launch_pdl(rmsnorm_heads_kernel<bf16>, blocks, warps * 32, 0, stream, (bf16*)x, n_rows, stride, first_col,
+                      n_heads, head_dim, gain, eps);
+  return STRATUM_ERR_DTYPE;
+}
+
 // ---------------------------------------------------------------- SwiGLU
 // a[j] = silu(g[j]) * u[j], silu(z) = z / (1 + exp(-z))   (stratum/native/stratum_engine.h:373-391)
 // gu holds gate and up interleaved: gu[r][2j] = g_j, gu[r][2j+1] = u_j.

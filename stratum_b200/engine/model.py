@@ -22,19 +22,32 @@ from ..weights.loader import check_tensors, load_weights, place
 
 
 class Layer:
-    """The parts of one decoder layer, built from its LayerSpec."""
+    """The parts of one decoder layer, built from its LayerSpec: whichever the arrangement asks for."""
 
     def __init__(self, spec: LayerSpec, runtime: Optional[Runtime]):
         self.spec = spec
         self.prefix = spec.prefix
         self.arrangement = find_part("arrangement", spec.arrangement)()
-        self.mixer = find_part("mixer", spec.mixer.kind)(spec.mixer, runtime)
-        self.mixer_norm = find_part("norm", spec.mixer_norm.kind)(spec.mixer_norm, runtime)
-        self.feed_forward = find_part("feed_forward", spec.feed_forward.kind)(spec.feed_forward, runtime)
-        self.feed_forward_norm = find_part("norm", spec.feed_forward_norm.kind)(spec.feed_forward_norm, runtime)
+        slots, optional = self.arrangement.slots, set(self.arrangement.optional)
+        missing = [n for n in slots if n not in spec.parts and n not in optional]
+        unknown = [n for n in spec.parts if n not in slots]
+        if missing or unknown:
+            raise ValueError(f"layer {spec.prefix!r}: arrangement {spec.arrangement!r} wires the parts "
+                             f"{sorted(slots)}; missing {missing}, not known to it {unknown}")
+        self._parts: Dict[str, object] = {name: find_part(slots[name], ps.kind)(ps, runtime)
+                                          for name, ps in spec.parts.items()}
+
+    def part(self, name: str):
+        """The built part of that name, or None when the spec left an optional one out."""
+        return self._parts.get(name)
 
     def parts(self):
-        return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+        return tuple(self._parts.values())
+
+    def cache_spec(self) -> Optional[CacheSpec]:
+        owner = self.arrangement.cache_owner
+        part = self._parts.get(owner) if owner else None
+        return part.cache_spec() if part is not None else None
 
     def tensors(self) -> Dict[str, TensorSpec]:
         out: Dict[str, TensorSpec] = {}
@@ -83,9 +96,9 @@ class Model:
         reads another stop's cache)."""
         specs: List[Optional[CacheSpec]] = []
         for i, e in enumerate(self.schedule):
-            own = self.layers[e.layer].mixer.cache_spec()
+            own = self.layers[e.layer].cache_spec()
             if e.cache_of is not None:
-                theirs = self.layers[self.schedule[e.cache_of].layer].mixer.cache_spec()
+                theirs = self.layers[self.schedule[e.cache_of].layer].cache_spec()
                 if theirs != own:
                     raise ValueError(f"model spec: stop {i} needs {own} but reads the cache of stop {e.cache_of}, "
                                      f"which holds {theirs}")

@@ -125,6 +125,21 @@ def rmsnorm(x: torch.Tensor, gain: torch.Tensor, eps: float, out: torch.Tensor,
              c_float(eps), _stream()), "rmsnorm")
 
 
+def rmsnorm_heads(x: torch.Tensor, first_col: int, n_heads: int, head_dim: int, gain: torch.Tensor,
+                  eps: float) -> None:
+    """In place, in every row of x [T, width]: each of the n_heads stretches of head_dim values from column
+    first_col on becomes rmsnorm(stretch) * gain.  gain float32 [head_dim]."""
+    _need(x, "x", contiguous=False); _need(gain, "gain", torch.float32)
+    if x.dim() != 2 or x.stride(1) != 1 or first_col < 0 or first_col + n_heads * head_dim > x.shape[1]:
+        raise KernelError("rmsnorm_heads: the heads do not lie inside the rows of x")
+    if gain.numel() != head_dim:
+        raise KernelError("rmsnorm_heads: gain and head_dim disagree")
+    f = _fn("elementwise", "stratum_rmsnorm_heads",
+            [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p])
+    _check(f(_ptr(x), dtype_code(x.dtype), x.shape[0], x.stride(0), first_col, n_heads, head_dim, _ptr(gain),
+             c_float(eps), _stream()), "rmsnorm_heads")
+
+
 def swiglu(gu: torch.Tensor, out: torch.Tensor) -> None:
     """out[r][j] = silu(gu[r][2j]) * gu[r][2j+1]."""
     _need(gu, "gu"); _need(out, "out", gu.dtype)

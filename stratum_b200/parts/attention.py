@@ -1,6 +1,8 @@
 """Grouped-query attention over the paged cache.
 
-q = Wq xn, k = Wk xn, v = Wv xn (+ biases); rotate q and k; append k and v to the cache at the
+q = Wq xn, k = Wk xn, v = Wv xn (+ biases); optionally normalise every head of q and of k
+(stratum/native/stratum_arch_llama.inc.c:403-420, :866-884: tensors found by name, skipped when
+absent); rotate q and k; append k and v to the cache at the
 token's position; score_t = (q_h . K_t[kv(h)]) * scale for the keys the token may see; softmax;
 o_h = sum_t p_t V_t[kv(h)]; residual += Wo o.  kv(h) = h / (n_heads / n_kv_heads).
 (stratum/native/stratum_arch_llama.inc.c:398-524.)  The three projections run as one matrix
@@ -26,7 +28,8 @@ from .spec import PartSpec, TensorSpec
 @register_part("mixer", "gqa_attention")
 class GQAAttention(Mixer):
     """params: hidden, n_heads, n_kv_heads, head_dim, bias, window (0 = all keys), scale (None =
-    1/sqrt(head_dim)), position (PartSpec of a position encoding, or None), prefix."""
+    1/sqrt(head_dim)), position (PartSpec of a position encoding, or None), q_norm / k_norm (PartSpec of a
+    norm of size head_dim applied to every query / key head between projection and rotation, or None), prefix."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -44,8 +47,17 @@ class GQAAttention(Mixer):
             raise ValueError(f"attention: head_dim {self.head_dim} must be even")
         pos: Optional[PartSpec] = spec.get("position")
         self.position = find_part("position", pos.kind)(pos, runtime) if pos is not None else None
+        self.q_norm = self._head_norm(spec.get("q_norm"), runtime)
+        self.k_norm = self._head_norm(spec.get("k_norm"), runtime)
         self.qkv: Optional[Linear] = None
         self.o: Optional[Linear] = None
+
+    def _head_norm(self, ps: Optional[PartSpec], runtime):
+        if ps is None:
+            return None
+        norm = find_part("norm", ps.kind)(ps, runtime)
+        norm.prefix = self.prefix + norm.prefix           # its tensors live under this mixer's names
+        return norm
 
     def tensors(self) -> Dict[str, TensorSpec]:
         p, H, D = self.prefix, self.hidden, self.head_dim
@@ -58,6 +70,9 @@ class GQAAttention(Mixer):
                       p + "k_proj.bias": TensorSpec((self.n_kv_heads * D,), role="vector"),
                       p + "v_proj.bias": TensorSpec((self.n_kv_heads * D,), role="vector"),
                       p + "o_proj.bias": TensorSpec((H,), role="vector")})
+        for norm in (self.q_norm, self.k_norm):
+            if norm is not None:
+                t.update(norm.tensors())
         return t
 
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
@@ -70,12 +85,19 @@ class GQAAttention(Mixer):
                            weights[p + "v_proj.bias"]]).contiguous()
         self.qkv = Linear(self.runtime, w, b)
         self.o = Linear(self.runtime, weights[p + "o_proj.weight"], weights.get(p + "o_proj.bias"))
+        for norm in (self.q_norm, self.k_norm):
+            if norm is not None:
+                norm.bind(weights)
 
     def cache_spec(self) -> KVSpec:
         return KVSpec(self.n_kv_heads, self.head_dim, self.window)
 
     def forward(self, xn: torch.Tensor, residual: torch.Tensor, step, cache: LayerCache) -> None:
         qkv = self.qkv(xn, mode=STORE)
+        if self.q_norm is not None:
+            self.q_norm.forward_heads(qkv, 0, self.n_heads, self.head_dim)
+        if self.k_norm is not None:
+            self.k_norm.forward_heads(qkv, self.n_heads * self.head_dim, self.n_kv_heads, self.head_dim)
         rot = self.position.rotary() if self.position is not None else None
         K.rope_store(qkv, step.token_pos, step.token_seq, cache.block_table,
                      None if rot is None else rot.inv_freq, bool(rot and rot.interleaved),

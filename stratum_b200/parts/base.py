@@ -68,6 +68,11 @@ class Norm(Part):
         """float32 [T, hidden] -> compute dtype [T or len(rows), hidden]."""
         raise NotImplementedError
 
+    def forward_heads(self, x: torch.Tensor, first_col: int, n_heads: int, head_dim: int) -> None:
+        """Normalise in place, in every row of x (compute dtype), each of the n_heads stretches of head_dim
+        values that start at column first_col: the form a mixer uses on its queries and keys.  Optional."""
+        raise NotImplementedError(f"norm {self.kind!r} has no per-head form")
+
 
 class PositionEncoding(Part):
     def rotary(self) -> Optional["RotaryTable"]:
@@ -122,8 +127,16 @@ class Head(Part):
 
 
 class Arrangement:
-    """How a layer's norms, mixer and feed-forward are wired around the residual stream."""
+    """How a layer's parts are wired around the residual stream.
+
+    `slots` names the parts this arrangement uses and the category each is looked up in; a layer's spec must
+    give exactly those (names in `optional` may be left out).  `cache_owner` names the part whose
+    `cache_spec()` says what the layer keeps per sequence (None: nothing).  `forward` reads the built parts
+    as `layer.part(name)`."""
     kind = ""
+    slots: Mapping[str, str] = {}
+    optional: tuple = ()
+    cache_owner: Optional[str] = "mixer"
 
     def forward(self, layer, x: torch.Tensor, step, cache: LayerCache) -> None:
         raise NotImplementedError

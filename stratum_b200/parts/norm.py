@@ -32,3 +32,8 @@ class RMSNorm(Norm):
         out = self.runtime.empty(n, self.size)
         K.rmsnorm(x, self.gain, self.eps, out, rows)
         return out
+
+    def forward_heads(self, x: torch.Tensor, first_col: int, n_heads: int, head_dim: int) -> None:
+        if head_dim != self.size:
+            raise ValueError(f"rmsnorm of size {self.size} asked to normalise heads of {head_dim}")
+        K.rmsnorm_heads(x, first_col, n_heads, head_dim, self.gain, self.eps)

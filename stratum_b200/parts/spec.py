@@ -31,12 +31,15 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One decoder layer: a mixer and a feed-forward, each behind a norm, in an arrangement."""
+    """One decoder layer: an arrangement and the parts it wires, by the names the arrangement gives them.
+
+    `parts` maps a name to a PartSpec.  Which names exist, and of which category each is (mixer, norm,
+    feed_forward, ...), is the arrangement's business: "prenorm_residual" asks for `mixer_norm`, `mixer`,
+    `feed_forward_norm` and `feed_forward`; another arrangement may ask for one shared norm, for four, or
+    for no feed-forward at all.  Tensor names are the layer's prefix, then the part's own prefix.
+    """
     arrangement: str                 # registered arrangement kind, e.g. "prenorm_residual"
-    mixer: PartSpec
-    mixer_norm: PartSpec
-    feed_forward: PartSpec
-    feed_forward_norm: PartSpec
+    parts: Mapping[str, PartSpec]
     prefix: str                      # tensor-name prefix of this layer's weights
 
 

@@ -46,6 +46,13 @@ def rms_norm(x: np.ndarray, gain: np.ndarray, eps: float) -> np.ndarray:
     return x * scale * np.asarray(gain, dtype=F64)
 
 
+def head_rms_norm(heads: np.ndarray, gain: np.ndarray, eps: float) -> np.ndarray:
+    """RMSNorm of every head on its own, [T, n_heads, head_dim] with a gain of head_dim values: the optional
+    norm of queries and keys, applied after the projection and before the rotation.
+    stratum/native/stratum_arch_llama.inc.c:403-420 (one token), :866-884 (a chunk)."""
+    return np.stack([rms_norm(heads[:, j], gain, eps) for j in range(heads.shape[1])], axis=1)
+
+
 def linear(x: np.ndarray, weight: np.ndarray, bias: Optional[np.ndarray] = None) -> np.ndarray:
     """y[r] = sum_k W[r][k] * x[k] (+ b[r]); W is row-major [out][in].
     stratum/native/stratum_linear.h:491-507 (no bias there); the bias form

@@ -100,8 +100,10 @@ def test_model_description_is_data():
     cfg = LlamaConfig.from_dict(TINY_B)
     spec = find_architecture(TINY_B).describe_model(cfg)
     assert len(spec.layers) == 3 and [e.layer for e in spec.schedule] == [0, 1, 2]
-    m = spec.layers[1].mixer
+    m = spec.layers[1].parts["mixer"]
     assert m.kind == "gqa_attention" and m["n_kv_heads"] == 1 and m["head_dim"] == 32 and m["bias"] is True
     assert m["position"].kind == "rope" and m["position"]["scaling"]["kind"] == "llama3"
-    assert spec.layers[0].feed_forward.kind == "swiglu" and spec.layers[0].feed_forward["intermediate"] == 256
+    ff = spec.layers[0].parts["feed_forward"]
+    assert ff.kind == "swiglu" and ff["intermediate"] == 256
+    assert sorted(spec.layers[0].parts) == ["feed_forward", "feed_forward_norm", "mixer", "mixer_norm"]
     assert spec.head["tied"] is True

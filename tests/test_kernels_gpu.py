@@ -57,6 +57,30 @@ def test_rmsnorm_many_rows(dtype, hidden):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_heads,head_dim,first", [(5, 48, 0), (2, 128, 640), (7, 20, 8)])
+def test_rmsnorm_heads_in_place(dtype, n_heads, head_dim, first):
+    """The per-head norm of queries or keys: only the named stretch of each row changes."""
+    from stratum_b200 import kernels as K
+    rng = np.random.default_rng(n_heads * head_dim)
+    width = first + n_heads * head_dim + 24
+    x = dev(rng.standard_normal((9, width)) * 2.0, DT[dtype])
+    gain = dev(rng.random(head_dim) + 0.5)
+    before = as64(x)
+    K.rmsnorm_heads(x, first, n_heads, head_dim, gain, 1e-6)
+    got = as64(x)
+    heads = before[:, first:first + n_heads * head_dim].reshape(9, n_heads, head_dim)
+    ref = P.head_rms_norm(heads, as64(gain), 1e-6).reshape(9, -1)
+    assert rel_err(got[:, first:first + n_heads * head_dim], ref) < (2e-6 if dtype == "float32" else 5e-3)
+    assert np.array_equal(got[:, :first], before[:, :first])
+    assert np.array_equal(got[:, first + n_heads * head_dim:], before[:, first + n_heads * head_dim:])
+    one = dev(before[4:5], DT[dtype])                      # a row alone gives the bits it gave in the batch
+    K.rmsnorm_heads(one, first, n_heads, head_dim, gain, 1e-6)
+    assert torch.equal(one[0], x[4])
+    with pytest.raises(K.KernelError):
+        K.rmsnorm_heads(x, first, n_heads + 1, head_dim, gain, 1e-6)      # would run past the row
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_embed_gather(dtype):
     from stratum_b200 import kernels as K
     rng = np.random.default_rng(1)

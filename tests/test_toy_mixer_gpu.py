@@ -107,9 +107,10 @@ def _define_toy():
                 PartSpec("gqa_attention", {"hidden": cfg.hidden, "n_heads": 2, "n_kv_heads": 1, "head_dim": 16,
                                            "bias": False, "window": 0, "scale": None, "position": None,
                                            "prefix": "attn."})
-            layers.append(LayerSpec("prenorm_residual", mixer, norm("n1."),
-                                    PartSpec("swiglu", {"hidden": cfg.hidden, "intermediate": 2 * cfg.hidden,
-                                                        "bias": False, "prefix": "ff."}), norm("n2."), f"l.{i}."))
+            layers.append(LayerSpec("prenorm_residual", {
+                "mixer_norm": norm("n1."), "mixer": mixer, "feed_forward_norm": norm("n2."),
+                "feed_forward": PartSpec("swiglu", {"hidden": cfg.hidden, "intermediate": 2 * cfg.hidden,
+                                                    "bias": False, "prefix": "ff."})}, f"l.{i}."))
         return ModelSpec(cfg.hidden, cfg.vocab,
                          PartSpec("token_embedding", {"vocab": cfg.vocab, "hidden": cfg.hidden, "prefix": "emb."}),
                          tuple(layers), tuple(ScheduleEntry(i) for i in range(cfg.n_layers)), norm("nf."),

@@ -1,6 +1,8 @@
 """Toy parts defined here, in the test, are registered, built and stepped without a change to the library's files:
-a feed-forward that routes every token to one of several experts, and a position encoding of another kind
-(a learned vector per absolute position, added to the embedded tokens).  They are no model of anyone's."""
+a feed-forward that routes every token to one of several experts, a position encoding of another kind
+(a learned vector per absolute position, added to the embedded tokens), and arrangements that own other
+parts than the built-in one (one norm shared by a parallel mixer and feed-forward; a norm before and after
+each part; a layer without a feed-forward).  They are no model of anyone's."""
 import json
 import os
 from dataclasses import dataclass
@@ -104,7 +106,9 @@ def _define_toy():
             ff = PartSpec("toy_routed", {"hidden": cfg.hidden, "inner": cfg.inner, "experts": cfg.experts,
                                          "prefix": "moe."}) if i % 2 == 0 else \
                 PartSpec("swiglu", {"hidden": cfg.hidden, "intermediate": cfg.inner, "bias": False, "prefix": "ff."})
-            layers.append(LayerSpec("prenorm_residual", mixer, norm("n1."), ff, norm("n2."), f"l.{i}."))
+            layers.append(LayerSpec("prenorm_residual", {"mixer_norm": norm("n1."), "mixer": mixer,
+                                                         "feed_forward_norm": norm("n2."), "feed_forward": ff},
+                                    f"l.{i}."))
         return ModelSpec(cfg.hidden, cfg.vocab,
                          PartSpec("token_embedding", {"vocab": cfg.vocab, "hidden": cfg.hidden, "prefix": "emb."}),
                          tuple(layers), tuple(ScheduleEntry(i) for i in range(cfg.n_layers)), norm("nf."),
@@ -190,3 +194,172 @@ def test_routed_feed_forward_and_learned_positions_register_build_and_step(tmp_p
         ref = _plain_toy(c, w, seq)[0][-1]
         assert ref[tok] >= ref.max() - 1e-4 * np.max(np.abs(ref))
         seq.append(tok)
+
+
+def _define_arranged():
+    """Three test-only arrangements and an architecture whose layers use one each, beside the built-in one."""
+    from stratum_b200.config import Architecture, ModelConfig, register_architecture
+    from stratum_b200.config.base import KeyReader
+    from stratum_b200.parts import Arrangement, LayerSpec, ModelSpec, PartSpec, ScheduleEntry, register_part
+
+    @register_part("arrangement", "toy_parallel_shared_norm", replace=True)
+    class ParallelSharedNorm(Arrangement):
+        """x += mixer(n(x)) + feed_forward(n(x)): one norm, both parts read the same normed rows."""
+        slots = {"norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
+
+        def forward(self, layer, x, step, cache):
+            xn = layer.part("norm").forward(x)
+            layer.part("mixer").forward(xn, x, step, cache)
+            layer.part("feed_forward").forward(xn, x, step)
+
+    @register_part("arrangement", "toy_sandwich", replace=True)
+    class Sandwich(Arrangement):
+        """x += post_a(mixer(pre_a(x))); x += post_b(feed_forward(pre_b(x))): four norms.  The feed-forward
+        and its two norms may be left out."""
+        slots = {"pre_mixer": "norm", "mixer": "mixer", "post_mixer": "norm",
+                 "pre_feed_forward": "norm", "feed_forward": "feed_forward", "post_feed_forward": "norm"}
+        optional = ("pre_feed_forward", "feed_forward", "post_feed_forward")
+
+        def forward(self, layer, x, step, cache):
+            out = torch.zeros_like(x)                      # parts add their result into what they are given
+            layer.part("mixer").forward(layer.part("pre_mixer").forward(x), out, step, cache)
+            x += layer.part("post_mixer").forward(out).float()
+            if layer.part("feed_forward") is not None:
+                out = torch.zeros_like(x)
+                layer.part("feed_forward").forward(layer.part("pre_feed_forward").forward(x), out, step)
+                x += layer.part("post_feed_forward").forward(out).float()
+
+    @dataclass(frozen=True)
+    class ArrangedConfig(ModelConfig):
+        hidden: int
+        inner: int
+        vocab: int
+        eps: float
+        torch_dtype: str = "float32"
+        architecture = "ToyArrangedForCausalLM"
+
+        @classmethod
+        def from_dict(cls, raw: Dict[str, Any]):
+            r = KeyReader(raw)
+            out = cls(r.integer("hidden"), r.integer("inner"), r.integer("vocab"), r.number("eps", 1e-5))
+            r.finish()
+            return out
+
+        def to_dict(self):
+            return {"architectures": [self.architecture], "hidden": self.hidden, "inner": self.inner,
+                    "vocab": self.vocab, "eps": self.eps}
+
+    def describe(cfg):
+        norm = lambda p, n=cfg.hidden: PartSpec("rmsnorm", {"size": n, "eps": cfg.eps, "prefix": p})   # noqa: E731
+        rope = PartSpec("rope", {"rope_dim": 16, "theta": 10000.0, "interleaved": False, "scaling": None})
+
+        def att(qk_norm):
+            return PartSpec("gqa_attention", {
+                "hidden": cfg.hidden, "n_heads": 4, "n_kv_heads": 2, "head_dim": 16, "bias": False, "window": 0,
+                "scale": None, "position": rope, "prefix": "attn.",
+                "q_norm": norm("q_norm.", 16) if qk_norm else None,
+                "k_norm": norm("k_norm.", 16) if qk_norm else None})
+
+        ff = PartSpec("swiglu", {"hidden": cfg.hidden, "intermediate": cfg.inner, "bias": False, "prefix": "ff."})
+        layers = (
+            LayerSpec("toy_parallel_shared_norm", {"norm": norm("n."), "mixer": att(False), "feed_forward": ff},
+                      "l.0."),
+            LayerSpec("toy_sandwich", {"pre_mixer": norm("n1."), "mixer": att(True), "post_mixer": norm("n2."),
+                                       "pre_feed_forward": norm("n3."), "feed_forward": ff,
+                                       "post_feed_forward": norm("n4.")}, "l.1."),
+            LayerSpec("toy_sandwich", {"pre_mixer": norm("n1."), "mixer": att(False), "post_mixer": norm("n2.")},
+                      "l.2."),                                                     # no feed-forward at all
+            LayerSpec("prenorm_residual", {"mixer_norm": norm("n1."), "mixer": att(True),
+                                           "feed_forward_norm": norm("n2."), "feed_forward": ff}, "l.3."))
+        return ModelSpec(cfg.hidden, cfg.vocab,
+                         PartSpec("token_embedding", {"vocab": cfg.vocab, "hidden": cfg.hidden, "prefix": "emb."}),
+                         layers, tuple(ScheduleEntry(i) for i in range(4)), norm("nf."),
+                         PartSpec("linear_head", {"vocab": cfg.vocab, "hidden": cfg.hidden, "tied": True,
+                                                  "prefix": "head."}))
+
+    register_architecture(Architecture(("ToyArrangedForCausalLM",), "test-only: arrangements that own other parts",
+                                       ArrangedConfig, describe), replace=True)
+    return ArrangedConfig
+
+
+def _plain_arranged(cfg, w, toks):
+    from plain import llama_plain as P
+    T, eps = len(toks), cfg["eps"]
+    pos = np.arange(T)
+    inv = P.rope_inv_freq(16, 10000.0)
+
+    def att(xn, p, qk_norm):
+        q = P.linear(xn, w[p + "attn.q_proj.weight"]).reshape(T, 4, 16)
+        k = P.linear(xn, w[p + "attn.k_proj.weight"]).reshape(T, 2, 16)
+        v = P.linear(xn, w[p + "attn.v_proj.weight"]).reshape(T, 2, 16)
+        if qk_norm:
+            q = P.head_rms_norm(q, w[p + "attn.q_norm.weight"], eps)
+            k = P.head_rms_norm(k, w[p + "attn.k_norm.weight"], eps)
+        q, k = P.apply_rope(q, pos, inv, False), P.apply_rope(k, pos, inv, False)
+        return P.linear(P.causal_gqa_attention(q, k, v).reshape(T, 64), w[p + "attn.o_proj.weight"])
+
+    ffn = lambda xn, p: P.swiglu_mlp(xn, w, p + "ff.")      # noqa: E731
+    n = lambda x, name: P.rms_norm(x, w[name + "weight"], eps)   # noqa: E731
+    x = P.embed(w["emb.weight"], toks)
+    xn = n(x, "l.0.n.")
+    x = x + att(xn, "l.0.", False) + ffn(xn, "l.0.")
+    x = x + n(att(n(x, "l.1.n1."), "l.1.", True), "l.1.n2.")
+    x = x + n(ffn(n(x, "l.1.n3."), "l.1."), "l.1.n4.")
+    x = x + n(att(n(x, "l.2.n1."), "l.2.", False), "l.2.n2.")
+    x = x + att(n(x, "l.3.n1."), "l.3.", True)
+    x = x + ffn(n(x, "l.3.n2."), "l.3.")
+    return P.linear(n(x, "nf."), w["emb.weight"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_arrangements_that_own_other_parts(tmp_path, dtype):
+    from helpers import TOL, load_plain
+    from stratum_b200 import StepEntry, Stratum
+    from stratum_b200.weights import write_random_model
+    ArrangedConfig = _define_arranged()
+    raw = {"architectures": ["ToyArrangedForCausalLM"], "hidden": 64, "inner": 96, "vocab": 90, "eps": 1e-5}
+
+    def gains(tensors):                                     # norm gains other than one, so that every norm counts
+        g = torch.Generator().manual_seed(1)
+        for name, t in tensors.items():
+            if name.endswith("weight") and t.dim() == 1:
+                t.copy_((0.5 + torch.rand(t.shape, generator=g)).to(t.dtype))
+
+    from stratum_b200.engine.model import expected_tensors
+    from stratum_b200.weights.random_init import random_tensors, _TORCH_DTYPES
+    from stratum_b200.weights.safetensors_io import write_safetensors
+    cfg = ArrangedConfig.from_dict(raw)
+    names = expected_tensors(cfg)
+    assert "l.1.attn.q_norm.weight" in names and "l.0.attn.q_norm.weight" not in names
+    assert "l.2.n1.weight" in names and not any(n.startswith("l.2.ff.") for n in names)
+    tensors = random_tensors(names, 3, 0.2, _TORCH_DTYPES[dtype])
+    gains(tensors)
+    path = str(tmp_path / "arranged")
+    os.makedirs(path)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(dict(cfg.to_dict(), torch_dtype=dtype), f)
+    write_safetensors(os.path.join(path, "model.safetensors"), tensors)
+    c, w = load_plain(path)
+    llm = Stratum(path, dtype=dtype, max_tokens=1024)
+    rng = np.random.default_rng(6)
+    seqs = [rng.integers(0, 90, size=n).tolist() for n in (70, 12)]
+    refs = [_plain_arranged(c, w, s) for s in seqs]
+    tol = lambda r: TOL[dtype] * np.max(np.abs(r))          # noqa: E731
+    slots = [llm.acquire() for _ in seqs]
+    cut = [60, 5]
+    out = llm.step([StepEntry(s, q[:n], list(range(n))) for s, q, n in zip(slots, seqs, cut)]).cpu().numpy()
+    assert np.max(np.abs(out[:60] - refs[0][:60])) < tol(refs[0])
+    assert np.max(np.abs(out[60:] - refs[1][:5])) < tol(refs[1])
+    for k in range(7):                                      # one token each, from the cache
+        out = llm.step([StepEntry(slots[i], [seqs[i][cut[i] + k]], [0]) for i in (0, 1)]).cpu().numpy()
+        for i in (0, 1):
+            assert np.max(np.abs(out[i] - refs[i][cut[i] + k])) < tol(refs[i]), (i, k)
+    # a spec that does not give an arrangement its parts is refused with the names
+    from stratum_b200.engine.model import Layer
+    from stratum_b200.parts import LayerSpec, PartSpec
+    with pytest.raises(ValueError, match="missing \\['mixer'\\].*not known to it \\['mixr'\\]"):
+        Layer(LayerSpec("toy_parallel_shared_norm", {"norm": PartSpec("rmsnorm", {"size": 8, "eps": 1e-5}),
+                                                     "mixr": PartSpec("rmsnorm", {"size": 8, "eps": 1e-5}),
+                                                     "feed_forward": PartSpec("swiglu", {"hidden": 8,
+                                                                                         "intermediate": 8})},
+                        "x."), None)
