@@ -120,11 +120,15 @@ static int launch_rmsnorm(const float* x, const float* gain, const int* rows, T*
   if (vec && hidden <= 4 * 4 * 1024) {
     // few rows (decode steps): as many threads per row as it has float4s, the shortest path through one row;
     // many rows (prompts): blocks of about 128 threads, several of which share an SM and hide each other's waits
+    // On the float32 path the block shape follows from the row's length alone: the order of a row's sum is then
+    // the same however the tokens are cut into steps, and so are the bits of its result.
     const int n4 = hidden / 4;
-    if (n_rows < 256 && n4 <= 1024) return launch_rmsnorm_vec<T, 1>(x, gain, rows, out, n_rows, hidden, eps, stream);
+    const bool few = n_rows < 256 || sizeof(T) == 4;
+    if (few && n4 <= 1024) return launch_rmsnorm_vec<T, 1>(x, gain, rows, out, n_rows, hidden, eps, stream);
+    if (few) return launch_rmsnorm_vec<T, 4>(x, gain, rows, out, n_rows, hidden, eps, stream);
     if (n4 <= 256) return launch_rmsnorm_vec<T, 1>(x, gain, rows, out, n_rows, hidden, eps, stream);
     if (n4 <= 512) return launch_rmsnorm_vec<T, 2>(x, gain, rows, out, n_rows, hidden, eps, stream);
-    if (n4 <= 1024 && n_rows >= 256) return launch_rmsnorm_vec<T, 8>(x, gain, rows, out, n_rows, hidden, eps, stream);
+    if (n4 <= 1024) return launch_rmsnorm_vec<T, 8>(x, gain, rows, out, n_rows, hidden, eps, stream);
     return launch_rmsnorm_vec<T, 4>(x, gain, rows, out, n_rows, hidden, eps, stream);
   }
   const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);

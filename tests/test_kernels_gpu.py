@@ -77,7 +77,7 @@ def test_rmsnorm_heads_in_place(dtype, n_heads, head_dim, first):
     K.rmsnorm_heads(one, first, n_heads, head_dim, gain, 1e-6)
     assert torch.equal(one[0], x[4])
     with pytest.raises(K.KernelError):
-        K.rmsnorm_heads(x, first, n_heads + 1, head_dim, gain, 1e-6)      # would run past the row
+        K.rmsnorm_heads(x, first, n_heads + 2, head_dim, gain, 1e-6)      # would run past the row
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
