@@ -158,6 +158,7 @@ def time_decode(llm, batch, context, steps, warmup, vocab, rng):
             llm.decode_step(slots, toks[i])
         e1.record()
         torch.cuda.synchronize()
+        kernels.check_status()               # a kernel that gave up a wait makes the number worthless: raise
         return e0.elapsed_time(e1) / steps, (kernels.launch_count() - l0) / steps
     finally:
         for s in slots:
@@ -206,6 +207,48 @@ def time_e2e(llm, batch, context, steps, warmup, vocab, rng):
     torch.cuda.synchronize()
     t1 = time.perf_counter()
     return batch * steps / (t1 - marks["t0"])
+
+
+def run_workload(llm, cfg, n_layers, workload, shape, peaks, rng):
+    """The baseline's other two workloads, end to end through Stratum.generate (host ids in and out): 8 prompts
+    of uniform random lengths in [64, 2048] + 256 new tokens each, or 64 prompts of 512 + 512 new tokens each.
+    `decode_frac`: bytes the decode steps had to read (every weight once per step, the live requests' keys and
+    values) / decode time / the HBM peak."""
+    import torch
+    from stratum_b200 import kernels
+    vocab = cfg.vocab
+    if workload == "unequal8":
+        lens = [int(x) for x in rng.integers(64, 2049, size=8)]
+        new = 256
+    else:
+        lens = [512] * 64
+        new = 512
+    prompts = [rng.integers(0, vocab, size=n).tolist() for n in lens]
+    marks = {}
+
+    def on_token(req, index, fed, picked, logit):
+        if index == 0 and req == len(lens) - 1:
+            marks["first"] = time.perf_counter()
+
+    llm.generate([p[:8] for p in prompts[:2]], max_new_tokens=2, stop_ids=())     # compile and warm up
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    out = llm.generate(prompts, max_new_tokens=new, stop_ids=(), on_token=on_token)
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    kernels.check_status()
+    n_out = sum(len(r.tokens) for r in out)
+    decode_s = t1 - marks["first"]
+    # decode step k (k = 1 .. new-1) reads the weights once and, per request, the keys and values of len + k tokens
+    total = sum(decode_bytes(cfg, n_layers, 0, 0) + sum(decode_bytes(cfg, n_layers, 1, n + k) -
+                                                        decode_bytes(cfg, n_layers, 0, 0) for n in lens)
+                for k in range(1, new))
+    return {"workload": workload, "shape": shape, "prompt_tokens": sum(lens), "new_tokens": n_out,
+            "prompt_s": round(marks["first"] - t0, 4),
+            "prompt_tok_per_s": round(sum(lens) / (marks["first"] - t0), 1),
+            "decode_s": round(decode_s, 4),
+            "decode_tok_per_s": round((n_out - len(lens)) / decode_s, 1),
+            "decode_frac": round(total / decode_s / 1e9 / peaks["hbm_gbs"], 4)}
 
 
 def main() -> int:
@@ -269,32 +312,7 @@ def main() -> int:
     vocab = cfg.vocab
 
     if args.workload:
-        # the baseline's other two workloads, end to end through Stratum.generate (host ids in and out)
-        if args.workload == "unequal8":          # 8 prompts of uniform random lengths in [64, 2048], 256 new tokens each
-            lens = [int(x) for x in rng.integers(64, 2049, size=8)]
-            new = 256
-        else:                                    # 64 prompts of 512 tokens, 512 new tokens each
-            lens = [512] * 64
-            new = 512
-        prompts = [rng.integers(0, vocab, size=n).tolist() for n in lens]
-        marks = {}
-
-        def on_token(req, index, fed, picked, logit):
-            if index == 0 and req == len(lens) - 1:
-                marks["first"] = time.perf_counter()
-
-        llm.generate([p[:8] for p in prompts[:2]], max_new_tokens=2, stop_ids=())     # compile and warm up
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        out = llm.generate(prompts, max_new_tokens=new, stop_ids=(), on_token=on_token)
-        torch.cuda.synchronize()
-        t1 = time.perf_counter()
-        n_out = sum(len(r.tokens) for r in out)
-        print(json.dumps({"workload": args.workload, "shape": args.shape, "prompt_tokens": sum(lens),
-                          "new_tokens": n_out, "prompt_s": round(marks["first"] - t0, 4),
-                          "prompt_tok_per_s": round(sum(lens) / (marks["first"] - t0), 1),
-                          "decode_s": round(t1 - marks["first"], 4),
-                          "decode_tok_per_s": round((n_out - len(lens)) / (t1 - marks["first"]), 1)}))
+        print(json.dumps(run_workload(llm, cfg, n_layers, args.workload, args.shape, peaks, rng)))
         return 0
     if args.prefill_only:
         n_tok = args.prefill_tokens
@@ -323,6 +341,23 @@ def main() -> int:
         for b in (1, 64):
             ms_b, _ = time_decode(llm, b, args.context, max(8, args.steps // 2), 3, vocab, rng)
             points[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 1)
+
+        # the baseline's fourth and fifth configurations, each on a model of its own shape, through generate
+        del llm
+        torch.cuda.empty_cache()
+        for key, shape, workload, seqs, ctx in (("llama2_7b_unequal8", "llama2-7b", "unequal8", 8, 2304),
+                                                ("llama3_2_1b_batch64", "llama3.2-1b", "batch64", 64, 1024)):
+            raw_o = {k: v for k, v in OTHER_SHAPES[shape].items() if v is not None}
+            if args.layers:
+                raw_o["num_hidden_layers"] = min(args.layers, raw_o["num_hidden_layers"])
+            cfg_o = LlamaConfig.from_dict(raw_o)
+            other = Stratum.from_random(cfg_o, seed=0, dtype="bfloat16", max_tokens=seqs * (ctx + 64), max_seqs=seqs)
+            w = run_workload(other, cfg_o, cfg_o.n_layers, workload, shape, peaks, rng)
+            points[key + "_decode"] = w["decode_tok_per_s"]
+            points[key + "_decode_frac"] = w["decode_frac"]
+            points[key + "_prompt"] = w["prompt_tok_per_s"]
+            del other
+            torch.cuda.empty_cache()
 
     step_bytes = decode_bytes(cfg, n_layers, args.batch, args.context)
     achieved = step_bytes / (ms_step * 1e-3) / 1e9

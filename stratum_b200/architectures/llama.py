@@ -52,4 +52,6 @@ LLAMA = register_architecture(Architecture(
     names=("LlamaForCausalLM", "llama"),
     description="Llama dense decoder: GQA attention, rotary positions, SwiGLU, RMSNorm",
     config_class=LlamaConfig,
-    describe_model=describe_llama), replace=True)
+    describe_model=describe_llama,
+    # the rotation frequencies some exporters store as a buffer per layer; they follow from the configuration
+    ignored_tensor_suffixes=("rotary_emb.inv_freq",)), replace=True)

@@ -16,7 +16,9 @@ Switches carry the reference's environment-variable names as well: --temp / STRA
 (stratum/native/stratum_rope.h:55-64), --multiseq / STRATUM_MULTISEQ (B copies of the prompt in
 one batch, stratum/native/stratum_arch_llama.inc.c:1458-1524), --timing / STRATUM_TIMING (:2062-2070),
 --logits-dump / STRATUM_LOGITS_DUMP (stratum/native/stratum_engine.h:489-525), --ppl / STRATUM_PPL
-(stratum/native/stratum_arch_llama.inc.c:1535-1557).  Without a counterpart there: --batch-file FILE, one prompt
+(stratum/native/stratum_arch_llama.inc.c:1535-1557), --profile / STRATUM_TYPETIME (device time per kind of
+kernel, launch by launch, as the reference totals its matrix products per weight type, :2081-2091).
+Without a counterpart there: --batch-file FILE, one prompt
 per line, run as one batch of unequal lengths (every request's ids come out on a line of their own).
 """
 from __future__ import annotations
@@ -82,7 +84,7 @@ def main(argv=None) -> int:
     if not argv or argv[0] in ("-h", "--help"):
         print(_usage_with_architectures(), file=sys.stderr)
         print("\noptions: --dtype bfloat16|float32  --fp32  --temp T  --top-k K  --top-p P  --seed S  --stop ID\n"
-              "         --max-kv N  --multiseq B  --timing  --logits-dump PATH  --ppl  --batch-file FILE\n"
+              "         --max-kv N  --multiseq B  --timing  --profile  --logits-dump PATH  --ppl  --batch-file FILE\n"
               "         --random-weights SEED --config FILE   (write <model_dir> with random weights first)",
               file=sys.stderr)
         return 1
@@ -100,6 +102,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-kv", type=int, default=int(env.get("STRATUM_MAX_KV", 0) or 0))
     ap.add_argument("--multiseq", type=int, default=int(env.get("STRATUM_MULTISEQ", 0) or 0))
     ap.add_argument("--timing", action="store_true", default="STRATUM_TIMING" in env)
+    ap.add_argument("--profile", action="store_true", default="STRATUM_TYPETIME" in env)
     ap.add_argument("--logits-dump", default=env.get("STRATUM_LOGITS_DUMP", ""))
     ap.add_argument("--ppl", action="store_true", default="STRATUM_PPL" in env)
     ap.add_argument("--batch-file", default=None,
@@ -170,7 +173,8 @@ def main(argv=None) -> int:
     from .engine.api import Stratum
     B = len(prompts) if prompts else max(1, args.multiseq)
     try:
-        llm = Stratum(args.model_dir, dtype=dtype, max_tokens=B * (((capacity + 63) // 64) * 64), max_seqs=B)
+        llm = Stratum(args.model_dir, dtype=dtype, max_tokens=B * (((capacity + 63) // 64) * 64), max_seqs=B,
+                      use_graphs=not args.profile)      # a profile brackets every launch: no replayed graphs
     except (WeightError, SafetensorsError, RuntimeError) as e:
         print(f"  {e}", file=sys.stderr)
         return 1
@@ -199,6 +203,9 @@ def main(argv=None) -> int:
             print(picked, end=" ", flush=True)
 
     import torch
+    from . import kernels
+    if args.profile:
+        kernels.profile_start()
     t0 = time.perf_counter()
     on_logits = None
     if dump is not None:
@@ -211,6 +218,8 @@ def main(argv=None) -> int:
             print(f"  request {i}: prompt {len(prompts[i])} tok, {len(r.tokens)} generated, ended by {r.finish_reason}",
                   file=sys.stderr)
             print(" ".join(map(str, r.tokens)), flush=True)
+        if args.profile:
+            _print_profile(kernels.profile_report())
         return 0
     results = llm.generate([prompt] * B, max_new_tokens=n_gen + 1, stop_ids=args.stop, sampling=params,
                            on_token=on_token, want_values=True, on_logits=on_logits)
@@ -224,6 +233,8 @@ def main(argv=None) -> int:
             return 1
     if dump is not None:
         dump.close()
+    if args.profile:
+        _print_profile(kernels.profile_report())
     if args.timing:
         pf = times.get("prefill_end", t1) - t0
         gn = t1 - times.get("prefill_end", t1)
@@ -232,6 +243,12 @@ def main(argv=None) -> int:
               f"gen {n_dec} tok: {gn:.3f}s ({1000 * gn / n_dec:.1f} ms/tok, {B * n_dec / gn:.1f} tok/s)",
               file=sys.stderr)
     return 0
+
+
+def _print_profile(rows) -> None:
+    print("  [profile] device time per kernel launcher (launch by launch, CUDA events):", file=sys.stderr)
+    for name, calls, secs in rows:
+        print(f"    {name:<18} {secs:.4f}s over {calls} calls ({1000.0 * secs / calls:.3f} ms/call)", file=sys.stderr)
 
 
 class _LogitsDump:
@@ -253,7 +270,7 @@ def _perplexity(llm, prompt: List[int]) -> int:
     """Teacher-forced negative log-likelihood of the prompt from the engine's own logits."""
     from .engine.step import StepEntry
     slot = llm.acquire()
-    logits = llm.step([StepEntry(slot, prompt, list(range(len(prompt) - 1)))]).double().cpu().numpy()
+    logits = llm.step([StepEntry(slot, prompt, list(range(len(prompt) - 1)))]).cpu().numpy().astype("float64")
     llm.release(slot)
     nll, n = 0.0, 0
     for t in range(len(prompt) - 1):

@@ -18,6 +18,9 @@ class Architecture:
     description: str
     config_class: Type[ModelConfig]
     describe_model: Callable[[ModelConfig], Any]  # typed config -> parts.spec.ModelSpec
+    # tensors a published file may carry that the model does not use (buffers, not weights): names ending in one
+    # of these are left alone by the loader instead of being reported as unexpected
+    ignored_tensor_suffixes: Tuple[str, ...] = ()
 
 
 _ARCHITECTURES: List[Architecture] = []

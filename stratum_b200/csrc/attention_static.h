@@ -16,9 +16,11 @@
 // Contract.
 //  * Same arguments and same result as stratum_attention_mma, minus the two scratch pointers.
 //    Inputs and outputs are still the caller's.
-//  * Needs tokens * n_q * n_splits * (head_dim + 2) <= STRATUM_ATTENTION_STATIC_SCRATCH_FLOATS;
+//  * With n_splits > 1 it needs, for s = tokens * n_q * n_splits,
+//        round_up(s * head_dim, 64) + 2 * s  <=  STRATUM_ATTENTION_STATIC_SCRATCH_FLOATS;
 //    a larger request is refused with STRATUM_ERR_LIMIT (-4) before anything is launched.  With the
 //    Llama-3.1-8B shape (32 heads of 128) and 16 splits that is up to 63 sequences per decode step.
+//    With n_splits == 1 no scratch is used and no limit applies.
 //  * It calls no cudaMalloc, cudaFree or any allocating routine.  The first call on a device looks
 //    up the array's device address (cudaGetSymbolAddress, with that device current) and remembers
 //    it; that first call should be made before any stream capture begins.

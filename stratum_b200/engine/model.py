@@ -6,6 +6,7 @@ in which order layers run and whose cache each stop uses.
 """
 from __future__ import annotations
 
+import hashlib
 import os
 from typing import Dict, List, Mapping, Optional, Tuple
 
@@ -150,7 +151,7 @@ def load_model(model_dir: str, dtype: torch.dtype, device="cuda") -> Tuple[Model
     config, arch = config_from_dir(model_dir)
     runtime = Runtime(dtype, device)
     model = Model(arch.describe_model(config), runtime)
-    weights = load_weights(model_dir, model.tensors(), dtype, runtime.device)
+    weights = load_weights(model_dir, model.tensors(), dtype, runtime.device, arch.ignored_tensor_suffixes)
     model.bind(weights)
     return model, config
 
@@ -162,7 +163,7 @@ def model_from_tensors(config: ModelConfig, tensors: Mapping[str, torch.Tensor],
     runtime = Runtime(dtype, device)
     model = Model(arch.describe_model(config), runtime)
     expected = model.tensors()
-    check_tensors("tensors in memory", expected, tensors)
+    check_tensors("tensors in memory", expected, tensors, arch.ignored_tensor_suffixes)
     placed = {n: place(tensors[n], s, dtype, runtime.device) for n, s in expected.items() if n in tensors}
     model.bind(placed)
     return model
@@ -176,7 +177,7 @@ def random_model_on_device(config: ModelConfig, seed: int, dtype: torch.dtype, d
     runtime = Runtime(dtype, device)
     model = Model(arch.describe_model(config), runtime)
     weights: Dict[str, torch.Tensor] = {}
-    for i, (name, ts) in enumerate(model.tensors().items()):
+    for name, ts in model.tensors().items():
         if ts.optional:
             continue
         dt = torch.float32 if ts.role in ("vector", "keep") else dtype
@@ -186,7 +187,10 @@ def random_model_on_device(config: ModelConfig, seed: int, dtype: torch.dtype, d
         elif ts.init == "zeros":
             t.zero_()
         else:
-            K.fill_normal(t, (seed << 20) + i, std)
+            # keyed by (seed, tensor name, element index): a tensor's values do not depend on which other
+            # tensors the model has or in which order they are made
+            key = int.from_bytes(hashlib.sha256(f"{seed}:{name}".encode()).digest()[:8], "little")
+            K.fill_normal(t, key, std)
         weights[name] = t
     model.bind(weights)
     return model

@@ -85,17 +85,60 @@ def _need(t: torch.Tensor, name: str, dtype=None, contiguous: bool = True) -> No
 
 
 _sigs_done = set()
+_profile: Optional[list] = None          # (function name, start event, end event) per launch while profiling
+
+
+def profile_start() -> None:
+    """From now on every launch made through this module is bracketed by two CUDA events (for launch-by-launch
+    runs; launches replayed inside a CUDA graph are not seen)."""
+    global _profile
+    _profile = []
+
+
+def profile_report():
+    """Stop profiling; [(function, calls, seconds on the device)] sorted by time, the reference's per-kind
+    totals (stratum/native/stratum_arch_llama.inc.c:2081-2091) with kernels in place of weight types."""
+    global _profile
+    rows, _profile = _profile or [], None
+    torch.cuda.synchronize()
+    totals = {}
+    for name, e0, e1 in rows:
+        calls, secs = totals.get(name, (0, 0.0))
+        totals[name] = (calls + 1, secs + e0.elapsed_time(e1) * 1e-3)
+    return sorted(((n, c, t) for n, (c, t) in totals.items()), key=lambda r: -r[2])
+
+
+class _Timed:
+    """A launcher whose calls are bracketed by events while profiling is on."""
+    __slots__ = ("f", "name")
+
+    def __init__(self, f, name):
+        self.f, self.name = f, name
+
+    def __call__(self, *args):
+        if _profile is None:
+            return self.f(*args)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        status = self.f(*args)
+        e1.record()
+        _profile.append((self.name, e0, e1))
+        return status
+
+
+_timed = {}
 
 
 def _fn(libname: str, fname: str, argtypes):
-    lib = build.load(libname)
-    f = getattr(lib, fname)
     key = (libname, fname)
-    if key not in _sigs_done:
+    t = _timed.get(key)
+    if t is None:
+        lib = build.load(libname)
+        f = getattr(lib, fname)
         f.argtypes = argtypes
         f.restype = c_int
-        _sigs_done.add(key)
-    return f
+        t = _timed[key] = _Timed(f, fname.replace("stratum_", "", 1))
+    return t if _profile is not None else t.f
 
 
 # ------------------------------------------------------------------ elementwise

@@ -15,7 +15,7 @@ tables become int32.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Mapping
+from typing import Dict, List, Mapping, Sequence
 
 import torch
 
@@ -42,10 +42,12 @@ _FLOATS = (torch.float32, torch.bfloat16, torch.float16, torch.float64)
 _INTS = (torch.int32, torch.int64, torch.int16, torch.int8, torch.uint8)
 
 
-def check_tensors(where: str, expected: Mapping[str, TensorSpec], present: Mapping[str, object]) -> None:
-    """`present`: name -> object with .shape and .dtype.  Raises WeightError if they disagree."""
+def check_tensors(where: str, expected: Mapping[str, TensorSpec], present: Mapping[str, object],
+                  ignored_suffixes: Sequence[str] = ()) -> None:
+    """`present`: name -> object with .shape and .dtype.  Raises WeightError if they disagree.
+    ignored_suffixes: names ending in one of these are no weights of the model and may be present."""
     missing = [n for n, s in expected.items() if n not in present and not s.optional]
-    unexpected = [n for n in present if n not in expected]
+    unexpected = [n for n in present if n not in expected and not n.endswith(tuple(ignored_suffixes) or ("\0",))]
     wrong = []
     for n, s in expected.items():
         if n not in present:
@@ -78,7 +80,7 @@ def place(t: torch.Tensor, spec: TensorSpec, compute_dtype: torch.dtype, device)
 
 
 def load_weights(model_dir: str, expected: Mapping[str, TensorSpec], compute_dtype: torch.dtype,
-                 device) -> Dict[str, torch.Tensor]:
+                 device, ignored_suffixes: Sequence[str] = ()) -> Dict[str, torch.Tensor]:
     """Read every expected tensor of a model folder onto the device."""
     files = open_model_files(model_dir)
     try:
@@ -90,7 +92,7 @@ def load_weights(model_dir: str, expected: Mapping[str, TensorSpec], compute_dty
                     raise SafetensorsError(f"{model_dir}: tensor {n!r} appears in two shards")
                 present[n] = e
                 owner[n] = f
-        check_tensors(model_dir, expected, present)
+        check_tensors(model_dir, expected, present, ignored_suffixes)
         out = {}
         for n, s in expected.items():
             if n in present:

@@ -116,6 +116,14 @@ def test_command_line_prints_the_reference_lines(folders):
     for g in range(4):
         assert f"step {g:2d}  in={expect[g]}  stratum_argmax={expect[g + 1]}  logit=" in r.stderr
     assert "[timing] prefill 8 tok" in r.stderr
+    # --profile: the same tokens launch by launch, and device time per kind of kernel
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "stratum"), path, "4", *map(str, prompt), "--fp32",
+                        "--profile"], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr
+    assert r.stdout.split() == [str(t) for t in expect]
+    prof = r.stderr[r.stderr.index("[profile]"):]
+    for name in ("linear_simple", "attention_simple", "rmsnorm", "rope_store", "embed_gather", "argmax"):
+        assert f"    {name} " in prof and " calls (" in prof, prof
     # errors: id outside the vocabulary, prompt beyond capacity; nonzero exit, as the reference
     r = subprocess.run([sys.executable, os.path.join(ROOT, "stratum"), path, "2", "999"], capture_output=True,
                        text=True, timeout=600)

@@ -41,3 +41,28 @@ def test_greedy_ids_match_reference_pins():
         prompt = z[f"run{ri}:prompt"].tolist()
         greedy = z[f"run{ri}:greedy"].tolist()
         assert P.greedy_generate(cfg, w, prompt, len(greedy)) == greedy
+
+
+def test_rotation_frequencies_match_the_reference_header():
+    """no scaling, linear and YaRN (ramp, clamps, derived and explicit magnitude) against what the reference's
+    stratum/native/stratum_rope.h computes (tests/golden/make_rope_golden.py compiled and ran it)."""
+    with open(os.path.join(os.path.dirname(GOLD), "rope_reference.json")) as f:
+        cases = json.load(f)
+    assert len(cases) == 5
+    for name, c in cases.items():
+        scaling = None
+        if c["type"] != "none":
+            scaling = {"rope_type": c["type"], "factor": c["factor"],
+                       "original_max_position_embeddings": c["original_max_position"],
+                       "beta_fast": c["beta_fast"], "beta_slow": c["beta_slow"]}
+            if c["attention_factor"] > 0:
+                scaling["attention_factor"] = c["attention_factor"]
+        inv = P.rope_inv_freq(2 * c["pairs"], c["theta"], scaling)
+        ref = np.asarray(c["inv_freq"])
+        assert inv.shape == ref.shape
+        assert np.max(np.abs(inv - ref) / ref) < 2e-6, name          # float32 powf/logf against float64
+        assert abs(P.rope_magnitude(scaling) - c["mscale"]) < 1e-6, name
+    yarn = np.asarray(cases["yarn_f4_orig32_80"]["inv_freq"])
+    plain = P.rope_inv_freq(80, 50000.0)
+    ratio = plain / yarn
+    assert np.isclose(ratio[0], 1.0) and np.isclose(ratio[-1], 4.0) and np.any((ratio > 1.05) & (ratio < 3.9))

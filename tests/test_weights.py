@@ -119,6 +119,27 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
     assert len(err.wrong) == 2
     msg = str(err)
     assert "missing (2)" in msg and "unexpected (1)" in msg and "[64, 32]" in msg and "[64, 64]" in msg
+    # an architecture may name buffers that published files carry and the model does not use: those pass,
+    # everything else about the file is still reported
+    from stratum_b200.config import find_architecture
+    ignore = find_architecture(TINY_A).ignored_tensor_suffixes
+    assert "rotary_emb.inv_freq" in ignore
+    with pytest.raises(WeightError) as e:
+        load_weights(d, expected_tensors(cfg), torch.float32, "cpu", ignore)
+    assert e.value.unexpected == [] and len(e.value.missing) == 2 and len(e.value.wrong) == 2
+
+
+def test_buffers_on_the_ignore_list_do_not_stop_a_load(tmp_path):
+    def edit(t):
+        for i in range(2):
+            t[f"model.layers.{i}.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    d = make_model_dir(str(tmp_path / "m"), TINY_A, seed=0, edit=edit)
+    from stratum_b200.engine.model import config_from_dir
+    cfg, arch = config_from_dir(d)
+    w = load_weights(d, expected_tensors(cfg), torch.float32, "cpu", arch.ignored_tensor_suffixes)
+    assert not any(n.endswith("inv_freq") for n in w)
+    with pytest.raises(WeightError, match="unexpected \\(2\\)"):
+        load_weights(d, expected_tensors(cfg), torch.float32, "cpu")
 
 
 def test_untied_model_needs_its_head(tmp_path):

@@ -60,6 +60,18 @@ def test_static_scratch_entry_point_matches_the_regular_one():
         assert rel_err(as64(got), c["ref"]) < 8e-3             # and against the plain reference itself
         assert torch.equal(got, want)                           # same kernels, same inputs: the same bits
 
+    # one split uses no scratch, so a step far beyond the scratch's size is taken as the regular entry point
+    # takes it: 1,100 sequences x 32 heads x 130 floats would be 4.6 M floats, more than the array holds
+    lens = [int(x) for x in rng.integers(0, 3, size=1100)]
+    c = _attention_case(rng, lens, [1] * len(lens), 32, 8, 128, "bfloat16")
+    want = _run_mma(c, [1] * len(lens), 32, 8, 128, n_splits=1, chunk=64)
+    status, got = _call_static(lib, c, 32, 8, 128, 1, 64)
+    torch.cuda.synchronize()
+    assert status == 0 and torch.equal(got, want)
+    assert rel_err(as64(got), c["ref"]) < 8e-3
+    status, _ = _call_static(lib, c, 32, 8, 128, 2, 64)        # the same step in two splits does need it
+    assert status == -4
+
     # beyond the built-in scratch: refused before anything is launched
     c = _attention_case(rng, [10] * 4, [1] * 4, 8, 2, 128, "bfloat16")
     status, _ = _call_static(lib, c, 8, 2, 128, 40000, 64)
