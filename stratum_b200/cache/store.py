@@ -25,10 +25,13 @@ from .pages import (PAGE_TOKENS, CacheFull, CacheMisuse, PagePool, SequencePages
 
 @dataclass(frozen=True)
 class KVSpec:
-    """Keys and values per token: `window` = 0 keeps all of them, W > 0 the last W."""
+    """Keys and values per token: `window` = 0 keeps all of them, W > 0 the last W.  `key_order` names the order
+    in which a mixer keeps the dimensions of a key (mixers that share a cache must agree on it, so it is part of
+    what makes two specs equal)."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    key_order: str = "as_projected"
 
 
 @dataclass(frozen=True)

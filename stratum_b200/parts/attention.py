@@ -8,6 +8,13 @@ o_h = sum_t p_t V_t[kv(h)]; residual += Wo o.  kv(h) = h / (n_heads / n_kv_heads
 (stratum/native/stratum_arch_llama.inc.c:398-524.)  The three projections run as one matrix
 product over a weight made by stacking their rows (the reference fuses them at dispatch time,
 stratum/native/stratum_linear.h:1086-1121).
+
+Where the position encoding rotates pairs (k, k + n_pairs), the rows of Wq and Wk (and their biases, and the
+gains of the per-head norms) are reordered once, when the weights are bound, so that a pair's two dimensions
+are neighbours (2k, 2k+1): q . k is the same sum in another order, the rotation touches neighbours only, and a
+matrix product's epilogue can rotate what one thread (or two neighbouring lanes) holds.  The reference's
+converter does the same to its Llama files, which is why its handler rotates neighbours
+(stratum/native/stratum_arch_llama.inc.c:82-87).  Keys therefore lie in the cache in that order.
 """
 from __future__ import annotations
 
@@ -75,22 +82,48 @@ class GQAAttention(Mixer):
                 t.update(norm.tensors())
         return t
 
+    def _pair_order(self) -> Optional[torch.Tensor]:
+        """For every dimension of a head, the projected dimension that takes its place (None: as projected)."""
+        layout = self.position.pair_layout() if self.position is not None else None
+        if layout is None or layout[1]:
+            return None
+        n_pairs = layout[0]
+        order = list(range(self.head_dim))
+        for k in range(n_pairs):
+            order[2 * k], order[2 * k + 1] = k, k + n_pairs
+        return torch.tensor(order, dtype=torch.long)
+
     def bind(self, weights: Mapping[str, torch.Tensor]) -> None:
-        p = self.prefix
-        w = torch.cat([weights[p + "q_proj.weight"], weights[p + "k_proj.weight"],
+        p, D = self.prefix, self.head_dim
+        order = self._pair_order()
+
+        def heads(t: torch.Tensor, n: int) -> torch.Tensor:
+            """Rows (or entries) of n heads, each head's dimensions in the cache's order."""
+            if order is None:
+                return t
+            idx = (torch.arange(n).unsqueeze(1) * D + order.unsqueeze(0)).reshape(-1).to(t.device)
+            return t.index_select(0, idx)
+
+        w = torch.cat([heads(weights[p + "q_proj.weight"], self.n_heads),
+                       heads(weights[p + "k_proj.weight"], self.n_kv_heads),
                        weights[p + "v_proj.weight"]], dim=0).contiguous()
         b = None
         if self.bias:
-            b = torch.cat([weights[p + "q_proj.bias"], weights[p + "k_proj.bias"],
+            b = torch.cat([heads(weights[p + "q_proj.bias"], self.n_heads),
+                           heads(weights[p + "k_proj.bias"], self.n_kv_heads),
                            weights[p + "v_proj.bias"]]).contiguous()
         self.qkv = Linear(self.runtime, w, b)
         self.o = Linear(self.runtime, weights[p + "o_proj.weight"], weights.get(p + "o_proj.bias"))
         for norm in (self.q_norm, self.k_norm):
             if norm is not None:
-                norm.bind(weights)
+                names = list(norm.tensors())
+                norm.bind({n: heads(weights[n], 1).contiguous() if weights[n].shape == (D,) else weights[n]
+                           for n in names if n in weights})
 
     def cache_spec(self) -> KVSpec:
-        return KVSpec(self.n_kv_heads, self.head_dim, self.window)
+        reordered = self._pair_order() is not None
+        return KVSpec(self.n_kv_heads, self.head_dim, self.window,
+                      f"pairs_adjacent_{self.position.pair_layout()[0]}" if reordered else "as_projected")
 
     def forward(self, xn: torch.Tensor, residual: torch.Tensor, step, cache: LayerCache) -> None:
         qkv = self.qkv(xn, mode=STORE)
@@ -100,7 +133,7 @@ class GQAAttention(Mixer):
             self.k_norm.forward_heads(qkv, self.n_heads * self.head_dim, self.n_kv_heads, self.head_dim)
         rot = self.position.rotary() if self.position is not None else None
         K.rope_store(qkv, step.token_pos, step.token_seq, cache.block_table,
-                     None if rot is None else rot.inv_freq, bool(rot and rot.interleaved),
+                     None if rot is None else rot.inv_freq, rot is not None,       # pairs are neighbours: see bind
                      1.0 if rot is None else rot.magnitude, cache.k, cache.v,
                      self.n_heads, self.n_kv_heads, self.head_dim, PAGE_TOKENS, cache.writes)
         out = self.runtime.empty(xn.shape[0], self.n_heads * self.head_dim)

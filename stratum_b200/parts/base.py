@@ -79,6 +79,12 @@ class PositionEncoding(Part):
         """Frequencies for a mixer that rotates queries and keys, or None if this encoding does not rotate."""
         return None
 
+    def pair_layout(self):
+        """(number of rotated pairs, interleaved) of a rotating encoding, or None; asked for when weights are
+        bound and when a model is only described, so it must not need a device."""
+        rot = self.rotary()
+        return None if rot is None else (int(rot.inv_freq.numel()), bool(rot.interleaved))
+
     def add_to_embedding(self, x: torch.Tensor, step) -> None:
         """Hook for encodings that act on the embedded tokens; the default does nothing."""
 

@@ -86,6 +86,9 @@ class RotaryEmbedding(PositionEncoding):
         self.scaling = spec.get("scaling")
         self._table: Optional[RotaryTable] = None
 
+    def pair_layout(self):
+        return self.rope_dim // 2, self.interleaved
+
     def rotary(self) -> RotaryTable:
         if self._table is None:
             inv, mag = inverse_frequencies(self.rope_dim, self.theta, self.scaling)

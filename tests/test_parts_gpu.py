@@ -142,7 +142,7 @@ def _attention_setup(dtype, n_heads, n_kv, hd, hidden, window, position, bias, l
         PartSpec("gqa_attention", {"hidden": hidden, "n_heads": n_heads, "n_kv_heads": n_kv, "head_dim": hd,
                                    "bias": bias, "window": window, "scale": None, "position": position,
                                    "prefix": "a."}), rt)
-    assert part.cache_spec() == KVSpec(n_kv, hd, window)
+    assert part.cache_spec() == KVSpec(n_kv, hd, window, part.cache_spec().key_order)
     w = _weights(part, rng, dtype, std=0.15)
     part.bind(w)
     cache = SequenceCache([part.cache_spec()], 64 * 40, 8, DT[dtype], "cuda")
