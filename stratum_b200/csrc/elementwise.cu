@@ -384,6 +384,31 @@ STRATUM_EXPORT int stratum_rope_store(void* qkv, int dtype, const int* token_pos
   return STRATUM_ERR_DTYPE;
 }
 
+// ---------------------------------------------------------------- rotation factors of a step, once
+// cs[t][k] = mscale * (cos, sin)((float)pos[t] * inv_freq[k]): the same arithmetic as in rope_store_kernel, evaluated
+// once per step for every token, for the matrix-product epilogues that rotate queries and keys (every layer of
+// the step reads the same table).
+__global__ void rope_table_kernel(const int* __restrict__ token_pos, const float* __restrict__ inv_freq, float mscale,
+                                  float2* __restrict__ cs, int n_tokens, int n_pairs) {
+  pdl_trigger();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_tokens * n_pairs) return;
+  const int t = i / n_pairs, k = i - t * n_pairs;
+  float s, c;
+  sincosf((float)token_pos[t] * inv_freq[k], &s, &c);
+  pdl_wait();                                    // an earlier kernel may still read the table of the step before
+  cs[i] = make_float2(c * mscale, s * mscale);
+}
+
+STRATUM_EXPORT int stratum_rope_table(const int* token_pos, const float* inv_freq, float mscale, float* cs,
+                                      int n_tokens, int n_pairs, cudaStream_t stream) {
+  if (n_tokens <= 0 || n_pairs <= 0) return 0;
+  const long long total = (long long)n_tokens * n_pairs;
+  if (total > (1ll << 30)) return STRATUM_ERR_LIMIT;
+  return launch_pdl(rope_table_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, token_pos, inv_freq, mscale,
+                    (float2*)cs, n_tokens, n_pairs);
+}
+
 // ---------------------------------------------------------------- seeded fill (random weights on the device)
 // value = std * z, z standard normal from a counter-based hash of (seed, element index): Box-Muller over
 // two 24-bit uniforms.  Filling a tensor in pieces or whole gives the same values.

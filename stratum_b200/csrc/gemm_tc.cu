@@ -31,6 +31,46 @@
 
 static int g_last_launches = 0;       // kernels the last stratum_gemm_tc call launched (for launch counting)
 
+// Work an epilogue may do beyond its basic form.  Every part is off while its pointer is null.
+//
+// (1) norm_ss: the rows of x were handed over by a norm that did not write them out in full: x holds r * gain
+//     (r: the residual row), and the row's factor 1 / sqrt(sum r^2 / size + eps) is applied here, to the product.
+//     norm_ss[p * norm_ld + m], p < norm_parts, are partial sums of r^2 of row m; they are added in the order of p.
+// (2) emit_x (epilogue 4, which adds into the float32 residual stream as epilogue 1 does): for the norm that
+//     follows, also write emit_x[m][n] = bf16(r * emit_gain[n]) for the new residual values r, and
+//     emit_ss[part * emit_ld + m] = the sum of r^2 over this tile's columns, part being the tile's number along N
+//     (tiles of 128 columns in the forms for few rows; every (part, m) is written exactly once).
+// (3) epilogue 5: the columns are the query heads, then the key heads, then the value heads of an attention layer,
+//     the two dimensions of a rotated pair being neighbours.  Queries are rotated and stored to `out`; keys are
+//     rotated and written, and values written, to the row's place in the paged cache (rows whose token_seq is
+//     negative write nothing there).  rope_cs[m][k] = (cos, sin) of row m's angle for pair k; null: no rotation.
+struct EpiExtra {
+  const float* norm_ss;
+  bf16* emit_x; const float* emit_gain; float* emit_ss;
+  const float2* rope_cs; const int* token_pos; const int* token_seq; const int* block_table;
+  bf16* k_cache; bf16* v_cache;
+  int norm_parts, norm_ld; float norm_size, norm_eps;
+  int emit_ldx, emit_ld;
+  int rope_pairs, bt_stride, n_q, n_kv, head_dim, page_tokens, write_cache;
+  int reserved;
+};
+
+__device__ __forceinline__ float epi_row_scale(const EpiExtra& X, int m) {
+  float t = 0.f;
+  for (int p = 0; p < X.norm_parts; p++) t += __ldcg(X.norm_ss + (size_t)p * X.norm_ld + m);
+  return 1.0f / sqrtf(t / X.norm_size + X.norm_eps);
+}
+
+// Element offset, in the key or value cache, of (the page of row m's position, kv head 0, the position's place in
+// the page, dimension 0); -1 if the row writes nothing there.  Cache layout: [pages][kv heads][page_tokens][head_dim].
+__device__ __forceinline__ long long epi_cache_row(const EpiExtra& X, int m) {
+  const int seq = X.token_seq[m];
+  if (seq < 0 || !X.write_cache) return -1;
+  const int pos = X.token_pos[m];
+  const int page = X.block_table[(size_t)seq * X.bt_stride + pos / X.page_tokens];
+  return ((long long)page * X.n_kv * X.page_tokens + (pos % X.page_tokens)) * (long long)X.head_dim;
+}
+
 struct TcParams {
   const float* bias;
   void* out;
@@ -39,7 +79,27 @@ struct TcParams {
   int ldo;
   int split;          // 1: the tiles left over after the full waves are cut along k and shared by all CTAs
   float* scratch;     // [gridDim.x][2][BN][128] float32: up to two partial tiles per CTA (split only)
+  EpiExtra X;
 };
+
+// What the thread that owns output row m (one token) carries through the columns of a tile.
+struct EpiRow {
+  float scale;        // factor of a handed-over norm (1 if none)
+  float ss;           // epilogue 4: sum of squares of the row's new residual values in this tile
+  long long cache;    // epilogue 5: epi_cache_row
+};
+template <int EPI>
+__device__ __forceinline__ EpiRow epi_row_begin(const EpiExtra& X, int m, int M) {
+  EpiRow r;
+  r.scale = (X.norm_ss && m < M) ? epi_row_scale(X, m) : 1.0f;
+  r.ss = 0.f;
+  r.cache = (EPI == 5 && m < M) ? epi_cache_row(X, m) : -1;
+  return r;
+}
+template <int EPI>
+__device__ __forceinline__ void epi_row_end(const EpiExtra& X, const EpiRow& r, int part, int m, int M) {
+  if (EPI == 4 && X.emit_ss && m < M) X.emit_ss[(size_t)part * X.emit_ld + m] = r.ss;
+}
 
 template <int BN, int STAGES>
 struct TcSmem {
@@ -50,17 +110,58 @@ struct TcSmem {
   int abort_flag;
 };
 
-// Output row m, columns col0 .. col0 + CW - 1 (contiguous in memory): bias, then the epilogue.
-// EPI: 0 store bf16, 1 add into float32, 2 store float32, 3 SwiGLU pairs -> bf16.
+// Output row m, columns col0 .. col0 + CW - 1 (contiguous in memory): the row's factor, bias, then the epilogue.
+// EPI: 0 store bf16, 1 add into float32, 2 store float32, 3 SwiGLU pairs -> bf16, 4 as 1 and hand on to the next
+// norm, 5 queries / keys / values of an attention layer (see EpiExtra).
 template <int EPI, int CW>
-__device__ __forceinline__ void tc_store_chunk(const TcParams& P, int m, int col0, float (&v)[CW]) {
+__device__ __forceinline__ void tc_store_chunk(const TcParams& P, int m, int col0, float (&v)[CW], EpiRow& R) {
+  if (R.scale != 1.0f) {
+#pragma unroll
+    for (int j = 0; j < CW; j++) v[j] *= R.scale;
+  }
   if (P.bias) {
 #pragma unroll
     for (int j = 0; j < CW; j++)
       if (col0 + j < P.N) v[j] += P.bias[col0 + j];
   }
   const bool whole = col0 + CW <= P.N;
-  if (EPI == 3) {
+  if (EPI == 5) {
+    // (the host checked: head_dim % CW == 0, so a chunk lies inside one head; N % CW == 0; 16-byte aligned rows)
+    if (!whole) return;
+    const EpiExtra& X = P.X;
+    const int h = col0 / X.head_dim, d0 = col0 - h * X.head_dim;
+    const bool is_q = h < X.n_q, is_k = !is_q && h < X.n_q + X.n_kv;
+    if ((is_q || is_k) && X.rope_cs) {
+      const float2* cs = X.rope_cs + (size_t)m * X.rope_pairs + (d0 >> 1);
+#pragma unroll
+      for (int j = 0; j < CW; j += 2) {
+        if ((d0 + j) >> 1 < X.rope_pairs) {
+          const float2 f = __ldg(cs + (j >> 1));
+          const float x0 = v[j], x1 = v[j + 1];
+          v[j] = x0 * f.x - x1 * f.y;
+          v[j + 1] = x0 * f.y + x1 * f.x;
+        }
+      }
+    }
+    bf16* o;
+    if (is_q) {
+      o = (bf16*)P.out + (size_t)m * P.ldo + col0;
+    } else {
+      if (R.cache < 0) return;
+      const int kvh = is_k ? h - X.n_q : h - X.n_q - X.n_kv;
+      o = (is_k ? X.k_cache : X.v_cache) + R.cache + (long long)kvh * X.page_tokens * X.head_dim + d0;
+    }
+#pragma unroll
+    for (int q = 0; q < CW / 8; q++) {
+      uint32_t w4[4];
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        __nv_bfloat162 pr = __floats2bfloat162_rn(v[8 * q + 2 * e], v[8 * q + 2 * e + 1]);
+        w4[e] = *reinterpret_cast<uint32_t*>(&pr);
+      }
+      reinterpret_cast<uint4*>(o)[q] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+    }
+  } else if (EPI == 3) {
     bf16* o = (bf16*)P.out + (size_t)m * P.ldo + (col0 >> 1);
     uint32_t packed[CW / 4];
 #pragma unroll
@@ -107,20 +208,49 @@ __device__ __forceinline__ void tc_store_chunk(const TcParams& P, int m, int col
     }
   } else {
     float* o = (float*)P.out + (size_t)m * P.ldo + col0;
+    constexpr bool ADD = EPI == 1 || EPI == 4;
     if (whole && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
 #pragma unroll
       for (int q = 0; q < CW / 4; q++) {
         float4 w4 = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-        if (EPI == 1) {
+        if (ADD) {
           const float4 old = ld_fresh(reinterpret_cast<const float4*>(o) + q);
           w4.x += old.x; w4.y += old.y; w4.z += old.z; w4.w += old.w;
         }
         reinterpret_cast<float4*>(o)[q] = w4;
+        if (EPI == 4) { v[4 * q] = w4.x; v[4 * q + 1] = w4.y; v[4 * q + 2] = w4.z; v[4 * q + 3] = w4.w; }
       }
     } else {
 #pragma unroll
-      for (int j = 0; j < CW; j++)
-        if (col0 + j < P.N) o[j] = (EPI == 1) ? ld_fresh(o + j) + v[j] : v[j];
+      for (int j = 0; j < CW; j++) {
+        if (col0 + j < P.N) { v[j] = ADD ? ld_fresh(o + j) + v[j] : v[j]; o[j] = v[j]; }
+        else v[j] = 0.f;
+      }
+    }
+    if (EPI == 4 && P.X.emit_x) {
+      // v now holds the new residual values: their squares for the norm's sum, and r * gain in bf16 for the
+      // product behind the norm
+      bf16* e = P.X.emit_x + (size_t)m * P.X.emit_ldx + col0;
+#pragma unroll
+      for (int j = 0; j < CW; j++) R.ss = fmaf(v[j], v[j], R.ss);
+      if (whole && ((reinterpret_cast<uintptr_t>(e) & 15) == 0)) {
+#pragma unroll
+        for (int q = 0; q < CW / 8; q++) {
+          uint32_t w4[4];
+#pragma unroll
+          for (int k = 0; k < 4; k++) {
+            const int j = 8 * q + 2 * k;
+            __nv_bfloat162 pr = __floats2bfloat162_rn(v[j] * __ldg(P.X.emit_gain + col0 + j),
+                                                      v[j + 1] * __ldg(P.X.emit_gain + col0 + j + 1));
+            w4[k] = *reinterpret_cast<uint32_t*>(&pr);
+          }
+          reinterpret_cast<uint4*>(e)[q] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < CW; j++)
+          if (col0 + j < P.N) e[j] = __float2bfloat16_rn(v[j] * P.X.emit_gain[col0 + j]);
+      }
     }
   }
 }
@@ -160,12 +290,12 @@ __device__ __forceinline__ void fixup_store(const PT& P, int m, int n, float4 v)
     float* o = (float*)P.out + idx;
     if (wide && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
       float4 r = make_float4(e[0], e[1], e[2], e[3]);
-      if (EPI == 1) { const float4 old = __ldcg(reinterpret_cast<const float4*>(o)); r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w; }
+      if (EPI == 1 || EPI == 4) { const float4 old = __ldcg(reinterpret_cast<const float4*>(o)); r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w; }
       *reinterpret_cast<float4*>(o) = r;
     } else {
 #pragma unroll
       for (int j = 0; j < 4; j++)
-        if (n + j < P.N) o[j] = (EPI == 1) ? ld_fresh(o + j) + e[j] : e[j];
+        if (n + j < P.N) o[j] = (EPI == 1 || EPI == 4) ? ld_fresh(o + j) + e[j] : e[j];
     }
   }
 }
@@ -328,6 +458,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const int m = ta * TC_BM + row;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
       constexpr int CW = (BN >= 32) ? 32 : 16;                  // columns per tcgen05.ld
+      EpiRow R = epi_row_begin<EPI>(P.X, m, slot >= 0 ? 0 : P.M);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += CW) {
         uint32_t r[CW];
@@ -344,9 +475,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           float v[CW];
 #pragma unroll
           for (int j = 0; j < CW; j++) v[j] = __uint_as_float(r[j]);
-          tc_store_chunk<EPI, CW>(P, m, tb * BN + c0, v);
+          tc_store_chunk<EPI, CW>(P, m, tb * BN + c0, v, R);
         }
       }
+      if (slot < 0) epi_row_end<EPI>(P.X, R, tb, m, P.M);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.acc_empty[buf]);
@@ -501,6 +633,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       tc_fence_after();
       const int m = tm * 2 * TC_BM + (int)rank * TC_BM + row;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
+      EpiRow R = epi_row_begin<EPI>(P.X, m, P.M);
 #pragma unroll 1
       for (int c0 = 0; c0 + 32 <= BN; c0 += 32) {
         uint32_t r[32];
@@ -510,7 +643,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; j++) v[j] = __uint_as_float(r[j]);
-          tc_store_chunk<EPI, 32>(P, m, tn * BN + c0, v);
+          tc_store_chunk<EPI, 32>(P, m, tn * BN + c0, v, R);
         }
       }
       if constexpr (BN % 32 != 0) {               // the last 16 columns
@@ -521,9 +654,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           float v[16];
 #pragma unroll
           for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
-          tc_store_chunk<EPI, 16>(P, m, tn * BN + (BN / 32) * 32, v);
+          tc_store_chunk<EPI, 16>(P, m, tn * BN + (BN / 32) * 32, v, R);
         }
       }
+      epi_row_end<EPI>(P.X, R, tn, m, P.M);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty_leader[buf]);
@@ -557,6 +691,7 @@ struct SkParams {
   float* scratch;         // [gridDim.x][2][BN][128] float32 partial tiles (first / last tile of a CTA's stretch)
   int M, N, K, ldo;
   int tiles, n_kb, total_kb;
+  EpiExtra X;
 };
 
 __device__ __forceinline__ int sk_begin(int c, int G, int total) { return (int)((long long)c * total / G); }
@@ -567,28 +702,77 @@ __device__ __forceinline__ int sk_owner(int i, int G, int total) {
   return c;
 }
 
+// Per row of x (a token of the step), in shared memory, for the epilogues of the forms below, whose threads own
+// weight rows and meet every token.
+struct SkTables {
+  float scale[TC_BM];       // factor of a handed-over norm (1 if none)
+  long long cache[TC_BM];   // epilogue 5: epi_cache_row (-1: the row writes nothing into the cache)
+  float ss[4][TC_BM];       // epilogue 4: per epilogue warp, the sum of squares over its 32 weight rows
+};
+template <int EPI, int BN>
+__device__ __forceinline__ void sk_tables_init(const SkParams& P, SkTables& T, int t0, int stride) {
+  for (int t = t0; t < BN; t += stride) {
+    T.scale[t] = (P.X.norm_ss && t < P.M) ? epi_row_scale(P.X, t) : 1.0f;
+    T.cache[t] = (EPI == 5 && t < P.M) ? epi_cache_row(P.X, t) : -1;
+  }
+}
+
 // Final values of weight row n for x rows m0 .. m0+CW-1 (one thread per weight row, lanes are neighbours in n).
+// Epilogue 4 leaves the squares of the new residual values in v (zero where nothing was written), for the caller
+// to add up over the weight rows.
 template <int EPI, int CW>
-__device__ __forceinline__ void sk_store(const SkParams& P, int n, int m0, float (&v)[CW]) {
-  if (EPI == 1) {
+__device__ __forceinline__ void sk_store(const SkParams& P, const SkTables& T, int n, int m0, float (&v)[CW]) {
+  const bool col_ok = n < P.N;
+  const float b = (P.bias && col_ok) ? P.bias[n] : 0.0f;
+#pragma unroll
+  for (int j = 0; j < CW; j++) v[j] = v[j] * T.scale[m0 + j] + b;
+  if constexpr (EPI == 1 || EPI == 4) {
     // all loads of the old values first, so that they are in flight together (the compiler may not move a load
     // above the store of another row: it cannot know that the rows do not overlap)
-    const bool col_ok = n < P.N;
-    const float b = (P.bias && col_ok) ? P.bias[n] : 0.0f;
     float old[CW];
 #pragma unroll
     for (int j = 0; j < CW; j++)
       old[j] = (col_ok && m0 + j < P.M) ? ld_fresh((const float*)P.out + (size_t)(m0 + j) * P.ldo + n) : 0.0f;
 #pragma unroll
-    for (int j = 0; j < CW; j++)
-      if (col_ok && m0 + j < P.M) ((float*)P.out)[(size_t)(m0 + j) * P.ldo + n] = old[j] + (v[j] + b);
-    return;
-  }
+    for (int j = 0; j < CW; j++) {
+      const bool ok = col_ok && m0 + j < P.M;
+      v[j] = ok ? old[j] + v[j] : 0.0f;
+      if (ok) ((float*)P.out)[(size_t)(m0 + j) * P.ldo + n] = v[j];
+    }
+    if (EPI == 4 && P.X.emit_x) {
+      const float gain = col_ok ? __ldg(P.X.emit_gain + n) : 0.0f;
+#pragma unroll
+      for (int j = 0; j < CW; j++) {
+        if (col_ok && m0 + j < P.M) P.X.emit_x[(size_t)(m0 + j) * P.X.emit_ldx + n] = __float2bfloat16_rn(v[j] * gain);
+        v[j] *= v[j];
+      }
+    }
+  } else if constexpr (EPI == 5) {
+    // weight row n is dimension d of head h; its partner in the rotation is the neighbouring row, one lane away
+    const EpiExtra& X = P.X;
+    const int h = n / X.head_dim, d = n - h * X.head_dim;
+    const bool is_q = h < X.n_q, is_k = !is_q && h < X.n_q + X.n_kv;
+    const bool rot = col_ok && (is_q || is_k) && X.rope_cs && (d >> 1) < X.rope_pairs;
+    const int kvh = is_k ? h - X.n_q : h - X.n_q - X.n_kv;
+    bf16* cache = (is_k ? X.k_cache : X.v_cache) + (long long)kvh * X.page_tokens * X.head_dim + d;
+#pragma unroll
+    for (int j = 0; j < CW; j++) {
+      const int m = m0 + j;
+      float val = v[j];
+      const float partner = __shfl_xor_sync(0xffffffffu, val, 1);
+      if (m >= P.M || !col_ok) continue;
+      if (rot) {
+        const float2 f = __ldg(X.rope_cs + (size_t)m * X.rope_pairs + (d >> 1));
+        val = (d & 1) ? partner * f.y + val * f.x : val * f.x - partner * f.y;
+      }
+      if (is_q) ((bf16*)P.out)[(size_t)m * P.ldo + n] = __float2bfloat16_rn(val);
+      else if (T.cache[m] >= 0) cache[T.cache[m]] = __float2bfloat16_rn(val);
+    }
+  } else {
 #pragma unroll
   for (int j = 0; j < CW; j++) {
     const int m = m0 + j;
     float val = v[j];
-    if (P.bias && n < P.N) val += P.bias[n];
     if (EPI == 3) {
       val = __bfloat162float(__float2bfloat16_rn(val));
       const float other = __shfl_xor_sync(0xffffffffu, val, 1);     // gate (even n) <-> up (odd n)
@@ -597,10 +781,26 @@ __device__ __forceinline__ void sk_store(const SkParams& P, int n, int m0, float
     } else if (m < P.M && n < P.N) {
       const size_t idx = (size_t)m * P.ldo + n;
       if (EPI == 0) ((bf16*)P.out)[idx] = __float2bfloat16_rn(val);
-      else if (EPI == 1) ((float*)P.out)[idx] = ld_fresh((const float*)P.out + idx) + val;
       else ((float*)P.out)[idx] = val;
     }
   }
+  }
+}
+
+// Epilogue 4, after sk_store: v holds squares; add them over the warp's 32 weight rows and leave the sums for
+// sk_emit_sums.
+template <int CW>
+__device__ __forceinline__ void sk_emit_squares(SkTables& T, int quarter, int lane, int m0, float (&v)[CW]) {
+#pragma unroll
+  for (int j = 0; j < CW; j++) {
+    const float t = warp_sum(v[j]);
+    if (lane == 0) T.ss[quarter][m0 + j] = t;
+  }
+}
+// Once the four epilogue warps have left their sums of a tile (a barrier among them lies between): the tile's part.
+__device__ __forceinline__ void sk_emit_sums(const SkParams& P, const SkTables& T, int tile, int t) {
+  if (t < P.M && P.X.emit_ss)
+    P.X.emit_ss[(size_t)tile * P.X.emit_ld + t] = ((T.ss[0][t] + T.ss[1][t]) + T.ss[2][t]) + T.ss[3][t];
 }
 
 template <int BN, int STAGES>
@@ -608,6 +808,7 @@ struct SkSmem {
   alignas(1024) bf16 a[STAGES][TC_BM * TC_BK];
   alignas(1024) bf16 b[STAGES][BN * TC_BK];
   uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+  SkTables tab;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -715,6 +916,8 @@ gemm_tc_streamk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     const int row = quarter * 32 + lane;          // weight row within the tile held by this thread
     const int first_tile = kb0 / P.n_kb;
     constexpr int CW = (BN >= 32) ? 32 : 16;
+    sk_tables_init<EPI, BN>(P, S.tab, threadIdx.x - 64, 128);
+    asm volatile("bar.sync 1, 128;" ::: "memory");
     uint32_t seg = 0;
     bool ok = true;
     int g = kb0;
@@ -742,7 +945,8 @@ gemm_tc_streamk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
           float v[CW];
 #pragma unroll
           for (int j = 0; j < CW; j++) v[j] = __uint_as_float(r[j]);
-          sk_store<EPI, CW>(P, n, c0, v);
+          sk_store<EPI, CW>(P, S.tab, n, c0, v);
+          if (EPI == 4) sk_emit_squares<CW>(S.tab, quarter, lane, c0, v);
         } else {
 #pragma unroll
           for (int j = 0; j < CW; j++) part[(size_t)(c0 + j) * TC_BM + row] = __uint_as_float(r[j]);
@@ -751,6 +955,11 @@ gemm_tc_streamk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&S.acc_empty[buf]);
+      if (EPI == 4 && whole) {                    // (uniform over the four warps: they walk the same tiles)
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        sk_emit_sums(P, S.tab, tile, threadIdx.x - 64);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
       g = seg_end;
       seg++;
     }
@@ -863,6 +1072,7 @@ gemm_tc_clusterk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5): this CTA's sums
     pdl_wait();
+    sk_tables_init<EPI, BN>(P, S.tab, threadIdx.x - 64, 128);      // (rank 0 uses them, after the cluster's barriers)
     if (kb1 > kb0) {
       if (!__all_sync(0xffffffffu, mbar_wait(&S.acc_full[0], 0, abort_flag))) {
         if (lane == 0) { atomicCAS(P.status, 0, 124); S.abort_flag = 1; }
@@ -909,10 +1119,12 @@ gemm_tc_clusterk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
       float o[CW];
 #pragma unroll
       for (int j = 0; j < CW; j++) o[j] = v[c0 + j];
-      sk_store<EPI, CW>(P, n, c0, o);
+      sk_store<EPI, CW>(P, S.tab, n, c0, o);
+      if (EPI == 4) sk_emit_squares<CW>(S.tab, warp & 3, lane, c0, o);
     }
   }
   __syncthreads();
+  if (EPI == 4 && rank == 0 && warp >= 2) sk_emit_sums(P, S.tab, tile, threadIdx.x - 64);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
@@ -1045,6 +1257,8 @@ static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, TcParams P, 
     case 1: TC2_LAUNCH(1) break;
     case 2: TC2_LAUNCH(2) break;
     case 3: TC2_LAUNCH(3) break;
+    case 4: TC2_LAUNCH(4) break;
+    case 5: TC2_LAUNCH(5) break;
     default: return STRATUM_ERR_SHAPE;
   }
 #undef TC2_LAUNCH
@@ -1090,7 +1304,8 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TcParams P, i
   int grid = n_tiles < sms ? n_tiles : sms;
   const int left = n_tiles % sms;
   P.split = 0; P.scratch = scratch;
-  if (scratch && split_pays(n_tiles, n_kb, sms, BN)) {
+  // (the second kernel of the split knows the four basic epilogues only)
+  if (scratch && epilogue < 4 && !P.X.norm_ss && split_pays(n_tiles, n_kb, sms, BN)) {
     P.split = 1;
     grid = sms;
   }
@@ -1117,6 +1332,8 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TcParams P, i
     case 1: TC_LAUNCH(1) break;
     case 2: TC_LAUNCH(2) break;
     case 3: TC_LAUNCH(3) break;
+    case 4: TC_LAUNCH(4) break;
+    case 5: TC_LAUNCH(5) break;
     default: return STRATUM_ERR_SHAPE;
   }
 #undef TC_LAUNCH
@@ -1149,10 +1366,16 @@ gemm_tc_fixup_kernel(const SkParams P, int G) {
   const int n = tile * TC_BM + col;
   const size_t idx = (size_t)m * P.ldo + n;
   // adding into float32: the old values are asked for together with the partial sums, not after them
-  const bool add_wide = EPI == 1 && n + 3 < P.N && ((reinterpret_cast<uintptr_t>((float*)P.out + idx) & 15) == 0);
+  constexpr bool ADD = EPI == 1 || EPI == 4;
+  const bool add_wide = ADD && n + 3 < P.N && ((reinterpret_cast<uintptr_t>((float*)P.out + idx) & 15) == 0);
   pdl_wait();
   float4 old = make_float4(0.f, 0.f, 0.f, 0.f);
   if (add_wide) old = __ldcg(reinterpret_cast<const float4*>((const float*)P.out + idx));
+  float scale = 1.0f;
+  if (P.X.norm_ss) {                               // one lane adds the row's parts, in their order
+    if ((threadIdx.x & 31) == 0) scale = epi_row_scale(P.X, m);
+    scale = __shfl_sync(0xffffffffu, scale, 0);
+  }
   float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int c0 = first_c; c0 <= last_c; c0 += 8) {
     float4 a[8];
@@ -1171,9 +1394,45 @@ gemm_tc_fixup_kernel(const SkParams P, int G) {
       if (c0 + j <= last_c) { v.x += a[j].x; v.y += a[j].y; v.z += a[j].z; v.w += a[j].w; }
     }
   }
+  v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
   if (add_wide) {
     if (P.bias) { v.x += P.bias[n]; v.y += P.bias[n + 1]; v.z += P.bias[n + 2]; v.w += P.bias[n + 3]; }
-    *reinterpret_cast<float4*>((float*)P.out + idx) = make_float4(old.x + v.x, old.y + v.y, old.z + v.z, old.w + v.w);
+    const float4 r = make_float4(old.x + v.x, old.y + v.y, old.z + v.z, old.w + v.w);
+    *reinterpret_cast<float4*>((float*)P.out + idx) = r;
+    if (EPI == 4 && P.X.emit_x) {
+      const float4 g = __ldg(reinterpret_cast<const float4*>(P.X.emit_gain + n));
+      __nv_bfloat162 lo = __floats2bfloat162_rn(r.x * g.x, r.y * g.y), hi = __floats2bfloat162_rn(r.z * g.z, r.w * g.w);
+      uint2 u; u.x = *reinterpret_cast<uint32_t*>(&lo); u.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(P.X.emit_x + (size_t)m * P.X.emit_ldx + n) = u;
+      const float ss = warp_sum(fmaf(r.x, r.x, fmaf(r.y, r.y, fmaf(r.z, r.z, r.w * r.w))));
+      if ((threadIdx.x & 31) == 0 && P.X.emit_ss) P.X.emit_ss[(size_t)tile * P.X.emit_ld + m] = ss;
+    }
+    return;
+  }
+  if (EPI == 5) {
+    // four neighbouring dimensions of one head: two rotated pairs
+    if (n + 3 >= P.N) return;
+    const EpiExtra& X = P.X;
+    if (P.bias) { v.x += P.bias[n]; v.y += P.bias[n + 1]; v.z += P.bias[n + 2]; v.w += P.bias[n + 3]; }
+    const int h = n / X.head_dim, d = n - h * X.head_dim;
+    const bool is_q = h < X.n_q, is_k = !is_q && h < X.n_q + X.n_kv;
+    if ((is_q || is_k) && X.rope_cs) {
+      const float2* cs = X.rope_cs + (size_t)m * X.rope_pairs + (d >> 1);
+      if ((d >> 1) < X.rope_pairs) { const float2 f = __ldg(cs); const float x0 = v.x, x1 = v.y; v.x = x0 * f.x - x1 * f.y; v.y = x0 * f.y + x1 * f.x; }
+      if ((d >> 1) + 1 < X.rope_pairs) { const float2 f = __ldg(cs + 1); const float x0 = v.z, x1 = v.w; v.z = x0 * f.x - x1 * f.y; v.w = x0 * f.y + x1 * f.x; }
+    }
+    bf16* o;
+    if (is_q) {
+      o = (bf16*)P.out + (size_t)m * P.ldo + n;
+    } else {
+      const long long row = epi_cache_row(X, m);
+      if (row < 0) return;
+      const int kvh = is_k ? h - X.n_q : h - X.n_q - X.n_kv;
+      o = (is_k ? X.k_cache : X.v_cache) + row + (long long)kvh * X.page_tokens * X.head_dim + d;
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u; u.x = *reinterpret_cast<uint32_t*>(&lo); u.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(o) = u;
     return;
   }
   fixup_store<EPI>(P, m, n, v);
@@ -1291,6 +1550,8 @@ static int launch_streamk(const CUtensorMap& mw, const CUtensorMap& mx, const Sk
     case 1: SK_LAUNCH(1)
     case 2: SK_LAUNCH(2)
     case 3: SK_LAUNCH(3)
+    case 4: SK_LAUNCH(4)
+    case 5: SK_LAUNCH(5)
     default: return STRATUM_ERR_SHAPE;
   }
 #undef SK_LAUNCH
@@ -1301,23 +1562,47 @@ STRATUM_EXPORT int stratum_gemm_tc_last_launches(void) { return g_last_launches;
 // Scratch for partial tiles (two 128 x 256 float32 tiles per SM cover both forms).
 STRATUM_EXPORT long long stratum_gemm_tc_scratch_floats(void) { return (long long)sm_count() * 2 * 256 * TC_BM; }
 
+static int g_last_parts = 0;          // epilogue 4: how many parts of sums of squares the last call wrote per row
+STRATUM_EXPORT int stratum_gemm_tc_last_parts(void) { return g_last_parts; }
+
 // x: bf16 [M][ldx], w: bf16 [N][K], bias float32 [N] or null, out [M][ldo] (SwiGLU: [M][N/2]).
 // scratch: partial tiles of tiles shared between CTAs (see stratum_gemm_tc_scratch_floats).  Without it more than
 // 128 rows of x still work (no tile is shared then); up to 128 rows need it.
 // status: one int in device memory, 0 before the call; non-zero afterwards means a wait inside the kernel ran out.
+// extra: null, or what EpiExtra describes (epilogues 4 and 5 need it).
 // Needs K % 8 == 0, ldx % 8 == 0, 16-byte aligned x and w (a TMA copy starts on a 16-byte boundary and its
 // row pitch is a multiple of 16 bytes; the k coordinate of every copy here is a multiple of 64).
-STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bias, void* out, int epilogue, int M,
-                                   int N, int K, int ldx, int ldo, int* status, float* scratch,
-                                   cudaStream_t stream) {
+STRATUM_EXPORT int stratum_gemm_tc_ex(const void* x, const void* w, const float* bias, void* out, int epilogue, int M,
+                                      int N, int K, int ldx, int ldo, int* status, float* scratch,
+                                      const EpiExtra* extra, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldx < K) return STRATUM_ERR_SHAPE;
   if (((uintptr_t)x | (uintptr_t)w) & 15) return STRATUM_ERR_ALIGN;
   if (epilogue == 3 && (N % 2 != 0)) return STRATUM_ERR_SHAPE;
   if (!status) return STRATUM_ERR_SHAPE;
+  EpiExtra X = {};
+  if (extra) X = *extra;
+  if (epilogue == 4) {
+    // the sums of squares are kept per tile of columns; vector stores everywhere
+    if (!X.emit_x || !X.emit_gain || !X.emit_ss) return STRATUM_ERR_SHAPE;
+    if (N % 128 != 0 || ldo % 4 != 0 || X.emit_ldx % 8 != 0 || X.emit_ld < M) return STRATUM_ERR_SHAPE;
+    if (((uintptr_t)out | (uintptr_t)X.emit_x | (uintptr_t)X.emit_gain) & 15) return STRATUM_ERR_ALIGN;
+  } else {
+    X.emit_x = nullptr; X.emit_gain = nullptr; X.emit_ss = nullptr;
+  }
+  if (epilogue == 5) {
+    if (X.head_dim < 32 || X.head_dim % 32 != 0 || X.n_q < 1 || X.n_kv < 1 || N != (X.n_q + 2 * X.n_kv) * X.head_dim)
+      return STRATUM_ERR_SHAPE;
+    if (X.rope_cs && (X.rope_pairs < 1 || 2 * X.rope_pairs > X.head_dim)) return STRATUM_ERR_SHAPE;
+    if (!X.token_pos || !X.token_seq || X.page_tokens < 1 || ldo % 8 != 0) return STRATUM_ERR_SHAPE;
+    if (X.write_cache && (!X.k_cache || !X.v_cache || !X.block_table)) return STRATUM_ERR_SHAPE;
+    if (((uintptr_t)out | (uintptr_t)X.k_cache | (uintptr_t)X.v_cache) & 15) return STRATUM_ERR_ALIGN;
+  }
+  if (X.norm_ss && (X.norm_parts < 1 || X.norm_ld < M || !(X.norm_size > 0.f))) return STRATUM_ERR_SHAPE;
   TcParams P;
   P.bias = bias; P.out = out; P.status = status; P.M = M; P.N = N; P.K = K; P.ldo = ldo;
-  P.split = 0; P.scratch = nullptr;
+  P.split = 0; P.scratch = nullptr; P.X = X;
+  g_last_parts = 0;
   CUtensorMap ma, mb;
   // up to 64 rows always; 65 to 128 rows unless the tile form fills most of the SMs with one wave (measured on the
   // Llama-8B shapes: 16.7 against 22 us for N = K = 4096, 70 against 53 us for N = 28672)
@@ -1335,10 +1620,12 @@ STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bi
         rows2 * 100 <= rows1 * 115) {               // (not where half of a pair would work on rows beyond M)
       const int pairs = resident_pairs();
       if (pairs >= 1) {
-        const int bn = pair_tile_width(M, N, pairs);
+        // (epilogue 5 walks whole heads: tiles of 256 columns begin where a head begins)
+        const int bn = epilogue == 5 ? 256 : pair_tile_width(M, N, pairs);
         const int tiles = ((M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((N + bn - 1) / bn);
         if ((st = make_map(&ma, x, M, K, ldx, TC_BM)) != 0) return st;
         if ((st = make_map(&mb, w, N, K, K, bn / 2)) != 0) return st;
+        g_last_parts = (N + bn - 1) / bn;
         if (bn == 256) return launch_tc2<256>(ma, mb, P, epilogue, tiles, stream);
         if (bn == 240) return launch_tc2<240>(ma, mb, P, epilogue, tiles, stream);
         return launch_tc2<224>(ma, mb, P, epilogue, tiles, stream);
@@ -1347,6 +1634,7 @@ STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bi
     if ((st = make_map(&ma, x, M, K, ldx, TC_BM)) != 0) return st;
     if ((st = make_map(&mb, w, N, K, K, wide ? 256 : 128)) != 0) return st;
     const int tiles_m = (M + TC_BM - 1) / TC_BM, n_kb = (K + TC_BK - 1) / TC_BK;
+    g_last_parts = wide ? (N + 255) / 256 : (N + 127) / 128;
     if (wide) return launch_tc<256, 4>(ma, mb, P, epilogue, tiles_m * ((N + 255) / 256), n_kb, tiles_m, scratch, stream);
     return launch_tc<128, 6>(ma, mb, P, epilogue, tiles_m * ((N + 127) / 128), n_kb, tiles_m, scratch, stream);
   }
@@ -1357,14 +1645,22 @@ STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bi
   if ((st = make_map(&mb, x, M, K, ldx, bn)) != 0) return st;
   SkParams Q;
   Q.bias = bias; Q.out = out; Q.status = status; Q.scratch = scratch;
-  Q.M = M; Q.N = N; Q.K = K; Q.ldo = ldo;
+  Q.M = M; Q.N = N; Q.K = K; Q.ldo = ldo; Q.X = X;
   Q.tiles = (N + TC_BM - 1) / TC_BM;
   Q.n_kb = (K + TC_BK - 1) / TC_BK;
   Q.total_kb = Q.tiles * Q.n_kb;
+  g_last_parts = Q.tiles;
   // rings of about 180 KB: what is in flight per SM decides the rate at which weights stream in (rings half
   // as deep, two CTAs per SM, ran a third slower)
   if (bn == 16) return launch_streamk<16, SK_RING_16>(ma, mb, Q, epilogue, stream);
   if (bn == 32) return launch_streamk<32, SK_RING_32>(ma, mb, Q, epilogue, stream);
   if (bn == 64) return launch_streamk<64, SK_RING_64>(ma, mb, Q, epilogue, stream);
   return launch_streamk<128, SK_RING_128>(ma, mb, Q, epilogue, stream);
+}
+
+STRATUM_EXPORT int stratum_gemm_tc(const void* x, const void* w, const float* bias, void* out, int epilogue, int M,
+                                   int N, int K, int ldx, int ldo, int* status, float* scratch,
+                                   cudaStream_t stream) {
+  if (epilogue < 0 || epilogue > 3) return STRATUM_ERR_SHAPE;
+  return stratum_gemm_tc_ex(x, w, bias, out, epilogue, M, N, K, ldx, ldo, status, scratch, nullptr, stream);
 }

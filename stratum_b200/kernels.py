@@ -213,6 +213,18 @@ def rope_store(qkv: torch.Tensor, token_pos: torch.Tensor, token_seq: torch.Tens
              int(write_cache), _stream()), "rope_store")
 
 
+def rope_table(token_pos: torch.Tensor, inv_freq: torch.Tensor, mscale: float, out: torch.Tensor) -> None:
+    """out[t][k] = mscale * (cos, sin)((float)pos[t] * inv_freq[k]): float32 [tokens, pairs, 2], once per step, for
+    the matrix-product epilogues that rotate queries and keys."""
+    _need(token_pos, "token_pos", torch.int32); _need(inv_freq, "inv_freq", torch.float32)
+    _need(out, "out", torch.float32)
+    if tuple(out.shape) != (token_pos.numel(), inv_freq.numel(), 2):
+        raise KernelError("rope_table: out must be [tokens, pairs, 2]")
+    f = _fn("elementwise", "stratum_rope_table", [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_ptr(token_pos), _ptr(inv_freq), c_float(mscale), _ptr(out), token_pos.numel(), inv_freq.numel(),
+             _stream()), "rope_table")
+
+
 def fill_normal(out: torch.Tensor, seed: int, std: float) -> None:
     """Fill with std * N(0,1) from a counter-based generator keyed by (seed, element index)."""
     _need(out, "out")
@@ -223,6 +235,7 @@ def fill_normal(out: torch.Tensor, seed: int, std: float) -> None:
 
 # ------------------------------------------------------------------ linear (any shape, CUDA cores)
 EPI_STORE, EPI_ADD_F32, EPI_STORE_F32, EPI_SWIGLU = 0, 1, 2, 3
+EPI_ADD_F32_EMIT, EPI_QKV_ROPE = 4, 5          # gemm_tc only: see GemmExtra
 
 
 def linear_simple(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
@@ -326,19 +339,92 @@ def _gemm_tc_scratch(device):
     return _gemm_scratch
 
 
+class _EpiExtra(ctypes.Structure):
+    """Mirror of struct EpiExtra in csrc/gemm_tc.cu (pointers first, then 4-byte fields)."""
+    _fields_ = [("norm_ss", c_void_p), ("emit_x", c_void_p), ("emit_gain", c_void_p), ("emit_ss", c_void_p),
+                ("rope_cs", c_void_p), ("token_pos", c_void_p), ("token_seq", c_void_p), ("block_table", c_void_p),
+                ("k_cache", c_void_p), ("v_cache", c_void_p),
+                ("norm_parts", c_int), ("norm_ld", c_int), ("norm_size", c_float), ("norm_eps", c_float),
+                ("emit_ldx", c_int), ("emit_ld", c_int),
+                ("rope_pairs", c_int), ("bt_stride", c_int), ("n_q", c_int), ("n_kv", c_int), ("head_dim", c_int),
+                ("page_tokens", c_int), ("write_cache", c_int), ("reserved", c_int)]
+
+
+class GemmExtra:
+    """What a gemm_tc call does beyond its basic epilogue (all optional):
+
+    scaled rows   norm_ss float32 [parts, rows] partial sums of squares of the rows a norm handed over as
+                  r * gain: the product's rows are multiplied by 1 / sqrt(sum / norm_size + norm_eps);
+    EPI_ADD_F32_EMIT   emit_x bfloat16 [rows, N] receives bf16(new residual * emit_gain), emit_ss float32
+                  [parts, rows] the sums of squares of the new residual values per tile of columns (how many
+                  parts were written: `last_parts()` after the call);
+    EPI_QKV_ROPE  the columns are query, key and value heads (pairs of rotated dimensions neighbours): queries
+                  are rotated and stored to `out`, keys rotated and written, values written, into the paged cache.
+    """
+
+    def __init__(self):
+        self.c = _EpiExtra()
+        self.keep = []                      # tensors whose memory the struct points into
+
+    def scaled_rows(self, norm_ss: torch.Tensor, parts: int, size: int, eps: float) -> "GemmExtra":
+        _need(norm_ss, "norm_ss", torch.float32)
+        if norm_ss.dim() != 2 or norm_ss.shape[0] < parts:
+            raise KernelError("gemm_tc: norm_ss must be [parts or more, rows]")
+        self.c.norm_ss, self.c.norm_parts, self.c.norm_ld = norm_ss.data_ptr(), parts, norm_ss.stride(0)
+        self.c.norm_size, self.c.norm_eps = float(size), float(eps)
+        self.keep.append(norm_ss)
+        return self
+
+    def emit(self, emit_x: torch.Tensor, gain: torch.Tensor, emit_ss: torch.Tensor) -> "GemmExtra":
+        _need(emit_x, "emit_x", torch.bfloat16); _need(gain, "gain", torch.float32)
+        _need(emit_ss, "emit_ss", torch.float32)
+        self.c.emit_x, self.c.emit_gain, self.c.emit_ss = emit_x.data_ptr(), gain.data_ptr(), emit_ss.data_ptr()
+        self.c.emit_ldx, self.c.emit_ld = emit_x.stride(0), emit_ss.stride(0)
+        self.keep += [emit_x, gain, emit_ss]
+        return self
+
+    def qkv_rope(self, rope_cs: Optional[torch.Tensor], token_pos: torch.Tensor, token_seq: torch.Tensor,
+                 block_table: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                 v_cache: Optional[torch.Tensor], n_q: int, n_kv: int, head_dim: int, page_tokens: int,
+                 write_cache: bool) -> "GemmExtra":
+        _need(token_pos, "token_pos", torch.int32); _need(token_seq, "token_seq", torch.int32)
+        if rope_cs is not None:
+            _need(rope_cs, "rope_cs", torch.float32)
+            if rope_cs.dim() != 3 or rope_cs.shape[0] != token_pos.numel() or rope_cs.shape[2] != 2:
+                raise KernelError("gemm_tc: rope_cs must be [rows, pairs, 2]")
+            self.c.rope_cs, self.c.rope_pairs = rope_cs.data_ptr(), rope_cs.shape[1]
+        if write_cache:
+            _need(k_cache, "k_cache", torch.bfloat16); _need(v_cache, "v_cache", torch.bfloat16)
+            _need(block_table, "block_table", torch.int32, contiguous=False)
+            self.c.k_cache, self.c.v_cache = k_cache.data_ptr(), v_cache.data_ptr()
+            self.c.block_table, self.c.bt_stride = block_table.data_ptr(), block_table.stride(0)
+        self.c.token_pos, self.c.token_seq = token_pos.data_ptr(), token_seq.data_ptr()
+        self.c.n_q, self.c.n_kv, self.c.head_dim, self.c.page_tokens = n_q, n_kv, head_dim, page_tokens
+        self.c.write_cache = int(bool(write_cache))
+        self.keep += [rope_cs, token_pos, token_seq, block_table, k_cache, v_cache]
+        return self
+
+
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-            epilogue: int) -> None:
-    """bfloat16 matrix product on the 5th-generation tensor cores (TMA + tcgen05/TMEM); see EPI_*.  The form
-    (k shared inside clusters, stream-K, tiles, tiles on pairs of CTAs) is chosen from the shapes in gemm_tc.cu."""
-    M, N, Kd = _linear_shapes(x, w, bias, out, epilogue, "gemm_tc")
+            epilogue: int, extra: Optional[GemmExtra] = None) -> int:
+    """bfloat16 matrix product on the 5th-generation tensor cores (TMA + tcgen05/TMEM); see EPI_* and GemmExtra.
+    The form (k shared inside clusters, stream-K, tiles, tiles on pairs of CTAs) is chosen from the shapes in
+    gemm_tc.cu.  Returns the number of parts written per row with EPI_ADD_F32_EMIT (else 0)."""
+    basic = {EPI_ADD_F32_EMIT: EPI_ADD_F32, EPI_QKV_ROPE: EPI_STORE}.get(epilogue, epilogue)
+    M, N, Kd = _linear_shapes(x, w, bias, out, basic, "gemm_tc")
     _need(x, "x", torch.bfloat16, contiguous=False)
+    if epilogue in (EPI_ADD_F32_EMIT, EPI_QKV_ROPE) and extra is None:
+        raise KernelError("gemm_tc: this epilogue needs a GemmExtra")
     part = _gemm_tc_scratch(x.device)
-    f = _fn("gemm_tc", "stratum_gemm_tc",
+    lib = build.load("gemm_tc")
+    f = _fn("gemm_tc", "stratum_gemm_tc_ex",
             [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-             c_void_p])
+             c_void_p, c_void_p])
     _check(f(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), epilogue, M, N, Kd, x.stride(0), out.stride(0),
-             _ptr(status_word()), _ptr(part), _stream()), "gemm_tc")
-    count_launches(build.load("gemm_tc").stratum_gemm_tc_last_launches() - 1)      # a second pass, if there was one
+             _ptr(status_word()), _ptr(part), None if extra is None else ctypes.addressof(extra.c), _stream()),
+           "gemm_tc")
+    count_launches(lib.stratum_gemm_tc_last_launches() - 1)      # a second pass, if there was one
+    return int(lib.stratum_gemm_tc_last_parts()) if epilogue == EPI_ADD_F32_EMIT else 0
 
 
 # ------------------------------------------------------------------ attention (any sizes, CUDA cores)
