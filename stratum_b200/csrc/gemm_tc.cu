@@ -56,8 +56,16 @@ struct EpiExtra {
 };
 
 __device__ __forceinline__ float epi_row_scale(const EpiExtra& X, int m) {
+  // sixteen loads in flight at a time (one after the other they would cost a trip to L2 each), added in order
   float t = 0.f;
-  for (int p = 0; p < X.norm_parts; p++) t += __ldcg(X.norm_ss + (size_t)p * X.norm_ld + m);
+  for (int p0 = 0; p0 < X.norm_parts; p0 += 16) {
+    float a[16];
+#pragma unroll
+    for (int u = 0; u < 16; u++)
+      a[u] = (p0 + u < X.norm_parts) ? __ldcg(X.norm_ss + (size_t)(p0 + u) * X.norm_ld + m) : 0.f;
+#pragma unroll
+    for (int u = 0; u < 16; u++) t += a[u];
+  }
   return 1.0f / sqrtf(t / X.norm_size + X.norm_eps);
 }
 
@@ -136,7 +144,7 @@ __device__ __forceinline__ void tc_store_chunk(const TcParams& P, int m, int col
 #pragma unroll
       for (int j = 0; j < CW; j += 2) {
         if ((d0 + j) >> 1 < X.rope_pairs) {
-          const float2 f = __ldg(cs + (j >> 1));
+          const float2 f = __ldcg(cs + (j >> 1));
           const float x0 = v[j], x1 = v[j + 1];
           v[j] = x0 * f.x - x1 * f.y;
           v[j + 1] = x0 * f.y + x1 * f.x;
@@ -762,7 +770,7 @@ __device__ __forceinline__ void sk_store(const SkParams& P, const SkTables& T, i
       const float partner = __shfl_xor_sync(0xffffffffu, val, 1);
       if (m >= P.M || !col_ok) continue;
       if (rot) {
-        const float2 f = __ldg(X.rope_cs + (size_t)m * X.rope_pairs + (d >> 1));
+        const float2 f = __ldcg(X.rope_cs + (size_t)m * X.rope_pairs + (d >> 1));
         val = (d & 1) ? partner * f.y + val * f.x : val * f.x - partner * f.y;
       }
       if (is_q) ((bf16*)P.out)[(size_t)m * P.ldo + n] = __float2bfloat16_rn(val);
@@ -1368,6 +1376,8 @@ gemm_tc_fixup_kernel(const SkParams P, int G) {
   // adding into float32: the old values are asked for together with the partial sums, not after them
   constexpr bool ADD = EPI == 1 || EPI == 4;
   const bool add_wide = ADD && n + 3 < P.N && ((reinterpret_cast<uintptr_t>((float*)P.out + idx) & 15) == 0);
+  // (positions and page tables are the step's description, not an earlier kernel's work: read before the wait)
+  const long long cache_row = (EPI == 5) ? epi_cache_row(P.X, m) : -1;
   pdl_wait();
   float4 old = make_float4(0.f, 0.f, 0.f, 0.f);
   if (add_wide) old = __ldcg(reinterpret_cast<const float4*>((const float*)P.out + idx));
@@ -1418,17 +1428,16 @@ gemm_tc_fixup_kernel(const SkParams P, int G) {
     const bool is_q = h < X.n_q, is_k = !is_q && h < X.n_q + X.n_kv;
     if ((is_q || is_k) && X.rope_cs) {
       const float2* cs = X.rope_cs + (size_t)m * X.rope_pairs + (d >> 1);
-      if ((d >> 1) < X.rope_pairs) { const float2 f = __ldg(cs); const float x0 = v.x, x1 = v.y; v.x = x0 * f.x - x1 * f.y; v.y = x0 * f.y + x1 * f.x; }
-      if ((d >> 1) + 1 < X.rope_pairs) { const float2 f = __ldg(cs + 1); const float x0 = v.z, x1 = v.w; v.z = x0 * f.x - x1 * f.y; v.w = x0 * f.y + x1 * f.x; }
+      if ((d >> 1) < X.rope_pairs) { const float2 f = __ldcg(cs); const float x0 = v.x, x1 = v.y; v.x = x0 * f.x - x1 * f.y; v.y = x0 * f.y + x1 * f.x; }
+      if ((d >> 1) + 1 < X.rope_pairs) { const float2 f = __ldcg(cs + 1); const float x0 = v.z, x1 = v.w; v.z = x0 * f.x - x1 * f.y; v.w = x0 * f.y + x1 * f.x; }
     }
     bf16* o;
     if (is_q) {
       o = (bf16*)P.out + (size_t)m * P.ldo + n;
     } else {
-      const long long row = epi_cache_row(X, m);
-      if (row < 0) return;
+      if (cache_row < 0) return;
       const int kvh = is_k ? h - X.n_q : h - X.n_q - X.n_kv;
-      o = (is_k ? X.k_cache : X.v_cache) + row + (long long)kvh * X.page_tokens * X.head_dim + d;
+      o = (is_k ? X.k_cache : X.v_cache) + cache_row + (long long)kvh * X.page_tokens * X.head_dim + d;
     }
     __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
     uint2 u; u.x = *reinterpret_cast<uint32_t*>(&lo); u.y = *reinterpret_cast<uint32_t*>(&hi);

@@ -123,11 +123,20 @@ class Model:
         x = self.embedding.forward(step.token_ids)
         if self.position is not None:
             self.position.add_to_embedding(x, step)
+        carry = None                  # rows a layer's last product prepared for the next layer's first norm
         for stop, entry in enumerate(self.schedule):
             layer = self.layers[entry.layer]
             owner = stop if entry.cache_of is None else entry.cache_of
             view = cache.layer_view(owner, entry.cache_of is None, step.block_tables)
-            layer.arrangement.forward(layer, x, step, view)
+            if layer.arrangement.carries:
+                hand_to = None
+                if stop + 1 < len(self.schedule):
+                    nxt = self.layers[self.schedule[stop + 1].layer]
+                    hand_to = nxt.arrangement.accepts_carry(nxt) if nxt.arrangement.carries else None
+                carry = layer.arrangement.forward(layer, x, step, view, carry=carry, hand_to=hand_to)
+            else:
+                layer.arrangement.forward(layer, x, step, view)
+                carry = None
         if step.want_rows.numel() == 0:
             return torch.empty((0, self.vocab), dtype=torch.float32, device=x.device)
         xn = self.final_norm.forward(x, rows=step.want_rows)

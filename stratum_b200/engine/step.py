@@ -53,6 +53,17 @@ class StepBatch:
     all_single: bool = True           # every sequence brings exactly one token
     host: Optional[dict] = None       # the same numbers on the host, for parts that plan launches
     _qblocks: Dict[int, tuple] = field(default_factory=dict)
+    _rotation: Dict[object, torch.Tensor] = field(default_factory=dict)
+
+    def rotation_table(self, rot) -> torch.Tensor:
+        """(cos, sin) of every token's angles under a RotaryTable, float32 [tokens, pairs, 2] on the device: made
+        by one small kernel the first time a layer of the step asks, and shared by all layers that rotate alike."""
+        t = self._rotation.get(rot.key)
+        if t is None:
+            t = torch.empty((self.n_tokens, rot.inv_freq.numel(), 2), dtype=torch.float32, device=self.token_pos.device)
+            K.rope_table(self.token_pos, rot.inv_freq, rot.magnitude, t)
+            self._rotation[rot.key] = t
+        return t
 
     def query_blocks(self, tokens_per_block: int):
         """Cut every sequence's new tokens into runs of at most `tokens_per_block`: int32 tensors

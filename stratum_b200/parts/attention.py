@@ -19,6 +19,7 @@ converter does the same to its Llama files, which is why its handler rotates nei
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, Mapping, Optional
 
 import torch
@@ -26,8 +27,8 @@ import torch
 from .. import kernels as K
 from ..cache.pages import PAGE_TOKENS
 from ..cache.store import KVSpec, LayerCache
-from .base import Mixer
-from .linear import ADD_TO_F32, STORE, Linear
+from .base import Mixer, NormedRows
+from .linear import ADD_TO_F32, QKV_ROPE, STORE, Linear
 from .registry import find_part, register_part
 from .spec import PartSpec, TensorSpec
 
@@ -37,6 +38,8 @@ class GQAAttention(Mixer):
     """params: hidden, n_heads, n_kv_heads, head_dim, bias, window (0 = all keys), scale (None =
     1/sqrt(head_dim)), position (PartSpec of a position encoding, or None), q_norm / k_norm (PartSpec of a
     norm of size head_dim applied to every query / key head between projection and rotation, or None), prefix."""
+    takes_normed_rows = True
+    hands_on = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -125,18 +128,39 @@ class GQAAttention(Mixer):
         return KVSpec(self.n_kv_heads, self.head_dim, self.window,
                       f"pairs_adjacent_{self.position.pair_layout()[0]}" if reordered else "as_projected")
 
-    def forward(self, xn: torch.Tensor, residual: torch.Tensor, step, cache: LayerCache) -> None:
-        qkv = self.qkv(xn, mode=STORE)
-        if self.q_norm is not None:
-            self.q_norm.forward_heads(qkv, 0, self.n_heads, self.head_dim)
-        if self.k_norm is not None:
-            self.k_norm.forward_heads(qkv, self.n_heads * self.head_dim, self.n_kv_heads, self.head_dim)
+    def _fused_projection(self, xn, step) -> bool:
+        """Whether rotation and cache write ride on the projection's epilogue: the tensor-core product takes the
+        call anyway, a chunk of its epilogue lies inside one head, and nothing stands between projection and
+        rotation.  Used for decode steps, where it takes one launch off every layer at the same step time; for
+        prompts the epilogue's trips to the rotation table cost more than the separate kernel's pass over q and k
+        (measured on the Llama-8B layer sizes: 107 us against 80 + 16 us at 2,048 tokens).
+        STRATUM_FUSE_ROPE=0 turns it off, =2 turns it on for prompts too (measurements)."""
+        from . import gemm_dispatch
+        mode = os.environ.get("STRATUM_FUSE_ROPE", "1")
+        if mode == "0" or (mode != "2" and not step.all_single):
+            return False
+        x = xn.x if isinstance(xn, NormedRows) else xn
+        return (self.head_dim % 32 == 0 and self.q_norm is None and self.k_norm is None
+                and gemm_dispatch.takes_tensor_cores(x, self.qkv.weight, extras=isinstance(xn, NormedRows)))
+
+    def forward(self, xn, residual: torch.Tensor, step, cache: LayerCache, emit=None) -> None:
         rot = self.position.rotary() if self.position is not None else None
-        K.rope_store(qkv, step.token_pos, step.token_seq, cache.block_table,
-                     None if rot is None else rot.inv_freq, rot is not None,       # pairs are neighbours: see bind
-                     1.0 if rot is None else rot.magnitude, cache.k, cache.v,
-                     self.n_heads, self.n_kv_heads, self.head_dim, PAGE_TOKENS, cache.writes)
-        out = self.runtime.empty(xn.shape[0], self.n_heads * self.head_dim)
+        if self._fused_projection(xn, step):
+            extra = K.GemmExtra().qkv_rope(None if rot is None else step.rotation_table(rot), step.token_pos,
+                                           step.token_seq, cache.block_table, cache.k, cache.v, self.n_heads,
+                                           self.n_kv_heads, self.head_dim, PAGE_TOKENS, cache.writes)
+            qkv = self.qkv(xn, mode=QKV_ROPE, extra=extra)        # only the query columns are written
+        else:
+            qkv = self.qkv(xn, mode=STORE)
+            if self.q_norm is not None:
+                self.q_norm.forward_heads(qkv, 0, self.n_heads, self.head_dim)
+            if self.k_norm is not None:
+                self.k_norm.forward_heads(qkv, self.n_heads * self.head_dim, self.n_kv_heads, self.head_dim)
+            K.rope_store(qkv, step.token_pos, step.token_seq, cache.block_table,
+                         None if rot is None else rot.inv_freq, rot is not None,       # pairs are neighbours: see bind
+                         1.0 if rot is None else rot.magnitude, cache.k, cache.v,
+                         self.n_heads, self.n_kv_heads, self.head_dim, PAGE_TOKENS, cache.writes)
+        out = self.runtime.empty(qkv.shape[0], self.n_heads * self.head_dim)
         from . import attention_dispatch
         attention_dispatch.run(self, qkv, cache, step, out)
-        self.o(out, out=residual, mode=ADD_TO_F32)
+        self.o(out, out=residual, mode=ADD_TO_F32, emit=emit)

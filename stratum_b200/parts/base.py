@@ -47,8 +47,36 @@ class Runtime:
         return t
 
 
+class NormedRows:
+    """Rows that a norm hands to a matrix product without writing them out in full.
+
+    `x` [rows, size] holds r * gain in the compute dtype (r: the residual rows); `ss` float32 [parts or more, rows]
+    holds partial sums of r^2, to be added in the order of the parts.  The product multiplies its result rows by
+    1 / sqrt(sum / size + eps), which is what the norm would have multiplied the operand rows by.  They are made
+    by the matrix product that wrote the residual rows (see Handover), so the norm costs no pass over memory."""
+
+    def __init__(self, x: torch.Tensor, ss: torch.Tensor, parts: int, size: int, eps: float):
+        self.x, self.ss, self.parts, self.size, self.eps = x, ss, parts, size, eps
+
+    @property
+    def shape(self):
+        return self.x.shape
+
+
+class Handover:
+    """A norm's request to the part in front of it: "with the matrix product that adds your result into the
+    residual stream, also leave what I need" (gain, size, eps).  A part that honours it sets `result` to the
+    NormedRows; one that does not leaves it None, and the norm runs as a kernel of its own."""
+
+    def __init__(self, gain: torch.Tensor, size: int, eps: float):
+        self.gain, self.size, self.eps = gain, size, eps
+        self.result: Optional[NormedRows] = None
+
+
 class Part:
     kind = ""
+    takes_normed_rows = False    # forward accepts NormedRows in place of the normed tensor
+    hands_on = False             # forward takes `emit=Handover` and may honour it
 
     def __init__(self, spec: PartSpec, runtime: Optional[Runtime]):
         self.spec = spec
@@ -67,6 +95,10 @@ class Norm(Part):
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """float32 [T, hidden] -> compute dtype [T or len(rows), hidden]."""
         raise NotImplementedError
+
+    def handover(self) -> Optional[Handover]:
+        """A request for the part in front of this norm (see Handover), or None if this norm cannot be handed over."""
+        return None
 
     def forward_heads(self, x: torch.Tensor, first_col: int, n_heads: int, head_dim: int) -> None:
         """Normalise in place, in every row of x (compute dtype), each of the n_heads stretches of head_dim
@@ -92,10 +124,13 @@ class PositionEncoding(Part):
 class RotaryTable:
     """inv_freq: float32 [n_pairs] on the device; pairs (2k,2k+1) if interleaved else (k, k+n_pairs)."""
 
-    def __init__(self, inv_freq: torch.Tensor, interleaved: bool, magnitude: float = 1.0):
+    def __init__(self, inv_freq: torch.Tensor, interleaved: bool, magnitude: float = 1.0, key=None):
         self.inv_freq = inv_freq
         self.interleaved = interleaved
         self.magnitude = magnitude
+        # tables with equal keys rotate alike: a step evaluates the angles of its tokens once per key, not once
+        # per layer (default: a key of this table's own)
+        self.key = key if key is not None else ("table", id(self))
 
 
 class Mixer(Part):
@@ -143,6 +178,13 @@ class Arrangement:
     slots: Mapping[str, str] = {}
     optional: tuple = ()
     cache_owner: Optional[str] = "mixer"
+    carries = False     # forward takes carry= / hand_to= and returns a carry (see accepts_carry)
 
     def forward(self, layer, x: torch.Tensor, step, cache: LayerCache) -> None:
         raise NotImplementedError
+
+    def accepts_carry(self, layer) -> Optional["Norm"]:
+        """The norm this layer begins with, if the layer can begin from NormedRows made for that norm by the
+        layer in front of it (then the model passes them as `carry=` and asks the layer in front with
+        `hand_to=` that norm); None otherwise."""
+        return None

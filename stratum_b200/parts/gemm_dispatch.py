@@ -27,6 +27,12 @@ STORE, ADD_TO_F32, STORE_F32, SWIGLU = K.EPI_STORE, K.EPI_ADD_F32, K.EPI_STORE_F
 # difference (4.00 against 3.99); on the Llama-3.2-1B shapes, where all but gate|up are that small, the step is
 # 8 to 11 % shorter with three to eight rows (1.20 against 1.29 ms at eight) and the same with sixteen.  Both can
 # be set in the environment for measurements.
+# Rows of x from which a product that adds into the residual stream honours the next norm's Handover (writes the
+# bfloat16 rows and the sums of squares the norm needs, so that the norm runs no kernel).  Measured on the Llama-8B
+# layer sizes: at 2,048 rows the two norm kernels of a layer (14 us each) go and the products' epilogues grow by
+# 12 + 5 + 5 us; in decode steps the norm kernels cost nothing to begin with (they run while the next product's
+# weights stream in) and the longer epilogues make a step 4 % slower.  STRATUM_HANDOVER_MIN_ROWS for measurements.
+HANDOVER_MIN_ROWS = int(os.environ.get("STRATUM_HANDOVER_MIN_ROWS", 256))
 SKINNY_MAX_ROWS = int(os.environ.get("STRATUM_SKINNY_MAX_ROWS", 8))
 STREAMK_MIN_WEIGHTS = int(os.environ.get("STRATUM_STREAMK_MIN_WEIGHTS", 20_000_000))
 
@@ -36,8 +42,24 @@ def _aligned(x: torch.Tensor, w: torch.Tensor) -> bool:
     return (k % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def run(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int) -> None:
+def takes_tensor_cores(x: torch.Tensor, w: torch.Tensor, extras: bool) -> bool:
+    """Whether this product goes to gemm_tc.  extras: the call carries work only gemm_tc's epilogues do (rows of
+    a handed-over norm, the query/key/value epilogue), which decides where the weight-streaming kernel would
+    otherwise have been taken."""
+    if x.dtype != torch.bfloat16 or not _aligned(x, w):
+        return False
+    return extras or not (x.shape[0] <= SKINNY_MAX_ROWS and w.numel() < STREAMK_MIN_WEIGHTS)
+
+
+def run(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, mode: int,
+        extra=None) -> None:
     """out (=|+=) epilogue(x @ w.T + bias); see the EPI_* modes in kernels.py."""
+    if extra is not None:
+        if not takes_tensor_cores(x, w, extras=True):
+            raise K.KernelError("this product carries epilogue work that only the tensor-core kernel does, and its "
+                                "shape is not one that kernel takes")
+        K.gemm_tc(x, w, bias, out, mode, extra)
+        return
     if x.dtype == torch.bfloat16 and _aligned(x, w):
         if x.shape[0] <= SKINNY_MAX_ROWS and w.numel() < STREAMK_MIN_WEIGHTS:
             K.gemm_skinny(x, w, bias, out, mode)

@@ -14,7 +14,8 @@ import torch
 from .. import kernels as K
 from .base import Runtime
 
-STORE, ADD_TO_F32, STORE_F32, SWIGLU = K.EPI_STORE, K.EPI_ADD_F32, K.EPI_STORE_F32, K.EPI_SWIGLU
+STORE, ADD_TO_F32, STORE_F32, SWIGLU, QKV_ROPE = (K.EPI_STORE, K.EPI_ADD_F32, K.EPI_STORE_F32, K.EPI_SWIGLU,
+                                                    K.EPI_QKV_ROPE)
 
 
 class Linear:
@@ -26,9 +27,18 @@ class Linear:
         self.bias = bias
         self.out_features, self.in_features = weight.shape
 
-    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None, mode: int = STORE) -> torch.Tensor:
+    def __call__(self, x, out: Optional[torch.Tensor] = None, mode: int = STORE, emit=None, extra=None) -> torch.Tensor:
         """mode STORE: new tensor of x's dtype; ADD_TO_F32: out (float32) += y; STORE_F32: float32 out;
-        SWIGLU: rows of W alternate gate and up, out[m][j] = silu(y[m][2j]) * y[m][2j+1] in x's dtype."""
+        SWIGLU: rows of W alternate gate and up, out[m][j] = silu(y[m][2j]) * y[m][2j+1] in x's dtype;
+        QKV_ROPE: see kernels.GemmExtra (extra carries the cache and the rotation table; out: the query rows).
+        x may be NormedRows (the product then applies the norm's row factors).  emit: a Handover that the
+        ADD_TO_F32 product honours where it can (emit.result is then set)."""
+        from . import gemm_dispatch
+        from .base import NormedRows
+        normed = x if isinstance(x, NormedRows) else None
+        if normed is not None:
+            x = normed.x
+            extra = (extra or K.GemmExtra()).scaled_rows(normed.ss, normed.parts, normed.size, normed.eps)
         M = x.shape[0]
         if out is None:
             if mode == ADD_TO_F32:
@@ -37,6 +47,14 @@ class Linear:
             out = self.runtime.empty(M, width, dtype=torch.float32 if mode == STORE_F32 else x.dtype)
         if M == 0:
             return out
-        from . import gemm_dispatch
-        gemm_dispatch.run(x, self.weight, self.bias, out, mode)
+        if (emit is not None and mode == ADD_TO_F32 and M >= gemm_dispatch.HANDOVER_MIN_ROWS
+                and self.out_features % 128 == 0 and out.stride(0) % 4 == 0
+                and gemm_dispatch.takes_tensor_cores(x, self.weight, extras=False)):
+            xb = self.runtime.empty(M, self.out_features, dtype=torch.bfloat16)
+            ss = self.runtime.empty(self.out_features // 128, M, dtype=torch.float32)
+            extra = (extra or K.GemmExtra()).emit(xb, emit.gain, ss)
+            parts = K.gemm_tc(x, self.weight, self.bias, out, K.EPI_ADD_F32_EMIT, extra)
+            emit.result = NormedRows(xb, ss, parts, emit.size, emit.eps)
+            return out
+        gemm_dispatch.run(x, self.weight, self.bias, out, mode, extra)
         return out

@@ -24,6 +24,8 @@ def interleave_rows(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 @register_part("feed_forward", "swiglu")
 class SwiGLU(FeedForward):
     """params: hidden, intermediate, bias, prefix."""
+    takes_normed_rows = True
+    hands_on = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -50,6 +52,6 @@ class SwiGLU(FeedForward):
         self.gate_up = Linear(self.runtime, w, b)
         self.down = Linear(self.runtime, weights[p + "down_proj.weight"], weights.get(p + "down_proj.bias"))
 
-    def forward(self, xn: torch.Tensor, residual: torch.Tensor, step) -> None:
+    def forward(self, xn, residual: torch.Tensor, step, emit=None) -> None:
         a = self.gate_up(xn, mode=SWIGLU)
-        self.down(a, out=residual, mode=ADD_TO_F32)
+        self.down(a, out=residual, mode=ADD_TO_F32, emit=emit)

@@ -6,7 +6,7 @@ from typing import Dict, Mapping, Optional
 import torch
 
 from .. import kernels as K
-from .base import Norm
+from .base import Handover, Norm
 from .registry import register_part
 from .spec import TensorSpec
 
@@ -32,6 +32,12 @@ class RMSNorm(Norm):
         out = self.runtime.empty(n, self.size)
         K.rmsnorm(x, self.gain, self.eps, out, rows)
         return out
+
+    def handover(self) -> Optional[Handover]:
+        # the matrix products that can honour it are the bfloat16 ones; sums of squares are kept per 128 columns
+        if self.runtime is None or self.runtime.dtype != torch.bfloat16 or self.size % 128 != 0:
+            return None
+        return Handover(self.gain, self.size, self.eps)
 
     def forward_heads(self, x: torch.Tensor, first_col: int, n_heads: int, head_dim: int) -> None:
         if head_dim != self.size:

@@ -92,7 +92,9 @@ class RotaryEmbedding(PositionEncoding):
     def rotary(self) -> RotaryTable:
         if self._table is None:
             inv, mag = inverse_frequencies(self.rope_dim, self.theta, self.scaling)
-            self._table = RotaryTable(torch.from_numpy(inv).to(self.runtime.device), self.interleaved, mag)
+            key = ("rope", self.rope_dim, self.theta, self.interleaved,
+                   tuple(sorted((self.scaling or {}).items())), str(self.runtime.device))
+            self._table = RotaryTable(torch.from_numpy(inv).to(self.runtime.device), self.interleaved, mag, key)
         return self._table
 
 

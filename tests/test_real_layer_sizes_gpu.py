@@ -83,3 +83,54 @@ def test_real_layer_sizes_in_every_cut(model, dtype):
                     live.remove(i)
         engine.cache.check()
     assert engine.cache.tokens_held() == 0
+
+
+@pytest.mark.parametrize("forced", [False, True])
+def test_fused_epilogues_at_model_level(model, forced, monkeypatch):
+    """The matrix products' extra epilogue work inside a model (bfloat16): rotation and cache write on the
+    projection's epilogue, and norms handed over to the product in front of them.  By default the first serves
+    decode steps and the second prompts of 256 rows or more; `forced` turns both on for every step, so that
+    every form of the kernel meets them (prompts of 300 and 40 tokens, batches of 3 and 20 single tokens)."""
+    from stratum_b200 import kernels as K
+    from stratum_b200.engine import Engine, StepEntry, load_model
+    from stratum_b200.parts import gemm_dispatch
+    path, cfg, w = model
+    if forced:
+        monkeypatch.setenv("STRATUM_FUSE_ROPE", "2")
+        monkeypatch.setattr(gemm_dispatch, "HANDOVER_MIN_ROWS", 1)
+        monkeypatch.setattr(gemm_dispatch, "SKINNY_MAX_ROWS", 0)        # every product on the tensor-core kernel
+    m, _ = load_model(path, torch.bfloat16, "cuda")
+    engine = Engine(m, max_tokens=4096)
+    rng = np.random.default_rng(11)
+    V = cfg["vocab_size"]
+    calls = {"rope_store": 0, "rmsnorm": 0}
+    for name in calls:
+        orig = getattr(K, name)
+        monkeypatch.setattr(K, name, (lambda o, n: lambda *a, **k: (calls.__setitem__(n, calls[n] + 1), o(*a, **k))[1])(orig, name))
+    lens = [300, 40, 7] + [int(x) for x in rng.integers(1, 20, size=17)]
+    seqs = [rand_tokens(rng, n + 3, V) for n in lens]
+    refs = [plain_logits(cfg, w, s) for s in seqs[:3]]
+    slots = [engine.acquire() for _ in lens]
+    got = engine.step([StepEntry(slots[0], seqs[0][:300], [0, 150, 299])]).cpu().numpy()      # 300 rows: pairs of CTAs
+    assert_close(got, refs[0][[0, 150, 299]], "bfloat16", "prompt of 300")
+    n_layers = cfg["num_hidden_layers"]
+    if forced:
+        assert calls["rope_store"] == 0                       # rotation rode on the projection
+    assert calls["rmsnorm"] == 2                              # the first layer's first norm, and the final one
+    got = engine.step([StepEntry(s, q[:n], [n - 1]) for s, q, n in zip(slots[1:], seqs[1:], lens[1:])]).cpu().numpy()
+    assert_close(got[:2], np.stack([refs[1][39], refs[2][6]]), "bfloat16", "prompts of 40 and 7 among others")
+    before = dict(calls)
+    for k in range(3):                                         # three tokens each for three sequences, then for all
+        live = range(3) if k < 2 else range(len(lens))
+        ropes = calls["rope_store"]
+        got = engine.step([StepEntry(slots[i], [seqs[i][lens[i] + k]], [0]) for i in live]).cpu().numpy()
+        assert_close(got[:3], np.stack([refs[i][lens[i] + k] for i in range(3)]), "bfloat16", f"decode {k}")
+        if forced or k == 2:          # decode steps whose projection the tensor-core kernel takes (here: 20 rows)
+            assert calls["rope_store"] == ropes                # rotation rode on the projection
+    if forced:
+        assert calls["rmsnorm"] == before["rmsnorm"] + 3 * 2
+    else:
+        assert calls["rmsnorm"] == before["rmsnorm"] + 3 * (2 * n_layers + 1)
+    for s in slots:
+        engine.release(s)
+    engine.cache.check()
