@@ -717,8 +717,12 @@ struct SkTables {
   long long cache[TC_BM];   // epilogue 5: epi_cache_row (-1: the row writes nothing into the cache)
   float ss[4][TC_BM];       // epilogue 4: per epilogue warp, the sum of squares over its 32 weight rows
 };
+// (nothing to do, and no barrier to pay, for a product without such work: the tables are then never read)
+template <int EPI>
+__device__ __forceinline__ bool sk_tables_used(const SkParams& P) { return EPI == 5 || P.X.norm_ss != nullptr; }
 template <int EPI, int BN>
 __device__ __forceinline__ void sk_tables_init(const SkParams& P, SkTables& T, int t0, int stride) {
+  if (!sk_tables_used<EPI>(P)) return;
   for (int t = t0; t < BN; t += stride) {
     T.scale[t] = (P.X.norm_ss && t < P.M) ? epi_row_scale(P.X, t) : 1.0f;
     T.cache[t] = (EPI == 5 && t < P.M) ? epi_cache_row(P.X, t) : -1;
@@ -732,8 +736,13 @@ template <int EPI, int CW>
 __device__ __forceinline__ void sk_store(const SkParams& P, const SkTables& T, int n, int m0, float (&v)[CW]) {
   const bool col_ok = n < P.N;
   const float b = (P.bias && col_ok) ? P.bias[n] : 0.0f;
+  if (P.X.norm_ss) {
 #pragma unroll
-  for (int j = 0; j < CW; j++) v[j] = v[j] * T.scale[m0 + j] + b;
+    for (int j = 0; j < CW; j++) v[j] = v[j] * T.scale[m0 + j] + b;
+  } else {
+#pragma unroll
+    for (int j = 0; j < CW; j++) v[j] += b;
+  }
   if constexpr (EPI == 1 || EPI == 4) {
     // all loads of the old values first, so that they are in flight together (the compiler may not move a load
     // above the store of another row: it cannot know that the rows do not overlap)
@@ -925,7 +934,7 @@ gemm_tc_streamk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     const int first_tile = kb0 / P.n_kb;
     constexpr int CW = (BN >= 32) ? 32 : 16;
     sk_tables_init<EPI, BN>(P, S.tab, threadIdx.x - 64, 128);
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (sk_tables_used<EPI>(P)) asm volatile("bar.sync 1, 128;" ::: "memory");
     uint32_t seg = 0;
     bool ok = true;
     int g = kb0;
