@@ -717,12 +717,10 @@ struct SkTables {
   long long cache[TC_BM];   // epilogue 5: epi_cache_row (-1: the row writes nothing into the cache)
   float ss[4][TC_BM];       // epilogue 4: per epilogue warp, the sum of squares over its 32 weight rows
 };
-// (nothing to do, and no barrier to pay, for a product without such work: the tables are then never read)
-template <int EPI>
-__device__ __forceinline__ bool sk_tables_used(const SkParams& P) { return EPI == 5 || P.X.norm_ss != nullptr; }
+// (The kernels of these forms are compiled twice, XT = false for products without rows of a handed-over norm and
+// without epilogue 5: those neither fill nor read the tables, and pay neither the barrier nor the multiply.)
 template <int EPI, int BN>
 __device__ __forceinline__ void sk_tables_init(const SkParams& P, SkTables& T, int t0, int stride) {
-  if (!sk_tables_used<EPI>(P)) return;
   for (int t = t0; t < BN; t += stride) {
     T.scale[t] = (P.X.norm_ss && t < P.M) ? epi_row_scale(P.X, t) : 1.0f;
     T.cache[t] = (EPI == 5 && t < P.M) ? epi_cache_row(P.X, t) : -1;
@@ -732,11 +730,11 @@ __device__ __forceinline__ void sk_tables_init(const SkParams& P, SkTables& T, i
 // Final values of weight row n for x rows m0 .. m0+CW-1 (one thread per weight row, lanes are neighbours in n).
 // Epilogue 4 leaves the squares of the new residual values in v (zero where nothing was written), for the caller
 // to add up over the weight rows.
-template <int EPI, int CW>
+template <int EPI, int CW, bool XT>
 __device__ __forceinline__ void sk_store(const SkParams& P, const SkTables& T, int n, int m0, float (&v)[CW]) {
   const bool col_ok = n < P.N;
   const float b = (P.bias && col_ok) ? P.bias[n] : 0.0f;
-  if (P.X.norm_ss) {
+  if constexpr (XT) {
 #pragma unroll
     for (int j = 0; j < CW; j++) v[j] = v[j] * T.scale[m0 + j] + b;
   } else {
@@ -830,7 +828,7 @@ struct SkSmem {
   int abort_flag;
 };
 
-template <int BN, int STAGES, int EPI>
+template <int BN, int STAGES, int EPI, bool XT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_streamk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                        const SkParams P) {
@@ -933,8 +931,10 @@ gemm_tc_streamk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     const int row = quarter * 32 + lane;          // weight row within the tile held by this thread
     const int first_tile = kb0 / P.n_kb;
     constexpr int CW = (BN >= 32) ? 32 : 16;
-    sk_tables_init<EPI, BN>(P, S.tab, threadIdx.x - 64, 128);
-    if (sk_tables_used<EPI>(P)) asm volatile("bar.sync 1, 128;" ::: "memory");
+    if constexpr (XT) {
+      sk_tables_init<EPI, BN>(P, S.tab, threadIdx.x - 64, 128);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+    }
     uint32_t seg = 0;
     bool ok = true;
     int g = kb0;
@@ -962,7 +962,7 @@ gemm_tc_streamk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
           float v[CW];
 #pragma unroll
           for (int j = 0; j < CW; j++) v[j] = __uint_as_float(r[j]);
-          sk_store<EPI, CW>(P, S.tab, n, c0, v);
+          sk_store<EPI, CW, XT>(P, S.tab, n, c0, v);
           if (EPI == 4) sk_emit_squares<CW>(S.tab, quarter, lane, c0, v);
         } else {
 #pragma unroll
@@ -1004,7 +1004,7 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
 }
 
-template <int BN, int STAGES, int EPI>
+template <int BN, int STAGES, int EPI, bool XT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_clusterk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                         const SkParams P) {
@@ -1089,7 +1089,7 @@ gemm_tc_clusterk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   } else {
     // ---------------------------------------------------------------- epilogue (warps 2..5): this CTA's sums
     pdl_wait();
-    sk_tables_init<EPI, BN>(P, S.tab, threadIdx.x - 64, 128);      // (rank 0 uses them, after the cluster's barriers)
+    if constexpr (XT) sk_tables_init<EPI, BN>(P, S.tab, threadIdx.x - 64, 128);   // (rank 0 uses them, after the cluster's barriers)
     if (kb1 > kb0) {
       if (!__all_sync(0xffffffffu, mbar_wait(&S.acc_full[0], 0, abort_flag))) {
         if (lane == 0) { atomicCAS(P.status, 0, 124); S.abort_flag = 1; }
@@ -1136,7 +1136,7 @@ gemm_tc_clusterk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
       float o[CW];
 #pragma unroll
       for (int j = 0; j < CW; j++) o[j] = v[c0 + j];
-      sk_store<EPI, CW>(P, S.tab, n, c0, o);
+      sk_store<EPI, CW, XT>(P, S.tab, n, c0, o);
       if (EPI == 4) sk_emit_squares<CW>(S.tab, warp & 3, lane, c0, o);
     }
   }
@@ -1363,7 +1363,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TcParams P, i
 // the tile if it is the first beginning inside it.  A block is 4 rows of x (one per warp) by 128 weight rows
 // (four neighbours per lane, so that every load and store is 16 bytes wide); the loads of up to eight partial
 // tiles are in flight together.
-template <int BN, int EPI>
+template <int BN, int EPI, bool XT>
 __global__ void __launch_bounds__(128)
 gemm_tc_fixup_kernel(const SkParams P, int G) {
   pdl_trigger();
@@ -1391,9 +1391,11 @@ gemm_tc_fixup_kernel(const SkParams P, int G) {
   float4 old = make_float4(0.f, 0.f, 0.f, 0.f);
   if (add_wide) old = __ldcg(reinterpret_cast<const float4*>((const float*)P.out + idx));
   float scale = 1.0f;
-  if (P.X.norm_ss) {                               // one lane adds the row's parts, in their order
-    if ((threadIdx.x & 31) == 0) scale = epi_row_scale(P.X, m);
-    scale = __shfl_sync(0xffffffffu, scale, 0);
+  if constexpr (XT) {
+    if (P.X.norm_ss) {                             // one lane adds the row's parts, in their order
+      if ((threadIdx.x & 31) == 0) scale = epi_row_scale(P.X, m);
+      scale = __shfl_sync(0xffffffffu, scale, 0);
+    }
   }
   float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int c0 = first_c; c0 <= last_c; c0 += 8) {
@@ -1413,7 +1415,7 @@ gemm_tc_fixup_kernel(const SkParams P, int G) {
       if (c0 + j <= last_c) { v.x += a[j].x; v.y += a[j].y; v.z += a[j].z; v.w += a[j].w; }
     }
   }
-  v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+  if constexpr (XT) { v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale; }
   if (add_wide) {
     if (P.bias) { v.x += P.bias[n]; v.y += P.bias[n + 1]; v.z += P.bias[n + 2]; v.w += P.bias[n + 3]; }
     const float4 r = make_float4(old.x + v.x, old.y + v.y, old.z + v.z, old.w + v.w);
@@ -1457,12 +1459,12 @@ gemm_tc_fixup_kernel(const SkParams P, int G) {
 }
 
 // Clusters of `cs` CTAs of the cluster kernel that can be resident at once (0: none, or the query failed).
-template <int BN, int STAGES, int EPI>
+template <int BN, int STAGES, int EPI, bool XT>
 static int clusterk_resident(int cs) {
   static int cached[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
   if (cs < 1 || cs > 8) return 0;
   if (cached[cs] < 0) {
-    auto kern = gemm_tc_clusterk_kernel<BN, STAGES, EPI>;
+    auto kern = gemm_tc_clusterk_kernel<BN, STAGES, EPI, XT>;
     const size_t smem = sizeof(SkSmem<BN, STAGES>) + 1024;
     cached[cs] = 0;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess) {
@@ -1482,14 +1484,14 @@ static int clusterk_resident(int cs) {
 
 // The cluster size with which `tiles` clusters fill most SMs in one wave, or 0 if there is none: the partial tiles
 // must fit into rank 0's ring, every rank needs a k-block, and all clusters must be resident together.
-template <int BN, int STAGES, int EPI>
+template <int BN, int STAGES, int EPI, bool XT>
 static int clusterk_size(int tiles, int n_kb) {
   const int sms = sm_count();
   if (tiles > sms) return 0;
   for (int cs = sms / tiles > 8 ? 8 : sms / tiles; cs >= 1; cs--) {
     if (tiles * cs * 10 < sms * 8) break;                       // too few SMs at work: the even split is better
     if (cs > n_kb || (size_t)(cs - 1) * BN * TC_BM * sizeof(float) > (size_t)STAGES * TC_BM * TC_BK * sizeof(bf16)) continue;
-    if (clusterk_resident<BN, STAGES, EPI>(cs) >= tiles) return cs;
+    if (clusterk_resident<BN, STAGES, EPI, XT>(cs) >= tiles) return cs;
   }
   return 0;
 }
@@ -1503,7 +1505,7 @@ static int clusterk_enabled() {
   return on;
 }
 
-template <int BN, int STAGES, int EPI>
+template <int BN, int STAGES, int EPI, bool XT>
 static int launch_clusterk(const CUtensorMap& mw, const CUtensorMap& mx, const SkParams& P, int cs,
                            cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
@@ -1519,7 +1521,7 @@ static int launch_clusterk(const CUtensorMap& mw, const CUtensorMap& mx, const S
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   g_last_launches = 1;
-  return (int)cudaLaunchKernelEx(&cfg, gemm_tc_clusterk_kernel<BN, STAGES, EPI>, mw, mx, P);
+  return (int)cudaLaunchKernelEx(&cfg, gemm_tc_clusterk_kernel<BN, STAGES, EPI, XT>, mw, mx, P);
 }
 
 // The cluster form up to this many (padded) rows of x.  Measured in whole decode steps on the Llama-8B shapes: ahead
@@ -1543,15 +1545,15 @@ static int launch_streamk(const CUtensorMap& mw, const CUtensorMap& mx, const Sk
   const int grid = P.total_kb < sm_count() ? P.total_kb : sm_count();
   // no tile is shared between CTAs when every CTA's stretch is a whole number of tiles
   const bool split_tiles = !(P.tiles % grid == 0);
-#define SK_LAUNCH(E)                                                                                        \
+#define SK_LAUNCH_X(E, XT)                                                                                  \
   {                                                                                                         \
     if constexpr (BN <= CLUSTERK_MAX_BN) {                                                                  \
       if (split_tiles && clusterk_enabled()) {                                                              \
-        const int cs = clusterk_size<BN, STAGES, E>(P.tiles, P.n_kb);                                       \
-        if (cs > 0) return launch_clusterk<BN, STAGES, E>(mw, mx, P, cs, stream);                           \
+        const int cs = clusterk_size<BN, STAGES, E, XT>(P.tiles, P.n_kb);                                   \
+        if (cs > 0) return launch_clusterk<BN, STAGES, E, XT>(mw, mx, P, cs, stream);                       \
       }                                                                                                     \
     }                                                                                                       \
-    auto kern = gemm_tc_streamk_kernel<BN, STAGES, E>;                                                      \
+    auto kern = gemm_tc_streamk_kernel<BN, STAGES, E, XT>;                                                  \
     static bool configured = false;                                                                         \
     if (!configured) {                                                                                      \
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
@@ -1561,8 +1563,12 @@ static int launch_streamk(const CUtensorMap& mw, const CUtensorMap& mx, const Sk
     int st = launch_pdl(kern, grid, TC_THREADS, smem, stream, mw, mx, P);                                   \
     g_last_launches = split_tiles ? 2 : 1;                                                                  \
     if (st != 0 || !split_tiles) return st;                                                                 \
-    return launch_pdl(gemm_tc_fixup_kernel<BN, E>, dim3(grid - 1, (P.M + 3) / 4), 128, 0, stream, P, grid);    \
+    return launch_pdl(gemm_tc_fixup_kernel<BN, E, XT>, dim3(grid - 1, (P.M + 3) / 4), 128, 0, stream, P, grid); \
   }
+  // the four basic epilogues without rows of a handed-over norm take the kernels compiled without the tables
+#define SK_LAUNCH(E)                                                                                        \
+  if (E < 4 && !P.X.norm_ss) SK_LAUNCH_X(E, (E >= 4))                                                       \
+  else SK_LAUNCH_X(E, true)
   switch (epilogue) {
     case 0: SK_LAUNCH(0)
     case 1: SK_LAUNCH(1)
@@ -1573,6 +1579,7 @@ static int launch_streamk(const CUtensorMap& mw, const CUtensorMap& mx, const Sk
     default: return STRATUM_ERR_SHAPE;
   }
 #undef SK_LAUNCH
+#undef SK_LAUNCH_X
 }
 
 STRATUM_EXPORT int stratum_gemm_tc_last_launches(void) { return g_last_launches; }
