@@ -461,3 +461,22 @@ STRATUM_EXPORT int stratum_sample(const float* logits, int ld, int n_rows, int v
   return launch_pdl(sample_kernel, n_rows, SAMPLE_THREADS, 0, stream, logits, ld, vocab, temperature, top_k, top_p,
                     uniform, ids, values);
 }
+
+// ---------------------------------------------------------------- feeding picked ids back on the device
+// ids[i] = prev[feed[i]] where feed[i] >= 0; elsewhere ids[i] stays what the host wrote.  It lets the next decode
+// step be launched before the host has read what this one picked (the reference queues its decode steps on the
+// GPU the same way, with the token ring on the device: stratum/native/stratum_arch_llama.inc.c:1992-2030).
+__global__ void feed_ids_kernel(int* __restrict__ ids, const int* __restrict__ feed, const int* prev, int n) {
+  pdl_trigger();
+  pdl_wait();                                      // `prev` is the work of the step before
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int f = feed[i];
+  if (f >= 0) ids[i] = __ldcg(prev + f);
+}
+
+STRATUM_EXPORT int stratum_feed_ids(int* ids, const int* feed, const int* prev, int n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  return launch_pdl(feed_ids_kernel, (n + 127) / 128, 128, 0, stream, ids, feed, prev, n);
+}
+

@@ -35,6 +35,21 @@ class _EngineBackend(Backend):
     def release(self, slot: int) -> None:
         self.engine.release(slot)
 
+    # one step ahead of the host (replayed graphs only; with an on_logits hook every step is read before the next)
+    @property
+    def runs_ahead(self) -> bool:
+        return self.graphs is not None and self.on_logits is None
+
+    def launch_ahead(self, work, streams, params, after=None, rows_of=None):
+        uniforms = None if params.greedy else [st.uniform() for st in streams]
+        return self.graphs.launch([s for s, _ in work], [t for _, t in work], params.temperature, params.top_k,
+                                  params.top_p, uniforms, trusted=True, advance_now=True, after=after,
+                                  rows_of=rows_of)
+
+    def collect(self, handle):
+        picked, values, _ = self.graphs.collect(handle)
+        return picked, values
+
     def step_and_pick(self, work, streams, params):
         if self.graphs is not None and all(len(toks) == 1 for _, toks in work):
             uniforms = None if params.greedy else [st.uniform() for st in streams]
@@ -114,15 +129,17 @@ class Stratum:
                  sampling: SamplingParams = SamplingParams(), max_batch: Optional[int] = None,
                  on_token: Optional[Callable] = None, want_values: bool = False,
                  on_logits: Optional[Callable] = None,
-                 stream_ids: Optional[Sequence[int]] = None) -> List[GenerationResult]:
+                 stream_ids: Optional[Sequence[int]] = None, run_ahead: bool = True) -> List[GenerationResult]:
         """stop_ids None: the configuration's eos ids; () : none.
         on_logits(logits on the device [live sequences, vocab], picked ids) is called after every step.
-        stream_ids: the random stream each request draws from (default: its index in this call)."""
+        stream_ids: the random stream each request draws from (default: its index in this call).
+        run_ahead: decode steps are launched one ahead of the host's reading of the picked ids (replayed graphs
+        only, and not with on_logits); the tokens are the same either way."""
         if stop_ids is None:
             stop_ids = tuple(getattr(self.config, "eos_token_ids", ()) or ())
         self._backend.on_logits = on_logits
         try:
             return generate(self._backend, prompts, max_new_tokens, stop_ids, sampling, max_batch, on_token,
-                            want_values, stream_ids)
+                            want_values, stream_ids, run_ahead)
         finally:
             self._backend.on_logits = None

@@ -34,10 +34,18 @@ class GenerationResult:
 
 class Backend:
     """What the loop needs from an engine.  `step_and_pick` runs one step for (slot, tokens)
-    pairs and returns the id picked from the logits at each pair's last token (and its logit)."""
+    pairs and returns the id picked from the logits at each pair's last token (and its logit).
+
+    A backend that can start a one-token step without waiting for its result says so with `runs_ahead` and
+    gives `launch_ahead(work, streams, params, after=None, rows_of=None) -> handle`, where work is (slot, token)
+    pairs and a token of None means "the id that the step `after` (launched before, not yet collected) picks
+    in its row rows_of[i]", and `collect(handle) -> (picked ids, their logits)`.  The loop then keeps one step in
+    flight while it reads the one before (the reference queues its decode steps on the GPU ahead of the host in
+    the same way, stratum/native/stratum_arch_llama.inc.c:1992-2030)."""
 
     n_pages: int
     max_seqs: int
+    runs_ahead = False
 
     def acquire(self) -> int: raise NotImplementedError
     def release(self, slot: int) -> None: raise NotImplementedError
@@ -76,7 +84,8 @@ def generate(backend: Backend, prompts: Sequence[Sequence[int]], max_new_tokens,
              stop_ids: Sequence[int] = (), params: SamplingParams = SamplingParams(),
              max_batch: Optional[int] = None,
              on_token: Optional[Callable[[int, int, int, int, float], None]] = None,
-             want_values: bool = False, stream_ids: Optional[Sequence[int]] = None) -> List[GenerationResult]:
+             want_values: bool = False, stream_ids: Optional[Sequence[int]] = None,
+             run_ahead: bool = True) -> List[GenerationResult]:
     """Generate for every prompt.  max_new_tokens: one int or one per request.
     on_token(request, index of the new token, token fed in, token picked, its logit).
     stream_ids: which random stream of the seed each request draws from (default: its index in this call).
@@ -100,30 +109,73 @@ def generate(backend: Backend, prompts: Sequence[Sequence[int]], max_new_tokens,
             if budgets[i] <= 0:
                 results[i].finish_reason = "length"
         slots = {i: backend.acquire() for i in live}
+        carried: List[int] = []          # slots of sequences that ended while a step launched ahead still carries them
+
+        def take(i: int, fed: int, tok: int, val: float) -> bool:
+            """Book one picked token; True if the request goes on."""
+            res = results[i]
+            if on_token is not None:
+                on_token(i, len(res.tokens), fed, tok, val)
+            res.tokens.append(tok)
+            if want_values:
+                res.logit_values.append(val)
+            if tok in stop:
+                res.finish_reason = "stop"
+            elif len(res.tokens) >= budgets[i]:
+                res.finish_reason = "length"
+            return not res.finish_reason
+
         try:
-            feed = {i: list(prompts[i]) for i in live}          # prompts first, then one token each
-            while live:
-                picked, values = backend.step_and_pick([(slots[i], feed[i]) for i in live],
-                                                       [streams[i] for i in live], params)
-                still = []
-                for i, tok, val in zip(live, picked, values):
-                    res = results[i]
-                    if on_token is not None:
-                        on_token(i, len(res.tokens), feed[i][-1], tok, val)
-                    res.tokens.append(tok)
-                    if want_values:
-                        res.logit_values.append(val)
-                    if tok in stop:
-                        res.finish_reason = "stop"
-                    elif len(res.tokens) >= budgets[i]:
-                        res.finish_reason = "length"
-                    if res.finish_reason:
-                        backend.release(slots.pop(i))           # ends early: its slot is free at once
-                    else:
-                        feed[i] = [tok]
-                        still.append(i)
-                live = still
+            # the prompts, of unequal lengths, in one step
+            picked, values = backend.step_and_pick([(slots[i], list(prompts[i])) for i in live],
+                                                   [streams[i] for i in live], params) if live else ([], [])
+            still = []
+            for i, tok, val in zip(live, picked, values):
+                if take(i, prompts[i][-1], tok, val):
+                    still.append(i)
+                else:
+                    backend.release(slots.pop(i))               # ends early: its slot is free at once
+            live = still
+            if run_ahead and backend.runs_ahead:
+                # one token per live sequence per step, the next step launched before this one's ids are read: it
+                # takes them on the device.  Who hits a stop id is known a step late; such a sequence rides along
+                # for one step more (its row is ignored, rows never mix) and its slot goes back after that step.
+                flight = backend.launch_ahead([(slots[i], results[i].tokens[-1]) for i in live],
+                                              [streams[i] for i in live], params) if live else None
+                while flight is not None:
+                    nxt = [i for i in live if not results[i].finish_reason
+                           and len(results[i].tokens) + 1 < budgets[i]]                  # if no stop id comes
+                    ahead = None
+                    if nxt:
+                        row = {i: r for r, i in enumerate(live)}
+                        ahead = backend.launch_ahead([(slots[i], None) for i in nxt], [streams[i] for i in nxt],
+                                                     params, after=flight, rows_of=[row[i] for i in nxt])
+                    picked, values = backend.collect(flight)
+                    while carried:                               # nothing in flight holds them any more
+                        backend.release(carried.pop())
+                    for i, tok, val in zip(live, picked, values):
+                        if results[i].finish_reason:             # ended a step ago; this row was its ride along
+                            continue
+                        if not take(i, results[i].tokens[-1], tok, val):
+                            if ahead is not None and i in nxt:
+                                carried.append(slots.pop(i))
+                            else:
+                                backend.release(slots.pop(i))
+                    flight, live = ahead, nxt
+            else:
+                while live:
+                    picked, values = backend.step_and_pick([(slots[i], [results[i].tokens[-1]]) for i in live],
+                                                           [streams[i] for i in live], params)
+                    still = []
+                    for i, tok, val in zip(live, picked, values):
+                        if take(i, results[i].tokens[-1], tok, val):
+                            still.append(i)
+                        else:
+                            backend.release(slots.pop(i))
+                    live = still
         finally:
+            for s in carried:
+                backend.release(s)
             for s in slots.values():
                 backend.release(s)
     return results

@@ -51,14 +51,19 @@ class _Captured:
         self.rows, self.width, self.greedy = rows, width, greedy
         B = rows
         self.desc = StepDescription(engine, B, B, B, width, pinned=True,
-                                    extras=(("temperature", B), ("top_k", B), ("top_p", B), ("uniform", B)))
+                                    extras=(("temperature", B), ("top_k", B), ("top_p", B), ("uniform", B),
+                                            ("feed", B)))
         self.views = self.desc.views
         dev = engine.runtime.device
         # picked ids | their logits (float32 bits) | the kernels' status word: one copy back per step
         self.out = torch.zeros(2 * B + 1, dtype=torch.int32, device=dev)
         self.out_ids = self.out[:B]
         self.out_vals = self.out[B:2 * B].view(torch.float32)
-        self.out_host = torch.empty(2 * B + 1, dtype=torch.int32).pin_memory()
+        # two host buffers for the results, used in turn: a step may be launched before the one before it is read
+        self.out_hosts = [torch.empty(2 * B + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.turn = 0
+        self.uploaded = torch.cuda.Event()            # the description's copy to the device has been made
+        self.upload_pending = False
         self.signature = None                         # (slots, cache epoch) the membership was last written for
         self.sampling = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -79,7 +84,6 @@ class DecodeGraphs:
         self.max_graphs = max_graphs
         self.graphs: "OrderedDict[Tuple[int, int, bool], _Captured]" = OrderedDict()
         self.pool = None
-        self.done = torch.cuda.Event()
         self.captures = 0
         self.h2d_bytes = self.d2h_bytes = 0           # of the last step
 
@@ -140,19 +144,38 @@ class DecodeGraphs:
         """One token for each slot; returns the picked ids and their logits (host lists).
         trusted: the tokens are ids this engine picked itself (no range check needed).
         On error nothing has changed: no sequence is longer than before."""
+        return self.collect(self.launch(slots, tokens, temperature, top_k, top_p, uniforms, trusted))
+
+    def launch(self, slots: Sequence[int], tokens: Sequence[Optional[int]], temperature: float, top_k: int,
+               top_p: float, uniforms: Optional[Sequence[float]], trusted: bool = False,
+               advance_now: bool = False, after: Optional["_InFlight"] = None,
+               rows_of: Optional[Sequence[int]] = None) -> "_InFlight":
+        """Start one token for each slot and return without waiting; `collect` gives the result.
+
+        advance_now: the sequences' lengths are advanced here, at the launch, not at `collect`: a caller that
+        launches the next step before it collects this one needs them so.  (A kernel that gives up a wait still
+        raises at `collect`, but the lengths then stay advanced.)
+        after / rows_of: the step launched just before this one (with advance_now), not yet collected, and for
+        every slot its row there (-1: the token is given).  Such a slot's token is the id that step picks: it is
+        fed back on the device, so the host launches this step before it has read the one before."""
         eng = self.engine
         cache = eng.cache
         B = len(slots)
         slots = list(slots)
-        token_lists = [(int(t),) for t in tokens]
-        eng.validate(slots, token_lists, None, trusted_tokens=trusted)
+        ahead = after is not None
+        if ahead and not (advance_now and after.advanced):
+            raise StepError("a step launched ahead of the one before needs both launched with advance_now")
+        token_lists = [((0 if t is None else int(t)),) for t in tokens]
+        eng.validate(slots, token_lists, None, trusted_tokens=trusted or ahead)
         ones = _ONES[:B] if B <= len(_ONES) else [1] * B
         cache.reserve(slots, ones)
         before = [cache.length(s) for s in slots]
         c = self._get(padded_rows(B), width_bucket(pages_for(max(before) + 1)), not (temperature > 0.0))
         if c.graph is None:
             self._capture(c)
-        R = c.rows
+        if c.upload_pending:                          # the pinned description is about to be rewritten
+            c.uploaded.synchronize()
+            c.upload_pending = False
         v = c.views
         # what a sequence holds changes every step; who is in the batch and which pages they own only now and then
         signature = (tuple(slots), cache.epoch)
@@ -169,18 +192,44 @@ class DecodeGraphs:
         u[:] = 0.0
         if uniforms is not None:
             u[:B] = uniforms
+        if ahead:
+            v["feed"][:] = -1
+            v["feed"][:B] = rows_of
         c.desc.upload()
+        c.uploaded.record()
+        c.upload_pending = True
+        if ahead:
+            K.feed_ids(c.desc.field("ids"), c.desc.field("feed"), after.captured.out_ids)
         c.graph.replay()
         K.count_launches(c.kernels)
-        c.out_host.copy_(c.out, non_blocking=True)
-        self.done.record()
-        self.done.synchronize()
-        out = c.out_host.numpy()
+        out_host = c.out_hosts[c.turn]
+        c.turn ^= 1
+        out_host.copy_(c.out, non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        if advance_now:
+            cache.advance(slots, ones)
+        self.h2d_bytes, self.d2h_bytes = c.total * 4, (2 * c.rows + 1) * 4
+        return _InFlight(c, slots, ones, out_host, done, advanced=advance_now)
+
+    def collect(self, h: "_InFlight") -> Tuple[List[int], List[float], _Captured]:
+        h.done.synchronize()
+        c, B, R = h.captured, len(h.slots), h.captured.rows
+        out = h.out_host.numpy()
         if out[2 * R] != 0:
             K.check_status()                          # raises, and clears the word
-        cache.advance(slots, ones)
-        self.h2d_bytes, self.d2h_bytes = c.total * 4, (2 * R + 1) * 4
+        if not h.advanced:
+            self.engine.cache.advance(h.slots, h.ones)
         return out[:B].tolist(), out[R:R + B].view(np.float32).tolist(), c
+
+
+class _InFlight:
+    """A launched decode step whose result has not been read yet."""
+    __slots__ = ("captured", "slots", "ones", "out_host", "done", "advanced")
+
+    def __init__(self, captured, slots, ones, out_host, done, advanced):
+        self.captured, self.slots, self.ones = captured, slots, ones
+        self.out_host, self.done, self.advanced = out_host, done, advanced
 
 
 _ONES = [1] * 1024

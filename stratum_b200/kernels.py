@@ -577,6 +577,15 @@ def argmax(logits: torch.Tensor, ids: torch.Tensor, values: Optional[torch.Tenso
              _ptr(pv), _ptr(pi), _ptr(cnt), _stream()), "argmax")
 
 
+def feed_ids(ids: torch.Tensor, feed: torch.Tensor, prev: torch.Tensor) -> None:
+    """ids[i] = prev[feed[i]] where feed[i] >= 0 (int32 tensors on the device): picked ids fed back without the host."""
+    _need(ids, "ids", torch.int32); _need(feed, "feed", torch.int32); _need(prev, "prev", torch.int32)
+    if feed.numel() != ids.numel():
+        raise KernelError("feed_ids: ids and feed disagree")
+    f = _fn("sampling", "stratum_feed_ids", [c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    _check(f(_ptr(ids), _ptr(feed), _ptr(prev), ids.numel(), _stream()), "feed_ids")
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
            uniform: torch.Tensor, ids: torch.Tensor, values: Optional[torch.Tensor] = None) -> None:
     _need(logits, "logits", torch.float32, contiguous=False); _need(ids, "ids", torch.int32)

@@ -263,3 +263,33 @@ def test_a_given_up_wait_is_an_error_and_changes_nothing(folders):
     assert llm.engine.length(slot) == 5
     llm.release(slot)
     assert llm.engine.cache.tokens_held() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_one_step_ahead_gives_the_same_tokens(folders, dtype):
+    """Decode steps launched before the host has read the step before (ids fed back on the device) against the
+    same steps read one by one: greedy with a stop id that ends requests at different steps, and sampling, in
+    batches that follow one another so that slots given back late (after their ride along) are used again."""
+    from stratum_b200 import SamplingParams, Stratum
+    path = folders["B", dtype]
+    cfg, w = load_plain(path)
+    rng = np.random.default_rng(31)
+    V = cfg["vocab_size"]
+    prompts = [rand_tokens(rng, n, V) for n in (3, 60, 17, 9, 64, 2, 30)]
+    budgets = [70, 9, 30, 12, 5, 66, 8]
+    llm = Stratum(path, dtype=dtype, max_tokens=64 * 6, max_seqs=3)      # three requests at a time: three batches
+    base = llm.generate(prompts, max_new_tokens=budgets, stop_ids=(), run_ahead=False)
+    # a stop id that some requests meet early, others never
+    counts = {}
+    for r in base:
+        for t in r.tokens[2:20]:
+            counts[t] = counts.get(t, 0) + 1
+    stop = max(counts, key=counts.get)
+    for params in (SamplingParams(), SamplingParams(temperature=0.9, top_k=20, seed=5)):
+        a = llm.generate(prompts, max_new_tokens=budgets, stop_ids=[stop], sampling=params, run_ahead=False)
+        b = llm.generate(prompts, max_new_tokens=budgets, stop_ids=[stop], sampling=params, run_ahead=True)
+        assert [(r.tokens, r.finish_reason) for r in a] == [(r.tokens, r.finish_reason) for r in b]
+        assert any(r.finish_reason == "stop" for r in a) and any(r.finish_reason == "length" for r in a)
+    _check_greedy(cfg, w, prompts[1], llm.generate([prompts[1]], 9, stop_ids=())[0].tokens, dtype)
+    llm.engine.cache.check()
+    assert llm.engine.cache.tokens_held() == 0

@@ -125,3 +125,91 @@ def test_streams_belong_to_requests_not_to_batches():
     assert sorted(seen.values()) == together
     assert together[0][:2] != together[1][:2]
     assert Pcg32(11, 2).uniform() in [v[0] for v in together]
+
+
+class AheadBackend(FakeBackend):
+    """The same arithmetic with steps that can be launched before the one before is read.  A token of None is
+    taken from the step named in `after`, as the device would; the backend checks what a real one relies on:
+    steps are collected in the order of their launches, at most two are in flight, a step launched ahead names
+    the one launched just before it, and no slot is released while a step in flight still carries it."""
+    runs_ahead = True
+
+    def __init__(self, **kw):
+        super().__init__(**kw)
+        self.flying = []
+        self.most_flying = 0
+        self.rides = 0
+
+    def launch_ahead(self, work, streams, params, after=None, rows_of=None):
+        assert len(streams) == len(work) and len(self.flying) <= 1
+        if after is not None:
+            assert self.flying and self.flying[-1] is after and len(rows_of) == len(work)
+        toks = []
+        for k, (slot, tok) in enumerate(work):
+            assert slot in self.sums, "stepped after its release"
+            if tok is None:
+                tok = after["picked"][rows_of[k]]
+            toks.append(tok)
+        self.steps.append([(s, [t]) for (s, _), t in zip(work, toks)])
+        picked = []
+        for (slot, _), tok in zip(work, toks):
+            self.sums[slot] += tok
+            picked.append(self.sums[slot] % 50)
+        h = {"picked": picked, "slots": [s for s, _ in work]}
+        self.flying.append(h)
+        self.most_flying = max(self.most_flying, len(self.flying))
+        return h
+
+    def collect(self, h):
+        assert self.flying and self.flying[0] is h, "collected out of order"
+        self.flying.pop(0)
+        return h["picked"], [float(p) for p in h["picked"]]
+
+    def release(self, slot):
+        assert all(slot not in h["slots"] for h in self.flying), "released while a step in flight carries it"
+        super().release(slot)
+
+
+@pytest.mark.parametrize("stop", [(), (40,), (6, 30), (10,)])
+def test_one_step_ahead_gives_the_same_tokens(stop):
+    prompts = [[10], [3], [1, 2, 3], [7, 7], [9]]
+    budgets = [6, 2, 9, 1, 5]
+    plain = generate(FakeBackend(max_seqs=3), prompts, budgets, stop_ids=stop)
+    b = AheadBackend(max_seqs=3)
+    seen = []
+    ahead = generate(b, prompts, budgets, stop_ids=stop, on_token=lambda *a: seen.append(a))
+    assert [(r.tokens, r.finish_reason) for r in ahead] == [(r.tokens, r.finish_reason) for r in plain]
+    assert b.most_flying == 2 and not b.flying and not b.sums and sorted(b.free) == [0, 1, 2]
+    # on_token sees every token once, in order, with the token that was fed in
+    for i, r in enumerate(ahead):
+        mine = [a for a in seen if a[0] == i]
+        assert [a[1] for a in mine] == list(range(len(r.tokens))) and [a[3] for a in mine] == r.tokens
+        assert [a[2] for a in mine] == [prompts[i][-1]] + r.tokens[:-1]
+    # and with run_ahead off the backend's ordinary steps are used
+    b2 = AheadBackend(max_seqs=3)
+    off = generate(b2, prompts, budgets, stop_ids=stop, run_ahead=False)
+    assert [r.tokens for r in off] == [r.tokens for r in plain] and b2.most_flying == 0
+
+
+def test_a_stopped_request_rides_one_step_and_is_then_released():
+    b = AheadBackend(max_seqs=2)
+    res = generate(b, [[10], [3]], [6, 6], stop_ids=[40])       # request 0: 10, 20, 40 stop; request 1 runs on
+    assert res[0].tokens == [10, 20, 40] and res[0].finish_reason == "stop"
+    assert res[1].tokens == _expected([3], 6)
+    # steps: prompts; then both; both; both (request 0 has stopped, unknown yet: it rides along); then request 1 alone
+    assert [len(s) for s in b.steps] == [2, 2, 2, 2, 1, 1]
+    assert not b.sums
+
+
+def test_errors_while_running_ahead_give_every_slot_back():
+    class Boom(AheadBackend):
+        def collect(self, h):
+            if len(self.steps) >= 4:
+                self.flying.clear()
+                raise RuntimeError("boom")
+            return super().collect(h)
+
+    b = Boom(max_seqs=3)
+    with pytest.raises(RuntimeError):
+        generate(b, [[1], [2], [3]], 8, stop_ids=[12])
+    assert not b.sums and sorted(b.free) == [0, 1, 2]
