@@ -21,6 +21,13 @@
 // rare, so per tile a softmax thread touches S and P only, and its few registers let two CTAs share an SM: one
 // CTA's MMAs run under the other's softmax.
 //
+// Two forms.  NH = 1: one CTA owns 128 query rows and two CTAs share an SM.  NH = 2: one CTA owns 256 query rows
+// as two halves of 128 (64 / gs consecutive tokens each), each half with its own MMA-issuing warp, eight softmax
+// warps, S buffers, P buffer and O accumulator, exactly as in a CTA of the first form; the halves share the
+// producer and the K and V rings, so every key and value tile is fetched from L2 once for 256 rows instead of once
+// for 128.  That traffic is what bounds the first form on long prompts: with every MMA and every exponential taken
+// out, a prompt of 8,192 tokens still took 251 of its 560 us, fetching 4.3 GB of K and V tiles at 17 TB/s.
+//
 // V is used as stored, [key][dim]: as the B operand of P V its n index (dim) is the contiguous one
 // ("MN-major"), which the instruction takes directly; no transpose is made anywhere.
 //
@@ -33,8 +40,8 @@
 #define FA_ROWS 128
 #define FA_KEYS 64
 #define FA_STAGES 2
-#define FA_SOFTMAX_WARPS 8
-#define FA_THREADS (64 + FA_SOFTMAX_WARPS * 32)
+#define FA_SOFTMAX_WARPS 8                         // per half
+#define FA_THREADS(NH) (32 + (NH) * 32 + (NH) * FA_SOFTMAX_WARPS * 32)
 
 struct FaParams {
   const int* token_pos;
@@ -46,14 +53,14 @@ struct FaParams {
   float scale_log2;        // scale * log2(e): exponentials are taken with exp2
 };
 
-template <int HD>
+template <int HD, int NH>
 struct FaSmem {
-  alignas(1024) bf16 q[FA_ROWS * HD];                 // [HD/64 blocks of 64 dims][128 rows][64]
+  alignas(1024) bf16 q[NH][FA_ROWS * HD];             // per half: [HD/64 blocks of 64 dims][128 rows][64]
   alignas(1024) bf16 k[FA_STAGES][FA_KEYS * HD];      // [HD/64][64 keys][64 dims]
   alignas(1024) bf16 v[FA_STAGES][FA_KEYS * HD];      // [HD/64][64 keys][64 dims]
-  alignas(1024) bf16 p[FA_ROWS * FA_KEYS];            // [128 rows][64 keys]; at the end: the rows' two half sums
+  alignas(1024) bf16 p[NH][FA_ROWS * FA_KEYS];        // per half: [128 rows][64 keys]; at the end: the rows' two half sums
   uint64_t q_full, k_full[FA_STAGES], v_full[FA_STAGES];
-  uint64_t s_full[2], p_full, pv_full[2];
+  uint64_t s_full[NH][2], p_full[NH], pv_full[NH][2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -73,16 +80,29 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 #define FA_FAIL(code) { atomicCAS(P.status, 0, code); S.abort_flag = 1; }
 
-template <int HD>
-__global__ void __launch_bounds__(FA_THREADS, 2)
+// What one half (128 query rows) of a CTA works on.
+struct FaHalf {
+  int ntok, first_pos, last_pos, n_tiles;
+};
+__device__ __forceinline__ FaHalf fa_half(const FaParams& P, int h, int seq, int first_pos, int ntok, int lo_tile) {
+  FaHalf H;
+  H.ntok = min(max(ntok - h * P.tokens_per_tile, 0), P.tokens_per_tile);
+  H.first_pos = first_pos + h * P.tokens_per_tile;
+  H.last_pos = H.first_pos + H.ntok - 1;
+  H.n_tiles = (seq < 0 || H.ntok <= 0) ? 0 : H.last_pos / FA_KEYS - lo_tile + 1;
+  return H;
+}
+
+template <int HD, int NH>
+__global__ void __launch_bounds__(FA_THREADS(NH), NH == 1 ? 2 : 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const FaParams P) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  using Smem = FaSmem<HD>;
+  using Smem = FaSmem<HD, NH>;
   Smem& S = *reinterpret_cast<Smem*>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int DB = HD / 64;                           // blocks of 64 dims
-  constexpr uint32_t TMEM_COLS = 256;                   // S0 | S1 | O (Hd columns); two CTAs of an SM fill its 512
+  constexpr uint32_t TMEM_COLS = 256 * NH;              // per half: S0 | S1 | O (Hd columns); an SM has 512
   constexpr uint32_t COL_PV = 128;
   pdl_trigger();
   // the swizzled tiles need 1024-byte alignment, and there is no room to round the base up when two CTAs are to
@@ -101,8 +121,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   if (threadIdx.x == 0) {
     mbar_init(&S.q_full, 1);
     for (int s = 0; s < FA_STAGES; s++) { mbar_init(&S.k_full[s], 1); mbar_init(&S.v_full[s], 1); }
-    for (int b = 0; b < 2; b++) { mbar_init(&S.s_full[b], 1); mbar_init(&S.pv_full[b], 1); }
-    mbar_init(&S.p_full, FA_SOFTMAX_WARPS);
+    for (int h = 0; h < NH; h++) {
+      for (int b = 0; b < 2; b++) { mbar_init(&S.s_full[h][b], 1); mbar_init(&S.pv_full[h][b], 1); }
+      mbar_init(&S.p_full[h], FA_SOFTMAX_WARPS);
+    }
     S.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -115,41 +137,62 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = S.tmem_base;
 
+  // keys are walked from the first half's first tile (a later half whose window begins further on masks them out)
   const int first_pos = P.token_pos[tok0];
-  const int last_pos = first_pos + ntok - 1;
   const int lo_tile = (P.window > 0 && first_pos - P.window + 1 > 0) ? (first_pos - P.window + 1) / FA_KEYS : 0;
-  const int n_tiles = (seq < 0) ? 0 : last_pos / FA_KEYS - lo_tile + 1;
+  const int nt0 = fa_half(P, 0, seq, first_pos, ntok, lo_tile).n_tiles;
+  const int nt1 = NH > 1 ? fa_half(P, 1, seq, first_pos, ntok, lo_tile).n_tiles : 0;      // (never more than nt0 + 1)
+  const int n_tiles_max = max(nt0, nt1);
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
-    if (lane == 0 && n_tiles > 0) {
+    if (lane == 0 && n_tiles_max > 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
       pdl_wait();                                        // q and the newest keys come from the kernel before
-      mbar_expect_tx(&S.q_full, FA_ROWS * HD * sizeof(bf16));
-      for (int db = 0; db < DB; db++)
-        tma_load_3d(&map_q, S.q + db * FA_ROWS * 64, &S.q_full, db * 64, kvh * P.gs, tok0);
+      const int live = (nt0 > 0) + (nt1 > 0);
+      mbar_expect_tx(&S.q_full, (uint32_t)live * FA_ROWS * HD * sizeof(bf16));
+#pragma unroll
+      for (int h = 0; h < NH; h++)
+        if ((h == 0 ? nt0 : nt1) > 0)
+          for (int db = 0; db < DB; db++)
+            tma_load_3d(&map_q, S.q[h] + db * FA_ROWS * 64, &S.q_full, db * 64, kvh * P.gs, tok0 + h * P.tokens_per_tile);
       const int* bt = P.block_table + (size_t)seq * P.bt_stride;
       // K and V have rings of their own: a K tile is free again as soon as its scores are computed (s_full), a
       // whole tile earlier than the V tile beside it (pv_full), so the next K is already on its way while P V still
       // runs.  One thread feeds both rings, polling (never suspended in a wait on one ring while the other has room).
-      // The MMA thread pays about a hundred cycles for every instruction it issues, commits and waits included,
-      // and is what the kernel's pace hangs on: so no barrier exists only to free a buffer.  (The S buffer of tile
-      // j-1 is free for tile j+1 once P of tile j-1 has arrived, which the MMA thread has waited for by then.)
+      // The MMA threads pay about a hundred cycles for every instruction they issue, commits and waits included:
+      // so no barrier exists only to free a buffer.  (The S buffer of tile j-1 is free for tile j+1 once P of tile
+      // j-1 has arrived, which the MMA thread has waited for by then.)  With two halves a stage is free once every
+      // half that walks that tile has read it.
+      auto k_free = [&](int j) -> bool {                 // tile j - 2 has left the K stage that tile j wants
+        bool ok = true;
+#pragma unroll
+        for (int h = 0; h < NH; h++)
+          if (j - 2 < (h == 0 ? nt0 : nt1)) ok = ok && mbar_test_wait(&S.s_full[h][j & 1], ((j - 2) >> 1) & 1);
+        return ok;
+      };
+      auto v_free = [&](int j) -> bool {
+        bool ok = true;
+#pragma unroll
+        for (int h = 0; h < NH; h++)
+          if (j - 2 < (h == 0 ? nt0 : nt1)) ok = ok && mbar_test_wait(&S.pv_full[h][j & 1], ((j - 2) >> 1) & 1);
+        return ok;
+      };
       bool ok = true;
       int jk = 0, jv = 0;
       uint32_t idle = 0;
-      while ((jk < n_tiles || jv < n_tiles) && ok) {
+      while ((jk < n_tiles_max || jv < n_tiles_max) && ok) {
         bool moved = false;
-        if (jk < n_tiles && (jk < 2 || mbar_test_wait(&S.s_full[jk & 1], ((jk - 2) >> 1) & 1))) {
+        if (jk < n_tiles_max && (jk < 2 || k_free(jk))) {
           const int s = jk % FA_STAGES;
           const int row = (bt[lo_tile + jk] * P.n_kv + kvh) * FA_KEYS;
           mbar_expect_tx(&S.k_full[s], FA_KEYS * HD * sizeof(bf16));
           for (int db = 0; db < DB; db++) tma_load_2d(&map_k, S.k[s] + db * FA_KEYS * 64, &S.k_full[s], db * 64, row);
           jk++; moved = true;
         }
-        if (jv < n_tiles && (jv < 2 || mbar_test_wait(&S.pv_full[jv & 1], ((jv - 2) >> 1) & 1))) {
+        if (jv < n_tiles_max && (jv < 2 || v_free(jv))) {
           const int s = jv % FA_STAGES;
           const int row = (bt[lo_tile + jv] * P.n_kv + kvh) * FA_KEYS;
           mbar_expect_tx(&S.v_full[s], FA_KEYS * HD * sizeof(bf16));
@@ -164,16 +207,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         for (int i = 0; i < 2000; i++) __nanosleep(1000);   // let copies already issued land
       }
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------------- MMA issuer
+  } else if (warp <= NH) {
+    // ---------------------------------------------------------------- MMA issuer of half `warp - 1`
     // The whole warp walks through the waits together and one elected lane issues: with warp-uniform control
     // flow the operands of the MMAs (descriptors, addresses) stay warp-uniform values.
+    const int h = warp - 1;
+    const int n_tiles = h == 0 ? nt0 : nt1;
     if (n_tiles > 0) {
       const uint32_t idesc_s = instr_desc_bf16(FA_KEYS);
       const uint32_t idesc_pv = instr_desc_bf16(HD, true);
+      const uint32_t tmem_h = tmem_base + h * 256;
       bool ok = __all_sync(0xffffffffu, mbar_wait(&S.q_full, 0, abort_flag));
       if (!ok && lane == 0) FA_FAIL(202);
-      const uint32_t q_addr = smem_u32(S.q), p_addr = smem_u32(S.p);
+      const uint32_t q_addr = smem_u32(S.q[h]), p_addr = smem_u32(S.p[h]);
       auto issue_scores = [&](int j) -> bool {
         const int s = j % FA_STAGES, b = j & 1;
         if (!__all_sync(0xffffffffu, mbar_wait(&S.k_full[s], (j / FA_STAGES) & 1, abort_flag))) {
@@ -187,9 +233,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           for (int db = 0; db < DB; db++)
 #pragma unroll
             for (int kk = 0; kk < 4; kk++)
-              umma_bf16(tmem_base + b * FA_KEYS, smem_desc_sw128(q_addr + db * FA_ROWS * 128 + kk * 32),
+              umma_bf16(tmem_h + b * FA_KEYS, smem_desc_sw128(q_addr + db * FA_ROWS * 128 + kk * 32),
                         smem_desc_sw128(k_addr + db * FA_KEYS * 128 + kk * 32), idesc_s, (db | kk) ? 1u : 0u);
-          umma_commit(&S.s_full[b]);            // to the softmax warps, and to the producer: K of this tile is read
+          umma_commit(&S.s_full[h][b]);         // to the softmax warps, and to the producer: K of this tile is read
         }
         __syncwarp();
         return true;
@@ -198,31 +244,36 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       for (int j = 0; j < n_tiles && ok; j++) {
         if (j + 1 < n_tiles) { ok = issue_scores(j + 1); if (!ok) break; }
         const int s = j % FA_STAGES;
-        if (!__all_sync(0xffffffffu, mbar_wait(&S.p_full, j & 1, abort_flag))) { if (lane == 0) FA_FAIL(205); ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&S.p_full[h], j & 1, abort_flag))) { if (lane == 0) FA_FAIL(205); ok = false; break; }
         if (!__all_sync(0xffffffffu, mbar_wait(&S.v_full[s], (j / FA_STAGES) & 1, abort_flag))) { if (lane == 0) FA_FAIL(206); ok = false; break; }
         tc_fence_after();
         const uint32_t v_addr = smem_u32(S.v[s]);
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < 4; kk++)        // 16 keys a step: 32 bytes along a row of P, 16 rows of V
-            umma_bf16(tmem_base + COL_PV, smem_desc_sw128(p_addr + kk * 32),
+            umma_bf16(tmem_h + COL_PV, smem_desc_sw128(p_addr + kk * 32),
                       smem_desc_sw128_mn(v_addr + kk * 16 * 128, FA_KEYS * 128), idesc_pv, (j | kk) ? 1u : 0u);
-          umma_commit(&S.pv_full[j & 1]);       // to the softmax warps (P is read, O has the tile), and to the
+          umma_commit(&S.pv_full[h][j & 1]);    // to the softmax warps (P is read, O has the tile), and to the
                                                 // producer: V of this tile is read
         }
         __syncwarp();
       }
     }
-  } else if (n_tiles > 0) {
-    // ---------------------------------------------------------------- softmax (warps 2..9)
+  } else {
+    // ---------------------------------------------------------------- softmax (eight warps per half)
+    const int sw = warp - (1 + NH);
+    const int h = sw / FA_SOFTMAX_WARPS;
+    const FaHalf H = fa_half(P, h, seq, first_pos, ntok, lo_tile);
+    const int n_tiles = H.n_tiles;
+    if (n_tiles > 0) {
     const int quarter = warp & 3;                        // TMEM lanes this warp may read
-    const int half = (warp - 2) >> 2;                    // 0: keys 0..31 and dims 0..Hd/2-1;  1: the other halves
+    const int half = (sw % FA_SOFTMAX_WARPS) >> 2;       // 0: keys 0..31 and dims 0..Hd/2-1;  1: the other halves
     const int row = quarter * 32 + lane;
     const int tok = row / P.gs, head = row % P.gs;
-    const bool valid = tok < ntok;
-    const int pos = first_pos + (valid ? tok : 0);
+    const bool valid = tok < H.ntok;
+    const int pos = H.first_pos + (valid ? tok : 0);
     const int lo = (P.window > 0 && pos - P.window + 1 > 0) ? pos - P.window + 1 : 0;
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t lane_addr = tmem_base + h * 256 + ((uint32_t)(quarter * 32) << 16);
     constexpr int OD = HD / 2;                           // output dims per thread
     const uint32_t o_addr = lane_addr + COL_PV + half * OD;
     float m_ref = -INFINITY, l = 0.f;                    // reference maximum (scaled, log2 domain); sum of this half
@@ -230,7 +281,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
     for (int j = 0; j < n_tiles; j++) {
       const int b = j & 1;
-      if (!__all_sync(0xffffffffu, mbar_wait(&S.s_full[b], (j >> 1) & 1, abort_flag))) {   // (a warp gives up as one)
+      if (!__all_sync(0xffffffffu, mbar_wait(&S.s_full[h][b], (j >> 1) & 1, abort_flag))) {   // (a warp gives up as one)
         if (lane == 0) FA_FAIL(209);
         ok = false;
         break;
@@ -243,7 +294,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // maximum over the whole tile; keys beyond a row's own position (or before its window) are masked, which
       // only tiles on the diagonal (or at the window's edge) need
       const int key0 = (lo_tile + j) * FA_KEYS;
-      const bool needs_mask = (key0 + FA_KEYS - 1 > first_pos) || (P.window > 0) || (ntok < P.tokens_per_tile);
+      const bool needs_mask = (key0 + FA_KEYS - 1 > H.first_pos) || (P.window > 0) || (H.ntok < P.tokens_per_tile);
       // (four running maxima, then combined: one chain of 64 dependent comparisons would cost more time than
       // everything else a thread does per tile)
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -286,7 +337,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       if (j > 0) {
         // P V of the tile before has read P and has been added into O
-        if (!__all_sync(0xffffffffu, mbar_wait(&S.pv_full[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag))) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&S.pv_full[h][(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag))) {
           if (lane == 0) FA_FAIL(208);
           ok = false;
           break;
@@ -307,7 +358,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       l = l * corr + (sum0 + sum1);
       {
-        uint8_t* prow = reinterpret_cast<uint8_t*>(S.p) + row * 128;
+        uint8_t* prow = reinterpret_cast<uint8_t*>(S.p[h]) + row * 128;
 #pragma unroll
         for (int c = 0; c < 4; c++) {
           const int chunk = half * 4 + c;                // 16-byte chunk = 8 keys
@@ -318,21 +369,23 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       fence_async_shared();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&S.p_full);
+      if (lane == 0) mbar_arrive(&S.p_full[h]);
     }
-    if (ok && !__all_sync(0xffffffffu, mbar_wait(&S.pv_full[(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag))) {
+    if (ok && !__all_sync(0xffffffffu, mbar_wait(&S.pv_full[h][(n_tiles - 1) & 1], ((n_tiles - 1) >> 1) & 1, abort_flag))) {
       if (lane == 0) FA_FAIL(208);
       ok = false;
     }
     tc_fence_after();
     // the two halves of the keys kept separate sums: add them (P is no longer read; named barrier among the
-    // softmax warps, reached by all of them)
-    float* l_buf = reinterpret_cast<float*>(S.p);
+    // softmax warps of this half of the rows, reached by all of them)
+    float* l_buf = reinterpret_cast<float*>(S.p[h]);
     l_buf[half * FA_ROWS + row] = l;
-    asm volatile("bar.sync 1, %0;" ::"n"(FA_SOFTMAX_WARPS * 32) : "memory");
+    if (h == 0) asm volatile("bar.sync 1, %0;" ::"n"(FA_SOFTMAX_WARPS * 32) : "memory");
+    else asm volatile("bar.sync 2, %0;" ::"n"(FA_SOFTMAX_WARPS * 32) : "memory");
     if (ok && !S.abort_flag) {
       const float inv = 1.0f / (l_buf[row] + l_buf[FA_ROWS + row]);
-      bf16* op = P.out + (size_t)(tok0 + (valid ? tok : 0)) * P.ldo + (size_t)(kvh * P.gs + head) * HD + half * OD;
+      bf16* op = P.out + (size_t)(tok0 + h * P.tokens_per_tile + (valid ? tok : 0)) * P.ldo +
+                 (size_t)(kvh * P.gs + head) * HD + half * OD;
 #pragma unroll
       for (int c = 0; c < OD; c += 32) {
         float o[32];
@@ -352,6 +405,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           }
         }
       }
+    }
     }
   }
   tc_fence_before();
@@ -374,30 +428,32 @@ static int make_map_nd(CUtensorMap* map, const void* base, int rank, const cuuin
   return r == CUDA_SUCCESS ? 0 : STRATUM_ERR_SHAPE;
 }
 
-template <int HD>
+template <int HD, int NH>
 static int launch_attention_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& P,
                                int n_qblocks, cudaStream_t stream) {
-  const size_t smem = sizeof(FaSmem<HD>);
-  auto kern = attention_tc_kernel<HD>;
+  const size_t smem = sizeof(FaSmem<HD, NH>);
+  auto kern = attention_tc_kernel<HD, NH>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return launch_pdl(kern, dim3((unsigned)n_qblocks * P.n_kv), FA_THREADS, smem, stream, mq, mk, mv, P);
+  return launch_pdl(kern, dim3((unsigned)n_qblocks * P.n_kv), FA_THREADS(NH), smem, stream, mq, mk, mv, P);
 }
 
 // q: bf16 [tokens][ldq], query heads first (n_q * head_dim values per row are used).
-// k_cache / v_cache: bf16 [n_pages][n_kv][64][head_dim].  Query tiles (qb_*): runs of at most 128 / (n_q / n_kv)
-// consecutive new tokens of one sequence.  head_dim 64 or 128; 128 % (n_q / n_kv) == 0; pages of 64 tokens.
+// k_cache / v_cache: bf16 [n_pages][n_kv][64][head_dim].  Query tiles (qb_*): runs of at most
+// halves * 128 / (n_q / n_kv) consecutive new tokens of one sequence (halves: 1 or 2, see the top of this file).
+// head_dim 64 or 128; 128 % (n_q / n_kv) == 0; pages of 64 tokens.
 STRATUM_EXPORT int stratum_attention_tc(const void* q, int ldq, const void* k_cache, const void* v_cache,
                                         long long n_pages, const int* token_pos, const int* block_table,
                                         int bt_stride, const int* qb_seq, const int* qb_tok0, const int* qb_ntok,
                                         int n_qblocks, void* out, int ldo, int n_tokens, int n_q, int n_kv,
-                                        int head_dim, int page_tokens, int window, float scale, int* status,
-                                        cudaStream_t stream) {
+                                        int head_dim, int page_tokens, int window, float scale, int halves,
+                                        int* status, cudaStream_t stream) {
   if (n_tokens <= 0 || n_qblocks <= 0) return 0;
+  if (halves != 1 && halves != 2) return STRATUM_ERR_SHAPE;
   if (head_dim != 64 && head_dim != 128) return STRATUM_ERR_SHAPE;
   if (n_kv < 1 || n_q % n_kv != 0 || page_tokens != FA_KEYS) return STRATUM_ERR_SHAPE;
   const int gs = n_q / n_kv;
@@ -427,6 +483,10 @@ STRATUM_EXPORT int stratum_attention_tc(const void* q, int ldq, const void* k_ca
   P.out = (bf16*)out; P.ldo = ldo; P.status = status;
   P.n_q = n_q; P.n_kv = n_kv; P.gs = gs; P.tokens_per_tile = R; P.window = window;
   P.scale_log2 = scale * 1.4426950408889634f;
-  if (head_dim == 64) return launch_attention_tc<64>(mq, mk, mv, P, n_qblocks, stream);
-  return launch_attention_tc<128>(mq, mk, mv, P, n_qblocks, stream);
+  if (halves == 2) {
+    if (head_dim == 64) return launch_attention_tc<64, 2>(mq, mk, mv, P, n_qblocks, stream);
+    return launch_attention_tc<128, 2>(mq, mk, mv, P, n_qblocks, stream);
+  }
+  if (head_dim == 64) return launch_attention_tc<64, 1>(mq, mk, mv, P, n_qblocks, stream);
+  return launch_attention_tc<128, 1>(mq, mk, mv, P, n_qblocks, stream);
 }

@@ -498,19 +498,21 @@ def attention_tile(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
 
 def attention_tc(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, token_pos: torch.Tensor,
                  block_table: torch.Tensor, qblocks, out: torch.Tensor, n_q: int, n_kv: int, head_dim: int,
-                 page_tokens: int, window: int, scale: float) -> None:
-    """bfloat16 attention for prompts on tcgen05/TMEM: query tiles of 128 / (n_q / n_kv) tokens (qblocks as for
-    attention_tile).  head_dim 64 or 128, group size dividing 128, pages of 64 tokens."""
+                 page_tokens: int, window: int, scale: float, halves: int = 1) -> None:
+    """bfloat16 attention for prompts on tcgen05/TMEM: query tiles of halves * 128 / (n_q / n_kv) tokens (qblocks
+    as for attention_tile).  halves 2: a CTA owns 256 query rows whose two halves share every key and value tile.
+    head_dim 64 or 128, group size dividing 128, pages of 64 tokens."""
     _need(qkv, "qkv", torch.bfloat16); _need(k_cache, "k_cache", torch.bfloat16)
     _need(v_cache, "v_cache", torch.bfloat16); _need(out, "out", torch.bfloat16)
     _need(block_table, "block_table", torch.int32)
     qs, qt, qn = qblocks
     f = _fn("attention_tc", "stratum_attention_tc",
             [c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-             c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
+             c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
+             c_void_p])
     _check(f(_ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(token_pos),
              _ptr(block_table), block_table.stride(0), _ptr(qs), _ptr(qt), _ptr(qn), qs.numel(), _ptr(out),
-             out.stride(0), qkv.shape[0], n_q, n_kv, head_dim, page_tokens, window, c_float(scale),
+             out.stride(0), qkv.shape[0], n_q, n_kv, head_dim, page_tokens, window, c_float(scale), halves,
              _ptr(status_word()), _stream()), "attention_tc")
 
 

@@ -57,9 +57,12 @@ def run(att, qkv: torch.Tensor, cache, step, out: torch.Tensor) -> None:
                         part_o, part_ml, att.n_heads, att.n_kv_heads, hd, PAGE_TOKENS, att.window, att.scale,
                         n_splits, chunk)
     elif hd in (64, 128) and 128 % gs == 0 and os.environ.get("STRATUM_ATTENTION_TC", "1") != "0":
-        # prompts: the tcgen05 kernel, query tiles of 128 rows (128 / gs tokens)
-        K.attention_tc(qkv, cache.k, cache.v, step.token_pos, cache.block_table, step.query_blocks(128 // gs), out,
-                       att.n_heads, att.n_kv_heads, hd, PAGE_TOKENS, att.window, att.scale)
+        # prompts: the tcgen05 kernel; a CTA owns 256 query rows (2 x 128 / gs tokens) whose two halves share every
+        # key and value tile (STRATUM_ATTENTION_HALVES=1: 128 rows per CTA, two CTAs per SM; measurements)
+        halves = int(os.environ.get("STRATUM_ATTENTION_HALVES", "2"))
+        K.attention_tc(qkv, cache.k, cache.v, step.token_pos, cache.block_table,
+                       step.query_blocks(halves * (128 // gs)), out, att.n_heads, att.n_kv_heads, hd, PAGE_TOKENS,
+                       att.window, att.scale, halves)
     else:
         per_warp = 16 // rows_per_token
         K.attention_tile(qkv, cache.k, cache.v, step.token_pos, step.token_seq, cache.block_table,

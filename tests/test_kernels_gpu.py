@@ -525,10 +525,10 @@ def test_attention_tile_far_key():
     assert rel_err(as64(_run_tile(c, [100, 700], n_q, n_kv, hd)), c["ref"]) < 8e-3
 
 
-def _run_tc(c, n_new, n_q, n_kv, hd, window=0):
+def _run_tc(c, n_new, n_q, n_kv, hd, window=0, halves=1):
     from stratum_b200 import kernels as K
     out = torch.zeros(c["T"], n_q * hd, dtype=torch.bfloat16, device="cuda")
-    per_tile = 128 // (n_q // n_kv)
+    per_tile = halves * (128 // (n_q // n_kv))
     seqs, rows, counts, r = [], [], [], 0
     for i, n in enumerate(n_new):
         for b in range(0, n, per_tile):
@@ -536,24 +536,28 @@ def _run_tc(c, n_new, n_q, n_kv, hd, window=0):
         r += n
     qblocks = tuple(dev(a, torch.int32) for a in (seqs, rows, counts))
     K.attention_tc(c["qkv"], c["kc"], c["vc"], c["pos"], c["table"], qblocks, out, n_q, n_kv, hd, 64, window,
-                   1.0 / math.sqrt(hd))
+                   1.0 / math.sqrt(hd), halves)
     K.check_status()
     return out
 
 
+@pytest.mark.parametrize("halves", [1, 2])
 @pytest.mark.parametrize("n_q,n_kv,hd", [(8, 2, 128), (4, 4, 64), (32, 8, 128), (16, 1, 64), (2, 1, 128)])
-def test_attention_tc_prompts_and_continuations(n_q, n_kv, hd):
+def test_attention_tc_prompts_and_continuations(n_q, n_kv, hd, halves):
+    """halves 2: a CTA's two halves of 128 rows share the key and value tiles; runs that fill one half only, that
+    end inside the second half, and that make the second half walk one tile more than the first."""
     rng = np.random.default_rng(hd + n_q + 2)
-    n_new = [70, 1, 3, 200, 17]
-    c = _attention_case(rng, [0, 130, 63, 200, 0], n_new, n_q, n_kv, hd, "bfloat16")
-    out = _run_tc(c, n_new, n_q, n_kv, hd)
+    n_new = [70, 1, 3, 200, 17, 300]
+    c = _attention_case(rng, [0, 130, 63, 200, 0, 40], n_new, n_q, n_kv, hd, "bfloat16")
+    out = _run_tc(c, n_new, n_q, n_kv, hd, halves=halves)
     assert rel_err(as64(out), c["ref"]) < 8e-3
     W = 100
     c = _attention_case(rng, [250, 0, 5], [60, 140, 1], n_q, n_kv, hd, "bfloat16", window=W)
-    assert rel_err(as64(_run_tc(c, [60, 140, 1], n_q, n_kv, hd, window=W)), c["ref"]) < 8e-3
+    assert rel_err(as64(_run_tc(c, [60, 140, 1], n_q, n_kv, hd, window=W, halves=halves)), c["ref"]) < 8e-3
 
 
-def test_attention_tc_far_key():
+@pytest.mark.parametrize("halves", [1, 2])
+def test_attention_tc_far_key(halves):
     rng = np.random.default_rng(41)
     n_q, n_kv, hd = 4, 2, 64
 
@@ -563,7 +567,7 @@ def test_attention_tc_far_key():
         q[-1, :, :] = d * 12.0
 
     c = _attention_case(rng, [600, 0], [100, 700], n_q, n_kv, hd, "bfloat16", spike=spike)
-    assert rel_err(as64(_run_tc(c, [100, 700], n_q, n_kv, hd)), c["ref"]) < 8e-3
+    assert rel_err(as64(_run_tc(c, [100, 700], n_q, n_kv, hd, halves=halves)), c["ref"]) < 8e-3
 
 
 def _run_stream(c, n_q, n_kv, hd, window=0, pad_rows=0):
