@@ -7,7 +7,8 @@
 Prints ONE JSON line.  `value` is decoded tokens per second at the given batch, with every
 sequence's cache filled to the given context at the end of the timed steps (so the timed steps
 read the longest keys of the run); a "step" is one decode step of the whole batch, timed on the
-device with CUDA events over exactly K steps after W warm-up steps.  `e2e` is the same through
+device with CUDA events over exactly K steps after W warm-up steps (given token ids; every step is launched
+while the one before runs, as generation does, and its picked ids and the kernels' status word are read).  `e2e` is the same through
 the Python entry point (`Stratum.generate`): host token ids in, host token ids out, every step's
 inputs copied from pinned host memory and its picked ids read back.  `prefill` times one prompt
 of 2,048 tokens; `roofline` relates the decode step to the bytes it must read (every weight it
@@ -154,8 +155,15 @@ def time_decode(llm, batch, context, steps, warmup, vocab, rng):
         l0 = kernels.launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
+        # the steps follow one another on the device as they do in generation: each is launched while the one
+        # before runs, and read (picked ids, status word) while the next runs
+        flying = None
         for i in range(warmup, warmup + steps):
-            llm.decode_step(slots, toks[i])
+            h = llm.launch_decode(slots, toks[i])
+            if flying is not None:
+                llm.collect(flying)
+            flying = h
+        llm.collect(flying)
         e1.record()
         torch.cuda.synchronize()
         kernels.check_status()               # a kernel that gave up a wait makes the number worthless: raise

@@ -124,6 +124,22 @@ class Stratum:
         ids, vals, c = self.graphs.step(slots, tokens, sampling.temperature, sampling.top_k, sampling.top_p, uniforms)
         return (ids, vals, c.logits[:len(ids)]) if with_logits else (ids, vals)
 
+    def launch_decode(self, slots: Sequence[int], tokens: Sequence[int],
+                      sampling: SamplingParams = SamplingParams(), streams: Optional[Sequence[Pcg32]] = None):
+        """Start one token for each slot and return a handle without waiting for the result; `collect(handle)`
+        gives (ids, logits of the ids).  The sequences' lengths are advanced at once, so the next step may be
+        launched before this one is collected (replayed graphs only).  Collect in the order of the launches, and
+        keep at most two steps in flight."""
+        if self.graphs is None:
+            raise RuntimeError("launch_decode needs replayed graphs (use_graphs=True)")
+        uniforms = None if sampling.greedy else [st.uniform() for st in streams]
+        return self.graphs.launch(slots, tokens, sampling.temperature, sampling.top_k, sampling.top_p, uniforms,
+                                  advance_now=True)
+
+    def collect(self, handle):
+        ids, vals, _ = self.graphs.collect(handle)
+        return ids, vals
+
     # -- generation ---------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens=16, stop_ids: Optional[Sequence[int]] = None,
                  sampling: SamplingParams = SamplingParams(), max_batch: Optional[int] = None,
