@@ -17,9 +17,12 @@ leaves the cache of rows with sequence index -1 alone (their state row is the sp
 A graph is specific to (rows, page-table width, greedy or sampling): rows is the batch padded up a little (padding
 rows carry sequence index -1, which every kernel that touches the cache skips; rows never mix, so
 padding changes no result), and the width is the next power of two of the pages the longest
-sequence holds, which also fixes how the keys are split across warps.  The reference queues its
-decode steps on the GPU ahead of time for the same reason
-(stratum/native/stratum_arch_llama.inc.c:1994-2038).
+sequence holds, which also fixes how the keys are split across warps.
+
+A step is `launch` + `collect`.  A caller that launches the next step before it collects this one (the
+generation loop does) lets that step take the picked ids on the device, through a small kernel in front of the
+replay, so the GPU goes from one step to the next without waiting for the host: the reference queues its decode
+steps on the GPU ahead of time for the same reason (stratum/native/stratum_arch_llama.inc.c:1992-2038).
 """
 from __future__ import annotations
 
