@@ -76,3 +76,54 @@ def test_attention_rules(recorded):
     assert _attention_call(recorded, bf, 128, 32, 8, 300, False)[0] == "attention_tc"
     assert _attention_call(recorded, bf, 128, 3, 1, 300, False)[0] == "attention_tile"       # 128 % 3 != 0
     assert _attention_call(recorded, bf, 96, 8, 2, 300, False)[0] == "attention_tile"
+
+
+def test_extra_epilogue_rules(recorded, monkeypatch):
+    """Where a product carries more than its basic epilogue: rows of a handed-over norm and the query/key/value
+    epilogue go to the tensor-core kernel or are refused; a Handover is honoured from HANDOVER_MIN_ROWS rows on,
+    where the tensor-core kernel takes the product anyway; prompt attention gets query tiles of 256 rows."""
+    from stratum_b200 import kernels as K
+    from stratum_b200.parts import gemm_dispatch as G
+    from stratum_b200.parts.base import Handover, NormedRows, Runtime
+    from stratum_b200.parts.linear import ADD_TO_F32, STORE, Linear
+    small = (4096, 4096)
+    x, w, out = _xw(4, *small)
+    assert not G.takes_tensor_cores(x, w, extras=False) and G.takes_tensor_cores(x, w, extras=True)
+    G.run(x, w, None, out, G.STORE, extra=object())               # few rows, small matrix: still the tensor cores
+    assert [c[0] for c in recorded] == ["gemm_tc"]
+    with pytest.raises(K.KernelError, match="only the tensor-core kernel"):
+        G.run(*_xw(4, 64, 20)[:2], None, torch.zeros(4, 64, dtype=torch.bfloat16), G.STORE, extra=object())
+    # Linear: the residual add honours a Handover only with enough rows
+    monkeypatch.setattr(K, "_need", lambda *a, **k: None)        # (the tensors of this test live on the host)
+    monkeypatch.setattr(K, "gemm_tc", lambda *a, **k: (recorded.append(("gemm_tc", a, k)), 7)[1])
+    rt = types.SimpleNamespace(dtype=torch.bfloat16, device="cpu",
+                               empty=lambda *shape, dtype=torch.bfloat16: torch.zeros(shape, dtype=dtype))
+    lin = Linear(rt, torch.zeros(4096, 4096, dtype=torch.bfloat16))
+    gain = torch.ones(4096)
+    for rows, honoured in ((G.HANDOVER_MIN_ROWS - 1, False), (G.HANDOVER_MIN_ROWS, True)):
+        recorded.clear()
+        ask = Handover(gain, 4096, 1e-5)
+        lin(torch.zeros(rows, 4096, dtype=torch.bfloat16), out=torch.zeros(rows, 4096), mode=ADD_TO_F32, emit=ask)
+        assert (ask.result is not None) == honoured
+        assert [c[0] for c in recorded] == ["gemm_tc"]
+        assert recorded[0][1][4] == (K.EPI_ADD_F32_EMIT if honoured else K.EPI_ADD_F32)
+        if honoured:
+            r = ask.result
+            assert isinstance(r, NormedRows) and r.parts == 7 and r.x.shape == (rows, 4096) and r.size == 4096
+            # and the product behind the norm takes them as rows to be scaled
+            recorded.clear()
+            lin(r, mode=STORE)
+            assert recorded[0][1][4] == K.EPI_STORE and recorded[0][1][5].c.norm_parts == 7
+    # prompt attention: a CTA's query tile is 256 rows (2 x 128 / group size tokens), 128 when asked for
+    from stratum_b200.parts import attention_dispatch as A
+    sizes = []
+    att = types.SimpleNamespace(head_dim=128, n_heads=32, n_kv_heads=8, window=0, scale=1.0, runtime=None)
+    step = types.SimpleNamespace(all_single=False, n_tokens=300, max_len=300, token_pos=None, token_seq=None,
+                                 query_blocks=lambda n: sizes.append(n))
+    cache = types.SimpleNamespace(k=None, v=None, block_table=None)
+    for env, tokens in ((None, 64), ("1", 32)):
+        if env:
+            monkeypatch.setenv("STRATUM_ATTENTION_HALVES", env)
+        recorded.clear()
+        A.run(att, torch.zeros(300, 48 * 128, dtype=torch.bfloat16), cache, step, torch.zeros(300, 4096, dtype=torch.bfloat16))
+        assert recorded[0][0] == "attention_tc" and sizes[-1] == tokens
