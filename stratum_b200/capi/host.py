@@ -45,7 +45,7 @@ def close_model(handle: int) -> int:
 
 
 def vocab(handle: int) -> int:
-    return int(_get(handle).config.vocab_size)
+    return int(_get(handle).engine.vocab)
 
 
 def slot_acquire(handle: int) -> int:
