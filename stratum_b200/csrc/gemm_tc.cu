@@ -30,6 +30,8 @@
 #define TC_THREADS 192
 
 static int g_last_launches = 0;       // kernels the last stratum_gemm_tc call launched (for launch counting)
+static int g_last_form = 0;           // and the form it took: 1 tiles, 2 tiles on pairs of CTAs, 3 stream-K,
+                                      // 4 + 16 * cluster size: k shared inside clusters (for tests)
 
 // Work an epilogue may do beyond its basic form.  Every part is off while its pointer is null.
 //
@@ -991,10 +993,10 @@ gemm_tc_streamk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
 
 // ---------------------------------------------------------------- few rows of x, N small: k shared inside a cluster
 // Where W has no more tiles of 128 rows than there are SMs, a cluster of CS CTAs takes one tile and cuts k into
-// CS stretches, one per CTA.  Each CTA sums its stretch in tensor memory; the CTAs of ranks 1.. write their float32
-// partial tile into the shared memory of rank 0 (into its ring, idle by then), and rank 0 adds them in the order
-// of the ranks, which is the order of k, and runs the epilogue.  One launch, no scratch in global memory; the cut
-// depends only on the shapes, so a row's result does not depend on its batch.
+// CS stretches, one per CTA.  Each CTA sums its stretch in tensor memory; the rows of x are then dealt out to the
+// ranks, every CTA writes its float32 partial sums of a rank's rows into that rank's shared memory (into its ring,
+// idle by then), and every rank adds what it got in the order of the ranks, which is the order of k, and runs the
+// epilogue for its rows.  One launch, no scratch in global memory; the cut depends only on the shapes.
 __device__ __forceinline__ uint32_t cluster_nctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
@@ -1112,36 +1114,55 @@ gemm_tc_clusterk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   }
   // Every thread of the cluster meets here twice, whatever happened above (a wait that ran out leaves its mark in
   // the status word and the CTA goes on with what it has).  After the first meeting every CTA's products have been
-  // read out of tensor memory and its ring is idle; after the second the partial tiles are in rank 0.
+  // read out of tensor memory and its ring is idle; between the two, the rows of x are dealt out in chunks of CWS
+  // to the ranks (chunk c to rank c % CS) and every CTA writes its partial sums of a chunk into the ring of the
+  // chunk's rank; after the second, every rank adds what it was given in the order of the ranks, which is the order
+  // of k, and runs the epilogue for its rows: the adding and storing is spread over the cluster.
+  constexpr int CWS = BN >= 32 ? 8 : 4;
+  constexpr int NCH = BN / CWS;
+  const int live = (P.M + CWS - 1) / CWS < NCH ? (P.M + CWS - 1) / CWS : NCH;   // chunks that hold rows of x
+  const int row = (warp & 3) * 32 + lane;
   __syncwarp();
   cluster_sync_all();
-  float* part = reinterpret_cast<float*>(S.a);      // rank 0's ring: [rank - 1][BN][128] float32
-  if (warp >= 2 && rank > 0) {
-    const int row = (warp & 3) * 32 + lane;
-    const uint32_t dst = cluster_map(part + (size_t)(rank - 1) * BN * TC_BM + row, 0);
+  float* part = reinterpret_cast<float*>(S.a);      // this CTA's ring: [its chunks][source rank][CWS][128] float32
+  if (warp >= 2) {
 #pragma unroll
-    for (int j = 0; j < BN; j++) st_cluster_f32(dst + (uint32_t)(j * TC_BM * sizeof(float)), v[j]);
+    for (int c = 0; c < NCH; c++) {
+      if (c < live) {
+        const int owner = c % CS, slot = c / CS;
+        float* mine = part + (size_t)(slot * CS + rank) * CWS * TC_BM + row;
+        if (owner == rank) {
+#pragma unroll
+          for (int j = 0; j < CWS; j++) mine[j * TC_BM] = v[c * CWS + j];
+        } else {
+          const uint32_t dst = cluster_map(mine, (uint32_t)owner);
+#pragma unroll
+          for (int j = 0; j < CWS; j++) st_cluster_f32(dst + (uint32_t)(j * TC_BM * sizeof(float)), v[c * CWS + j]);
+        }
+      }
+    }
   }
   cluster_sync_all();
-  if (warp >= 2 && rank == 0) {
-    const int row = (warp & 3) * 32 + lane;
-    for (int r = 1; r < CS; r++) {
-      const float* src = part + (size_t)(r - 1) * BN * TC_BM + row;
-#pragma unroll
-      for (int j = 0; j < BN; j++) v[j] += src[j * TC_BM];
-    }
+  if (warp >= 2) {
     const int n = tile * TC_BM + row;
+    for (int c = rank, slot = 0; c < live; c += CS, slot++) {
+      float o[CWS];
 #pragma unroll
-    for (int c0 = 0; c0 < BN; c0 += CW) {
-      float o[CW];
+      for (int j = 0; j < CWS; j++) o[j] = 0.0f;
+      for (int r = 0; r < CS; r++) {
+        const float* src = part + (size_t)(slot * CS + r) * CWS * TC_BM + row;
 #pragma unroll
-      for (int j = 0; j < CW; j++) o[j] = v[c0 + j];
-      sk_store<EPI, CW, XT>(P, S.tab, n, c0, o);
-      if (EPI == 4) sk_emit_squares<CW>(S.tab, warp & 3, lane, c0, o);
+        for (int j = 0; j < CWS; j++) o[j] += src[j * TC_BM];
+      }
+      sk_store<EPI, CWS, XT>(P, S.tab, n, c * CWS, o);
+      if (EPI == 4) sk_emit_squares<CWS>(S.tab, warp & 3, lane, c * CWS, o);
     }
   }
   __syncthreads();
-  if (EPI == 4 && rank == 0 && warp >= 2) sk_emit_sums(P, S.tab, tile, threadIdx.x - 64);
+  if (EPI == 4 && warp >= 2) {                      // each rank the sums of the rows it stored
+    const int t = threadIdx.x - 64;
+    if (t < P.M && (t / CWS) % CS == rank) sk_emit_sums(P, S.tab, tile, t);
+  }
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
@@ -1267,7 +1288,7 @@ static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, TcParams P, 
     const int pairs = n_tiles < max_pairs ? n_tiles : max_pairs;                                            \
     const int st = launch_pdl(kern, 2 * pairs, TC_THREADS, smem, stream, ma, mb, P);                        \
     if (st != 0) return st;                                                                                 \
-    g_last_launches = 1;                                                                                    \
+    g_last_launches = 1; g_last_form = 2;                                                                   \
   }
   switch (epilogue) {
     case 0: TC2_LAUNCH(0) break;
@@ -1337,7 +1358,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TcParams P, i
     }                                                                                                       \
     int st = launch_pdl(kern, grid, TC_THREADS, smem, stream, ma, mb, P);                                   \
     if (st != 0) return st;                                                                                 \
-    g_last_launches = P.split ? 2 : 1;                                                                      \
+    g_last_launches = P.split ? 2 : 1; g_last_form = 1;                                                     \
     if (P.split) {                                                                                          \
       st = launch_pdl(gemm_tc_pieces_kernel<BN, E>, dim3(left, 4 * (BN / 64)), 256, 0, stream, P, grid,              \
                       n_tiles, n_kb, tiles_a);                                                              \
@@ -1482,15 +1503,28 @@ static int clusterk_resident(int cs) {
   return cached[cs];
 }
 
-// The cluster size with which `tiles` clusters fill most SMs in one wave, or 0 if there is none: the partial tiles
-// must fit into rank 0's ring, every rank needs a k-block, and all clusters must be resident together.
+// The cluster size with which `tiles` clusters fill most SMs in one wave, or 0 if there is none: every rank needs a
+// k-block, and all clusters must be resident together.  (What the ranks exchange always fits a ring: at most
+// BN / CWS + 7 chunks of CWS x 128 float32, 60 KB.)
+// A rank's stretch must be CLUSTERK_MIN_KB k-blocks or more, and a "cluster" of one CTA (a whole tile's k per CTA,
+// on fewer SMs than stream-K uses) is not taken.  Measured in whole decode steps: a cluster launch does not start
+// as early behind its predecessor as a plain one, which a second pass saved pays for only where the product is
+// long enough.  Llama-3.2-1B shape (QKV 5 k-blocks a rank, gate|up one CTA a tile): with both 0.965 / 1.158 ms
+// at 8 / 16 rows, with neither 0.927 / 1.071; Llama-3.1-8B and Llama-2-7B shapes (16 to 56 k-blocks a rank) are
+// ahead with the cluster form up to about 40 rows (8B: 5.35 against 5.53 ms at 24 rows, 6.10 against 6.24 at 32,
+// level from 48 on; at 3.93 ms for 8 rows against 4.02 without).
+#ifndef CLUSTERK_MIN_KB
+#define CLUSTERK_MIN_KB 16
+#define CLUSTERK_MIN_CS 2
+#endif
 template <int BN, int STAGES, int EPI, bool XT>
 static int clusterk_size(int tiles, int n_kb) {
   const int sms = sm_count();
   if (tiles > sms) return 0;
   for (int cs = sms / tiles > 8 ? 8 : sms / tiles; cs >= 1; cs--) {
     if (tiles * cs * 10 < sms * 8) break;                       // too few SMs at work: the even split is better
-    if (cs > n_kb || (size_t)(cs - 1) * BN * TC_BM * sizeof(float) > (size_t)STAGES * TC_BM * TC_BK * sizeof(bf16)) continue;
+    if (cs > n_kb) continue;                                    // (every rank needs a k-block)
+    if (cs < CLUSTERK_MIN_CS || n_kb / cs < CLUSTERK_MIN_KB) return 0;
     if (clusterk_resident<BN, STAGES, EPI, XT>(cs) >= tiles) return cs;
   }
   return 0;
@@ -1520,16 +1554,22 @@ static int launch_clusterk(const CUtensorMap& mw, const CUtensorMap& mx, const S
   attr[1].val.clusterDim.x = cs; attr[1].val.clusterDim.y = 1; attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  g_last_launches = 1;
+  g_last_launches = 1; g_last_form = 4 + 16 * cs;
   return (int)cudaLaunchKernelEx(&cfg, gemm_tc_clusterk_kernel<BN, STAGES, EPI, XT>, mw, mx, P);
 }
 
-// The cluster form up to this many (padded) rows of x.  Measured in whole decode steps on the Llama-8B shapes: ahead
-// at 16 rows (4.63 against 4.79 ms), behind at 32 and 64 (6.40 against 6.28, 9.48 against 9.19 ms), where rank 0
-// alone adds and stores a tile that is two and four times as wide.
+// The cluster form up to this many (padded) rows of x (STRATUM_GEMM_CLUSTERK_ROWS overrides, for measurements).
 #ifndef CLUSTERK_MAX_BN
-#define CLUSTERK_MAX_BN 16
+#define CLUSTERK_MAX_BN 64
 #endif
+static int clusterk_max_rows() {
+  static int rows = -1;
+  if (rows < 0) {
+    const char* e = getenv("STRATUM_GEMM_CLUSTERK_ROWS");
+    rows = e ? atoi(e) : CLUSTERK_MAX_BN;
+  }
+  return rows;
+}
 
 #ifndef SK_RING_16
 #define SK_RING_16 10
@@ -1547,8 +1587,8 @@ static int launch_streamk(const CUtensorMap& mw, const CUtensorMap& mx, const Sk
   const bool split_tiles = !(P.tiles % grid == 0);
 #define SK_LAUNCH_X(E, XT)                                                                                  \
   {                                                                                                         \
-    if constexpr (BN <= CLUSTERK_MAX_BN) {                                                                  \
-      if (split_tiles && clusterk_enabled()) {                                                              \
+    if constexpr (BN <= 64) {                                                                               \
+      if (split_tiles && clusterk_enabled() && BN <= clusterk_max_rows()) {                                   \
         const int cs = clusterk_size<BN, STAGES, E, XT>(P.tiles, P.n_kb);                                   \
         if (cs > 0) return launch_clusterk<BN, STAGES, E, XT>(mw, mx, P, cs, stream);                       \
       }                                                                                                     \
@@ -1561,7 +1601,7 @@ static int launch_streamk(const CUtensorMap& mw, const CUtensorMap& mx, const Sk
       configured = true;                                                                                    \
     }                                                                                                       \
     int st = launch_pdl(kern, grid, TC_THREADS, smem, stream, mw, mx, P);                                   \
-    g_last_launches = split_tiles ? 2 : 1;                                                                  \
+    g_last_launches = split_tiles ? 2 : 1; g_last_form = 3;                                                 \
     if (st != 0 || !split_tiles) return st;                                                                 \
     return launch_pdl(gemm_tc_fixup_kernel<BN, E, XT>, dim3(grid - 1, (P.M + 3) / 4), 128, 0, stream, P, grid); \
   }
@@ -1583,6 +1623,7 @@ static int launch_streamk(const CUtensorMap& mw, const CUtensorMap& mx, const Sk
 }
 
 STRATUM_EXPORT int stratum_gemm_tc_last_launches(void) { return g_last_launches; }
+STRATUM_EXPORT int stratum_gemm_tc_last_form(void) { return g_last_form; }
 
 // Scratch for partial tiles (two 128 x 256 float32 tiles per SM cover both forms).
 STRATUM_EXPORT long long stratum_gemm_tc_scratch_floats(void) { return (long long)sm_count() * 2 * 256 * TC_BM; }

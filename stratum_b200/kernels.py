@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import c_float, c_int, c_size_t, c_uint64, c_void_p
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -425,6 +425,12 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
            "gemm_tc")
     count_launches(lib.stratum_gemm_tc_last_launches() - 1)      # a second pass, if there was one
     return int(lib.stratum_gemm_tc_last_parts()) if epilogue == EPI_ADD_F32_EMIT else 0
+
+
+def gemm_tc_last_form() -> Tuple[str, int]:
+    """The form the last gemm_tc call took, for tests: ("tiles" | "pairs" | "stream-k" | "cluster-k", cluster size)."""
+    code = int(build.load("gemm_tc").stratum_gemm_tc_last_form())
+    return {1: "tiles", 2: "pairs", 3: "stream-k", 4: "cluster-k"}.get(code % 16, "none"), code // 16
 
 
 # ------------------------------------------------------------------ attention (any sizes, CUDA cores)

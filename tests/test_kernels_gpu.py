@@ -158,6 +158,12 @@ def test_gemm_skinny(M, N, K_):
     assert torch.equal(one[0], out32[M - 1])
 
 
+# shapes of test_gemm_tc that take the cluster form on 148 SMs (clusters of 4, 3, 5, 5, 2, 4 and 4 CTAs when this
+# was written; how many clusters of a size fit at once is the driver's answer)
+CLUSTER_FORMS = {(8, 4096, 4096), (40, 4096, 4096 + 72), (30, 5000, 3080), (24, 3072, 6144), (13, 3000, 6152),
+                 (64, 8192 + 8, 2048 + 16), (17, 4096, 14336), (64, 4096 + 64, 14336)}
+
+
 @pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (33, 48, 64), (64, 1000, 200), (100, 256, 4096), (300, 4096 + 16, 512),
                                      (2048, 2 * 177, 96), (129, 6144, 1024), (1, 128, 128), (17, 130, 72),
                                      (8, 4096, 4096), (5, 28672, 1024), (64, 4096 + 64, 14336), (16, 6144, 4096),
@@ -171,9 +177,13 @@ def test_gemm_skinny(M, N, K_):
                                      # pairs of CTAs on 256 x 256 tiles: rows and columns that end inside a tile, more
                                      # tiles than pairs of SMs, one row of tiles
                                      (1000, 2100, 264), (256, 28672, 128), (2304, 9000, 72),
-                                     # few rows, no more tiles than SMs: k shared inside clusters of 4, 3, 8 and 1 CTAs
-                                     (40, 4096, 2048), (30, 5120, 1000), (3, 2304, 1032), (8, 16000, 520)])
+                                     # few rows, no more tiles than SMs: too little k for clusters to share
+                                     (40, 4096, 2048), (30, 5120, 1000), (3, 2304, 1032), (8, 16000, 520),
+                                     # k shared inside clusters, rows dealt out to the ranks
+                                     (40, 4096, 4096 + 72), (30, 5000, 3080), (24, 3072, 6144), (13, 3000, 6152),
+                                     (64, 8192 + 8, 2048 + 16), (17, 4096, 14336)])
 def test_gemm_tc(M, N, K_):
+    """(The forms the few-row cases take on 148 SMs are checked too; see CLUSTER_FORMS.)"""
     from stratum_b200 import kernels as K
     rng = np.random.default_rng(M + N + K_)
     x = dev(rng.standard_normal((M, K_)), torch.bfloat16)
@@ -184,6 +194,11 @@ def test_gemm_tc(M, N, K_):
     K.gemm_tc(x, w, b, out32, K.EPI_STORE_F32)
     K.check_status()
     assert rel_err(as64(out32), ref) < 2e-5
+    if (M, N, K_) in CLUSTER_FORMS:
+        form, size = K.gemm_tc_last_form()
+        assert form == "cluster-k" and 2 <= size <= 8
+    elif M <= 64:
+        assert K.gemm_tc_last_form()[0] == "stream-k"
     out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
     K.gemm_tc(x, w, b, out, K.EPI_STORE)
     assert rel_err(as64(out), ref) < 6e-3
