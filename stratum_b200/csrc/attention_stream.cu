@@ -22,12 +22,12 @@
 //
 // Every mbarrier wait is bounded (see gemm_tc.cu): on expiry a code goes to the status word and the CTA winds down.
 #include <math.h>
+#include <stdlib.h>
 
 #include "mma_common.cuh"
 #include "tc_common.cuh"
 
 #define SA_KEYS 64
-#define SA_THREADS 160
 #define SA_MAX_SEQS 1024
 #define SA_MAX_GS 8
 
@@ -44,19 +44,29 @@ struct SaParams {
   int late_trigger;
 };
 
-template <int CH>
+template <int CH, int NW>
 struct SaSmem {
   static constexpr int HD = 32 * CH;
   static constexpr int STAGE = SA_KEYS * HD;    // elements of one K (or V) page
   static constexpr int STAGES = (160 * 1024) / (2 * STAGE * 2);
   alignas(1024) bf16 k[STAGES][STAGE];          // [Hd/64 boxes][64 keys][64 dims]
   alignas(1024) bf16 v[STAGES][STAGE];
-  float mo[4][SA_MAX_GS][HD];                   // the four warps' outputs, maxima and sums at the end of a run
-  float mm[4][SA_MAX_GS], ml[4][SA_MAX_GS];
+  float mo[NW][SA_MAX_GS][HD];                  // the consumer warps' outputs, maxima and sums at the end of a run
+  float mm[NW][SA_MAX_GS], ml[NW][SA_MAX_GS];
   int pre[SA_MAX_SEQS + 1];                     // pages before sequence b (per kv head)
   uint64_t full[STAGES], empty[STAGES];
+  uint32_t seen[STAGES];                        // whole pages per warp: fillings of the stage that a warp has seen complete
   int abort_flag;
 };
+
+__device__ __forceinline__ uint32_t ld_acquire_shared(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_shared(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(p)), "r"(v) : "memory");
+}
 
 struct SaSeq {                                  // the keys sequence b attends to, in pages
   int pos, lo, first, n;
@@ -102,13 +112,15 @@ struct SaCursor {
   }
 };
 
-template <int CH>
-__global__ void __launch_bounds__(SA_THREADS, 1)
+template <int CH, bool WP, int NW>
+__global__ void __launch_bounds__(32 + 32 * NW, 1)
 attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                         const SaParams P) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  using Smem = SaSmem<CH>;
+  using Smem = SaSmem<CH, NW>;
   constexpr int HD = Smem::HD, STAGES = Smem::STAGES, DB = HD / 64;
+  static_assert(WP || NW == 4, "a quarter of a page per warp needs four consumer warps");
+  static_assert(!WP || NW <= STAGES, "whole pages per warp: more consumer warps than ring stages would only wait");
   Smem& S = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = gridDim.x, c = blockIdx.x;
@@ -116,12 +128,12 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
   // head start is worth; measured)
   volatile int* abort_flag = &S.abort_flag;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; s++) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], 4); }
+    for (int s = 0; s < STAGES; s++) { mbar_init(&S.full[s], 1); mbar_init(&S.empty[s], WP ? 1 : NW); S.seen[s] = 0; }
     S.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   // pages per sequence (positions and the batch are the step's description, not the work of an earlier kernel)
-  for (int b = threadIdx.x; b < P.n_seqs; b += SA_THREADS) S.pre[b + 1] = sa_seq(P, b).n;
+  for (int b = threadIdx.x; b < P.n_seqs; b += 32 + 32 * NW) S.pre[b + 1] = sa_seq(P, b).n;
   if (threadIdx.x == 0) S.pre[0] = 0;
   __syncthreads();
   if (warp == 0) {                               // running sum, 32 sequences at a time
@@ -211,74 +223,169 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     bool to_end = false;
     while (u < u1 && cur.b == b && cur.kvh == kvh) {
       const int s = it % STAGES;
-      // (the lanes of a warp go on or give up together)
-      if (!__all_sync(0xffffffffu, mbar_wait(&S.full[s], (it / STAGES) & 1, abort_flag))) {
-        if (lane == 0) { atomicCAS(P.status, 0, 302); S.abort_flag = 1; }
-        ok = false;
-        break;
-      }
-      const int key0 = cur.page * SA_KEYS + 16 * w;
-      to_end = cur.page == sq.first + sq.n - 1;
-      if (key0 <= sq.pos && key0 + 15 >= sq.lo) {  // (a page's last 16-key blocks may lie beyond the newest key)
-        // 16-byte fragments at the swizzled address of (row, 8 dims): box = dims / 64, chunk ^ (row & 7)
-        const uint8_t* kb_ = reinterpret_cast<const uint8_t*>(S.k[s]);
-        const uint8_t* vb_ = reinterpret_cast<const uint8_t*>(S.v[s]);
-        const int r0 = 16 * w + g;               // rows r0 and r0 + 8; both have (row & 7) == g
-        uint4 ka[CH], kb[CH], va[CH], vb[CH];
+      if constexpr (WP) {
+        // a warp takes every fourth page whole: the scores of its 64 keys first, one maximum and one rescaling of
+        // the sums per page, then the products with V; the four warps work on four pages at a time
+        to_end = cur.page == sq.first + sq.n - 1;
+        if ((int)(it % NW) == w) {
+          // A wait can tell a barrier's current phase from the one before only, and the filling of this stage
+          // before this one was another warp's page: until that warp has seen its filling complete, a wait for
+          // this one would take the filling before that for its own.  So that warp says so (S.seen), and this
+          // one waits for its word first.  (The word comes before that warp frees the stage, so before this
+          // filling can even be asked for: nothing here waits for anything that is not older than itself.)
+          const uint32_t fill = it / STAGES;
+          bool seen = false;
+          for (uint32_t i = 0; i < TC_SPIN_LIMIT && !seen; i++) {
+            seen = ld_acquire_shared(&S.seen[s]) >= fill;
+            if ((i & 1023u) == 1023u && *abort_flag) break;
+          }
+          if (!__all_sync(0xffffffffu, seen && mbar_wait(&S.full[s], fill & 1, abort_flag))) {
+            if (lane == 0) { atomicCAS(P.status, 0, 302); S.abort_flag = 1; }
+            ok = false;
+            break;
+          }
+          __syncwarp();
+          if (lane == 0) st_release_shared(&S.seen[s], fill + 1);
+          const uint8_t* kb_ = reinterpret_cast<const uint8_t*>(S.k[s]);
+          const uint8_t* vb_ = reinterpret_cast<const uint8_t*>(S.v[s]);
+          const int pk0 = cur.page * SA_KEYS;
+          float sc[4][4];
 #pragma unroll
-        for (int ch = 0; ch < CH; ch++) {
-          const int off = (ch >> 1) * (SA_KEYS * 128) + (((((ch & 1) << 2) | t) ^ g) << 4);
-          ka[ch] = *reinterpret_cast<const uint4*>(kb_ + off + r0 * 128);
-          kb[ch] = *reinterpret_cast<const uint4*>(kb_ + off + (r0 + 8) * 128);
-          va[ch] = *reinterpret_cast<const uint4*>(vb_ + off + r0 * 128);
-          vb[ch] = *reinterpret_cast<const uint4*>(vb_ + off + (r0 + 8) * 128);
+          for (int blk = 0; blk < 4; blk++) {
+            const int key0 = pk0 + 16 * blk;
+            sc[blk][0] = sc[blk][1] = sc[blk][2] = sc[blk][3] = 0.f;
+            if (key0 <= sq.pos && key0 + 15 >= sq.lo) {   // (a page's last blocks may lie beyond the newest key)
+              const int r0 = 16 * blk + g;            // rows r0 and r0 + 8; both have (row & 7) == g
+#pragma unroll
+              for (int ch = 0; ch < CH; ch++) {
+                const int off = (ch >> 1) * (SA_KEYS * 128) + (((((ch & 1) << 2) | t) ^ g) << 4);
+                const uint4 ka = *reinterpret_cast<const uint4*>(kb_ + off + r0 * 128);
+                const uint4 kb = *reinterpret_cast<const uint4*>(kb_ + off + (r0 + 8) * 128);
+                mma16816(sc[blk], ka.x, kb.x, ka.y, kb.y, qv[ch].x, qv[ch].y);
+                mma16816(sc[blk], ka.z, kb.z, ka.w, kb.w, qv[ch].z, qv[ch].w);
+              }
+            }
+            const bool ok0 = key0 + g <= sq.pos && key0 + g >= sq.lo;
+            const bool ok1 = key0 + g + 8 <= sq.pos && key0 + g + 8 >= sq.lo;
+            sc[blk][0] = ok0 ? sc[blk][0] * P.scale : -INFINITY; sc[blk][1] = ok0 ? sc[blk][1] * P.scale : -INFINITY;
+            sc[blk][2] = ok1 ? sc[blk][2] * P.scale : -INFINITY; sc[blk][3] = ok1 ? sc[blk][3] * P.scale : -INFINITY;
+          }
+          float bm[2], corr[2], m_use[2];
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            bm[e] = fmaxf(fmaxf(fmaxf(sc[0][e], sc[0][2 + e]), fmaxf(sc[1][e], sc[1][2 + e])),
+                          fmaxf(fmaxf(sc[2][e], sc[2][2 + e]), fmaxf(sc[3][e], sc[3][2 + e])));
+            bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 4));
+            bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 8));
+            bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 16));
+            const float m_new = fmaxf(m_run[e], bm[e]);
+            m_use[e] = (m_new == -INFINITY) ? 0.f : m_new;
+            corr[e] = __expf(m_run[e] - m_use[e]);
+            m_run[e] = m_new;
+            l_run[e] *= corr[e];
+          }
+#pragma unroll
+          for (int i = 0; i < 2 * CH; i++) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[1]; o[i][2] *= corr[0]; o[i][3] *= corr[1];
+          }
+#pragma unroll
+          for (int blk = 0; blk < 4; blk++) {
+            const int key0 = pk0 + 16 * blk;
+            if (key0 <= sq.pos && key0 + 15 >= sq.lo) {
+              const float p0 = __expf(sc[blk][0] - m_use[0]), p1 = __expf(sc[blk][1] - m_use[1]);
+              const float p2 = __expf(sc[blk][2] - m_use[0]), p3 = __expf(sc[blk][3] - m_use[1]);
+              l_run[0] += p0 + p2;
+              l_run[1] += p1 + p3;
+              // P^T as the B operand: (keys 2t, 2t+1; head g) and (keys 2t+8, 2t+9; head g)
+              const uint32_t pb0 = transpose8x8(pack_bf16(p0, p1)), pb1 = transpose8x8(pack_bf16(p2, p3));
+              const int r0 = 16 * blk + g;
+#pragma unroll
+              for (int ch = 0; ch < CH; ch++) {
+                const int off = (ch >> 1) * (SA_KEYS * 128) + (((((ch & 1) << 2) | t) ^ g) << 4);
+                const uint4 va = *reinterpret_cast<const uint4*>(vb_ + off + r0 * 128);
+                const uint4 vb = *reinterpret_cast<const uint4*>(vb_ + off + (r0 + 8) * 128);
+#pragma unroll
+                for (int ii = 0; ii < 2; ii++) {
+                  const uint32_t a0 = transpose8x8(reg_of(va, 2 * ii)), a1 = transpose8x8(reg_of(va, 2 * ii + 1));
+                  const uint32_t a2 = transpose8x8(reg_of(vb, 2 * ii)), a3 = transpose8x8(reg_of(vb, 2 * ii + 1));
+                  mma16816(o[2 * ch + ii], a0, a1, a2, a3, pb0, pb1);
+                }
+              }
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&S.empty[s]);   // the stage has been read
         }
-        // S^T: [0],[1] = (key g, heads 2t, 2t+1); [2],[3] = (key g+8, same heads)
-        float sc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int ch = 0; ch < CH; ch++) {
-          mma16816(sc, ka[ch].x, kb[ch].x, ka[ch].y, kb[ch].y, qv[ch].x, qv[ch].y);
-          mma16816(sc, ka[ch].z, kb[ch].z, ka[ch].w, kb[ch].w, qv[ch].z, qv[ch].w);
+      } else {
+        // (the lanes of a warp go on or give up together)
+        if (!__all_sync(0xffffffffu, mbar_wait(&S.full[s], (it / STAGES) & 1, abort_flag))) {
+          if (lane == 0) { atomicCAS(P.status, 0, 302); S.abort_flag = 1; }
+          ok = false;
+          break;
         }
-        const bool ok0 = key0 + g <= sq.pos && key0 + g >= sq.lo;
-        const bool ok1 = key0 + g + 8 <= sq.pos && key0 + g + 8 >= sq.lo;
-        sc[0] = ok0 ? sc[0] * P.scale : -INFINITY; sc[1] = ok0 ? sc[1] * P.scale : -INFINITY;
-        sc[2] = ok1 ? sc[2] * P.scale : -INFINITY; sc[3] = ok1 ? sc[3] * P.scale : -INFINITY;
-        // maximum per head over the block's 16 keys: this lane's two keys, then across g (lanes 4, 8, 16 apart)
-        float bm[2] = {fmaxf(sc[0], sc[2]), fmaxf(sc[1], sc[3])};
-        float corr[2], m_use[2];
-#pragma unroll
-        for (int e = 0; e < 2; e++) {
-          bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 4));
-          bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 8));
-          bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 16));
-          const float m_new = fmaxf(m_run[e], bm[e]);
-          m_use[e] = (m_new == -INFINITY) ? 0.f : m_new;
-          corr[e] = __expf(m_run[e] - m_use[e]);
-          m_run[e] = m_new;
-        }
-        const float p0 = __expf(sc[0] - m_use[0]), p1 = __expf(sc[1] - m_use[1]);
-        const float p2 = __expf(sc[2] - m_use[0]), p3 = __expf(sc[3] - m_use[1]);
-        l_run[0] = l_run[0] * corr[0] + p0 + p2;
-        l_run[1] = l_run[1] * corr[1] + p1 + p3;
-#pragma unroll
-        for (int i = 0; i < 2 * CH; i++) {
-          o[i][0] *= corr[0]; o[i][1] *= corr[1]; o[i][2] *= corr[0]; o[i][3] *= corr[1];
-        }
-        // P^T as the B operand: (keys 2t, 2t+1; head g) and (keys 2t+8, 2t+9; head g)
-        const uint32_t pb0 = transpose8x8(pack_bf16(p0, p1)), pb1 = transpose8x8(pack_bf16(p2, p3));
-#pragma unroll
-        for (int ch = 0; ch < CH; ch++) {
-#pragma unroll
-          for (int ii = 0; ii < 2; ii++) {
-            const uint32_t a0 = transpose8x8(reg_of(va[ch], 2 * ii)), a1 = transpose8x8(reg_of(va[ch], 2 * ii + 1));
-            const uint32_t a2 = transpose8x8(reg_of(vb[ch], 2 * ii)), a3 = transpose8x8(reg_of(vb[ch], 2 * ii + 1));
-            mma16816(o[2 * ch + ii], a0, a1, a2, a3, pb0, pb1);
+        const int key0 = cur.page * SA_KEYS + 16 * w;
+        to_end = cur.page == sq.first + sq.n - 1;
+        if (key0 <= sq.pos && key0 + 15 >= sq.lo) {  // (a page's last 16-key blocks may lie beyond the newest key)
+          // 16-byte fragments at the swizzled address of (row, 8 dims): box = dims / 64, chunk ^ (row & 7)
+          const uint8_t* kb_ = reinterpret_cast<const uint8_t*>(S.k[s]);
+          const uint8_t* vb_ = reinterpret_cast<const uint8_t*>(S.v[s]);
+          const int r0 = 16 * w + g;               // rows r0 and r0 + 8; both have (row & 7) == g
+          uint4 ka[CH], kb[CH], va[CH], vb[CH];
+  #pragma unroll
+          for (int ch = 0; ch < CH; ch++) {
+            const int off = (ch >> 1) * (SA_KEYS * 128) + (((((ch & 1) << 2) | t) ^ g) << 4);
+            ka[ch] = *reinterpret_cast<const uint4*>(kb_ + off + r0 * 128);
+            kb[ch] = *reinterpret_cast<const uint4*>(kb_ + off + (r0 + 8) * 128);
+            va[ch] = *reinterpret_cast<const uint4*>(vb_ + off + r0 * 128);
+            vb[ch] = *reinterpret_cast<const uint4*>(vb_ + off + (r0 + 8) * 128);
+          }
+          // S^T: [0],[1] = (key g, heads 2t, 2t+1); [2],[3] = (key g+8, same heads)
+          float sc[4] = {0.f, 0.f, 0.f, 0.f};
+  #pragma unroll
+          for (int ch = 0; ch < CH; ch++) {
+            mma16816(sc, ka[ch].x, kb[ch].x, ka[ch].y, kb[ch].y, qv[ch].x, qv[ch].y);
+            mma16816(sc, ka[ch].z, kb[ch].z, ka[ch].w, kb[ch].w, qv[ch].z, qv[ch].w);
+          }
+          const bool ok0 = key0 + g <= sq.pos && key0 + g >= sq.lo;
+          const bool ok1 = key0 + g + 8 <= sq.pos && key0 + g + 8 >= sq.lo;
+          sc[0] = ok0 ? sc[0] * P.scale : -INFINITY; sc[1] = ok0 ? sc[1] * P.scale : -INFINITY;
+          sc[2] = ok1 ? sc[2] * P.scale : -INFINITY; sc[3] = ok1 ? sc[3] * P.scale : -INFINITY;
+          // maximum per head over the block's 16 keys: this lane's two keys, then across g (lanes 4, 8, 16 apart)
+          float bm[2] = {fmaxf(sc[0], sc[2]), fmaxf(sc[1], sc[3])};
+          float corr[2], m_use[2];
+  #pragma unroll
+          for (int e = 0; e < 2; e++) {
+            bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 4));
+            bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 8));
+            bm[e] = fmaxf(bm[e], __shfl_xor_sync(0xffffffffu, bm[e], 16));
+            const float m_new = fmaxf(m_run[e], bm[e]);
+            m_use[e] = (m_new == -INFINITY) ? 0.f : m_new;
+            corr[e] = __expf(m_run[e] - m_use[e]);
+            m_run[e] = m_new;
+          }
+          const float p0 = __expf(sc[0] - m_use[0]), p1 = __expf(sc[1] - m_use[1]);
+          const float p2 = __expf(sc[2] - m_use[0]), p3 = __expf(sc[3] - m_use[1]);
+          l_run[0] = l_run[0] * corr[0] + p0 + p2;
+          l_run[1] = l_run[1] * corr[1] + p1 + p3;
+  #pragma unroll
+          for (int i = 0; i < 2 * CH; i++) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[1]; o[i][2] *= corr[0]; o[i][3] *= corr[1];
+          }
+          // P^T as the B operand: (keys 2t, 2t+1; head g) and (keys 2t+8, 2t+9; head g)
+          const uint32_t pb0 = transpose8x8(pack_bf16(p0, p1)), pb1 = transpose8x8(pack_bf16(p2, p3));
+  #pragma unroll
+          for (int ch = 0; ch < CH; ch++) {
+  #pragma unroll
+            for (int ii = 0; ii < 2; ii++) {
+              const uint32_t a0 = transpose8x8(reg_of(va[ch], 2 * ii)), a1 = transpose8x8(reg_of(va[ch], 2 * ii + 1));
+              const uint32_t a2 = transpose8x8(reg_of(vb[ch], 2 * ii)), a3 = transpose8x8(reg_of(vb[ch], 2 * ii + 1));
+              mma16816(o[2 * ch + ii], a0, a1, a2, a3, pb0, pb1);
+            }
           }
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&S.empty[s]);   // this warp has read the stage
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&S.empty[s]);   // this warp has read the stage
       cur.next(P);
       u++; it++;
     }
@@ -304,20 +411,25 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
           for (int r = 0; r < 2; r++)
             S.mo[w][hq][32 * ch + 8 * (g >> 1) + (g & 1) + 2 * (2 * ii + r)] = o[2 * ch + ii][2 * r + e];
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * NW) : "memory");
     if (S.abort_flag) break;
     {
       const bool whole = from_start && to_end;
       float* slot = P.scratch + ((size_t)c * 2 + (holds_u0 ? 0 : 1)) * (size_t)(gs * (HD + 2));
-      const int tid = threadIdx.x - 32;          // 0..127
-      for (int idx = tid; idx < gs * HD; idx += 128) {
+      const int tid = threadIdx.x - 32;          // 0 .. 32 NW - 1
+      for (int idx = tid; idx < gs * HD; idx += 32 * NW) {
         const int h = idx / HD, d = idx % HD;
-        const float m0 = S.mm[0][h], m1 = S.mm[1][h], m2 = S.mm[2][h], m3 = S.mm[3][h];
-        const float M = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        float M = S.mm[0][h];
+#pragma unroll
+        for (int i = 1; i < NW; i++) M = fmaxf(M, S.mm[i][h]);
         const float Mu = (M == -INFINITY) ? 0.f : M;
-        const float e0 = __expf(m0 - Mu), e1 = __expf(m1 - Mu), e2 = __expf(m2 - Mu), e3 = __expf(m3 - Mu);
-        const float acc = e0 * S.mo[0][h][d] + e1 * S.mo[1][h][d] + e2 * S.mo[2][h][d] + e3 * S.mo[3][h][d];
-        const float L = e0 * S.ml[0][h] + e1 * S.ml[1][h] + e2 * S.ml[2][h] + e3 * S.ml[3][h];
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int i = 0; i < NW; i++) {
+          const float e = __expf(S.mm[i][h] - Mu);
+          acc += e * S.mo[i][h][d];
+          L += e * S.ml[i][h];
+        }
         if (whole) {
           P.out[(size_t)b * P.ldo + (size_t)(kvh * gs + h) * HD + d] = __float2bfloat16_rn(acc / L);
         } else {
@@ -326,7 +438,7 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
         }
       }
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory");   // the merge area is free for the next run
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * NW) : "memory");   // the merge area is free for the next run
   }
 }
 
@@ -420,18 +532,18 @@ static int make_cache_map(CUtensorMap* map, const void* base, long long rows, in
   return r == CUDA_SUCCESS ? 0 : STRATUM_ERR_SHAPE;
 }
 
-template <int CH>
+template <int CH, bool WP, int NW>
 static int launch_stream(const CUtensorMap& mk, const CUtensorMap& mv, const SaParams& P, int grid,
                          cudaStream_t stream) {
-  const size_t smem = sizeof(SaSmem<CH>) + 1024;
-  auto kern = attention_stream_kernel<CH>;
+  const size_t smem = sizeof(SaSmem<CH, NW>) + 1024;
+  auto kern = attention_stream_kernel<CH, WP, NW>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  int st = launch_pdl(kern, grid, SA_THREADS, smem, stream, mk, mv, P);
+  int st = launch_pdl(kern, grid, 32 + 32 * NW, smem, stream, mk, mv, P);
   if (st != 0) return st;
   return launch_pdl(attention_stream_merge_kernel<CH>, P.n_seqs * P.n_q, 32 * CH, 0, stream, P, grid);
 }
@@ -444,11 +556,18 @@ STRATUM_EXPORT long long stratum_attention_stream_scratch_floats(int gs, int hea
 // q: bf16 [seqs][ldq], query heads first.  k_cache / v_cache: bf16 [n_pages][n_kv][64][head_dim].
 // One new token per sequence (row i of q, token_pos[i], block-table row token_seq[i], -1 = padding).
 // head_dim 64 or 128; at most 8 query heads per kv head; pages of 64 tokens; at most 1024 sequences.
+// whole_pages (head_dim 64 only): eight warps that take whole pages in turn instead of four warps that take a
+// quarter of every page.  With a quarter of a 16 KB page per warp little arrives per pass through a warp's chain of
+// dependent instructions, and the four warps together read 3.4 to 4.5 TB/s; eight warps with whole pages (one
+// maximum and one rescaling per 64 keys, two warps per scheduler to hide each other's latencies) read 5.8 TB/s at
+// 64 sequences of 4,096 tokens, but are behind where an SM gets only a few pages (11.2 against 9.9 us for one
+// sequence of 4,096 tokens).  At head_dim 128 (5 stages of 32 KB) the quarter form reads 6.5 TB/s.
 STRATUM_EXPORT int stratum_attention_stream(const void* q, int ldq, const void* k_cache, const void* v_cache,
                                             long long n_pages, const int* token_pos, const int* token_seq,
                                             const int* block_table, int bt_stride, void* out, int ldo, int n_seqs,
                                             int n_q, int n_kv, int head_dim, int page_tokens, int window, float scale,
-                                            int late_trigger, float* scratch, int* status, cudaStream_t stream) {
+                                            int late_trigger, int whole_pages, float* scratch, int* status,
+                                            cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   if (head_dim != 64 && head_dim != 128) return STRATUM_ERR_SHAPE;
   if (n_kv < 1 || n_q % n_kv != 0 || n_q / n_kv > SA_MAX_GS || page_tokens != SA_KEYS) return STRATUM_ERR_SHAPE;
@@ -467,6 +586,10 @@ STRATUM_EXPORT int stratum_attention_stream(const void* q, int ldq, const void* 
   P.late_trigger = late_trigger;
   // one CTA per SM; with fewer pages than SMs the surplus CTAs find an empty stretch and leave
   const int grid = sm_count() < SA_MAX_PIECES ? sm_count() : SA_MAX_PIECES;
-  if (head_dim == 64) return launch_stream<2>(mk, mv, P, grid, stream);
-  return launch_stream<4>(mk, mv, P, grid, stream);
+  if (whole_pages) {
+    if (head_dim != 64) return STRATUM_ERR_SHAPE;
+    return launch_stream<2, true, 8>(mk, mv, P, grid, stream);
+  }
+  if (head_dim == 64) return launch_stream<2, false, 4>(mk, mv, P, grid, stream);
+  return launch_stream<4, false, 4>(mk, mv, P, grid, stream);
 }

@@ -527,11 +527,13 @@ _stream_scratch = None
 
 def attention_stream(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, token_pos: torch.Tensor,
                      token_seq: torch.Tensor, block_table: torch.Tensor, out: torch.Tensor, n_q: int, n_kv: int,
-                     head_dim: int, page_tokens: int, window: int, scale: float, late_trigger: bool = True) -> None:
+                     head_dim: int, page_tokens: int, window: int, scale: float, late_trigger: bool = True,
+                     whole_pages: bool = False) -> None:
     """bfloat16 attention for decode steps (one new token per sequence, row i of qkv): the pages of all
     sequences are spread evenly over the SMs and streamed by TMA.  head_dim 64 or 128, at most 8 query heads per
     kv head, pages of 64 tokens, at most 1024 sequences.  late_trigger: a CTA that has asked for its last page lets
-    the kernels after this one start (they then wait on the SMs for this one to end)."""
+    the kernels after this one start (they then wait on the SMs for this one to end).  whole_pages (head_dim 64):
+    eight warps take whole pages in turn, instead of four warps a quarter of every page."""
     global _stream_scratch
     _need(qkv, "qkv", torch.bfloat16, contiguous=False); _need(k_cache, "k_cache", torch.bfloat16)
     _need(v_cache, "v_cache", torch.bfloat16); _need(out, "out", torch.bfloat16)
@@ -546,10 +548,11 @@ def attention_stream(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
         scratch_regrown()
     f = _fn("attention_stream", "stratum_attention_stream",
             [c_void_p, c_int, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p])
+             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p])
     _check(f(_ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), k_cache.shape[0], _ptr(token_pos),
              _ptr(token_seq), _ptr(block_table), block_table.stride(0), _ptr(out), out.stride(0), qkv.shape[0],
-             n_q, n_kv, head_dim, page_tokens, window, c_float(scale), int(bool(late_trigger)), _ptr(_stream_scratch[1]),
+             n_q, n_kv, head_dim, page_tokens, window, c_float(scale), int(bool(late_trigger)),
+             int(bool(whole_pages)), _ptr(_stream_scratch[1]),
              _ptr(status_word()),
              _stream()), "attention_stream")
     count_launches(1)

@@ -29,6 +29,14 @@ def plan_splits(n_items: int, max_len: int):
     return (max_len + chunk - 1) // chunk, chunk
 
 
+WHOLE_PAGES_MIN = 1184          # pages of all sequences and kv heads: eight to an SM of 148
+
+
+def _stream_form() -> str:
+    """STRATUM_ATTENTION_STREAM_FORM=0: never whole pages per warp (for measurements)."""
+    return os.environ.get("STRATUM_ATTENTION_STREAM_FORM", "")
+
+
 def run(att, qkv: torch.Tensor, cache, step, out: torch.Tensor) -> None:
     hd = att.head_dim
     if qkv.dtype != torch.bfloat16 or hd % 16 != 0 or hd > 128 or qkv.stride(0) % 8 != 0:
@@ -43,9 +51,13 @@ def run(att, qkv: torch.Tensor, cache, step, out: torch.Tensor) -> None:
         # decode steps: the pages of all sequences spread evenly over the SMs, streamed by TMA.  With more than
         # two sequences the kernels after it get a head start while the last pages stream in (3 % of a step on
         # the Llama-8B shape at 8 sequences); with one or two it costs more than it gives (measured)
+        # heads of 64: whole pages per warp where an SM gets more than a few pages (by the step's longest sequence;
+        # measured: 93 against 119 us at 64 sequences of 4,096 tokens, 11.2 against 9.9 us at one)
+        pages = step.n_tokens * att.n_kv_heads * ((step.max_len + PAGE_TOKENS - 1) // PAGE_TOKENS)
         K.attention_stream(qkv, cache.k, cache.v, step.token_pos, step.token_seq, cache.block_table, out,
                            att.n_heads, att.n_kv_heads, hd, PAGE_TOKENS, att.window, att.scale,
-                           late_trigger=step.n_tokens > 2)
+                           late_trigger=step.n_tokens > 2,
+                           whole_pages=hd == 64 and pages >= WHOLE_PAGES_MIN and _stream_form() != "0")
     elif step.all_single:
         n_splits, chunk = plan_splits(step.n_tokens * att.n_kv_heads * head_groups, step.max_len)
         part_o = part_ml = None

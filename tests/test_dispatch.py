@@ -71,6 +71,10 @@ def test_attention_rules(recorded):
     name, _, kw = _attention_call(recorded, bf, 128, 32, 8, 8, True)
     assert name == "attention_stream" and kw["late_trigger"] is True
     assert _attention_call(recorded, bf, 64, 8, 2, 2, True)[2]["late_trigger"] is False     # one or two sequences
+    # heads of 64: whole pages per warp once an SM gets more than a few pages (here 5 pages a sequence and kv head)
+    assert _attention_call(recorded, bf, 64, 8, 2, 100, True)[2]["whole_pages"] is False    # 1,000 pages
+    assert _attention_call(recorded, bf, 64, 32, 8, 64, True)[2]["whole_pages"] is True     # 2,560 pages
+    assert _attention_call(recorded, bf, 128, 32, 8, 64, True)[2]["whole_pages"] is False
     assert _attention_call(recorded, bf, 80, 6, 2, 8, True)[0] == "attention_mma"            # head size 80
     assert _attention_call(recorded, bf, 128, 12, 1, 8, True)[0] == "attention_mma"          # 12 heads per kv head
     assert _attention_call(recorded, bf, 128, 32, 8, 300, False)[0] == "attention_tc"

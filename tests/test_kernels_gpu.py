@@ -585,7 +585,7 @@ def test_attention_tc_far_key(halves):
     assert rel_err(as64(_run_tc(c, [100, 700], n_q, n_kv, hd, halves=halves)), c["ref"]) < 8e-3
 
 
-def _run_stream(c, n_q, n_kv, hd, window=0, pad_rows=0):
+def _run_stream(c, n_q, n_kv, hd, window=0, pad_rows=0, whole_pages=False):
     """attention_stream on the case's new tokens (one per sequence), optionally with padding rows appended."""
     from stratum_b200 import kernels as K
     T = c["T"]
@@ -596,19 +596,24 @@ def _run_stream(c, n_q, n_kv, hd, window=0, pad_rows=0):
         seq = torch.cat([seq, torch.full((pad_rows,), -1, dtype=torch.int32, device="cuda")])
     out = torch.zeros(T + pad_rows, n_q * hd, dtype=torch.bfloat16, device="cuda")
     K.attention_stream(qkv, c["kc"], c["vc"], pos, seq, c["table"], out, n_q, n_kv, hd, 64, window,
-                       1.0 / math.sqrt(hd))
+                       1.0 / math.sqrt(hd), whole_pages=whole_pages)
     K.check_status()
     # when the kernels after it may start changes nothing in the result
     early = torch.zeros_like(out)
     K.attention_stream(qkv, c["kc"], c["vc"], pos, seq, c["table"], early, n_q, n_kv, hd, 64, window,
-                       1.0 / math.sqrt(hd), late_trigger=False)
+                       1.0 / math.sqrt(hd), late_trigger=False, whole_pages=whole_pages)
     K.check_status()
     assert torch.equal(early, out)
     return out
 
 
-@pytest.mark.parametrize("n_q,n_kv,hd", [(8, 2, 128), (4, 4, 64), (32, 8, 128), (8, 1, 64), (3, 1, 128), (12, 2, 128)])
-def test_attention_stream_decode_steps(n_q, n_kv, hd):
+@pytest.mark.parametrize("n_q,n_kv,hd,whole", [(8, 2, 128, False), (4, 4, 64, False), (32, 8, 128, False),
+                                               (8, 1, 64, False), (3, 1, 128, False), (12, 2, 128, False),
+                                               (4, 4, 64, True), (8, 1, 64, True), (32, 8, 64, True), (6, 2, 64, True)])
+def test_attention_stream_decode_steps(n_q, n_kv, hd, whole):
+    """whole: eight warps that take whole pages in turn (heads of 64), else four warps a quarter of every page."""
+    from functools import partial
+    _run_stream = partial(globals()["_run_stream"], whole_pages=whole)
     rng = np.random.default_rng(hd + n_q + 3)
     # unequal sequences: one short of a page end, one just past it, a long one, a single key, a few pages
     lens = [63, 64, 1500, 0, 300, 129]
@@ -623,9 +628,18 @@ def test_attention_stream_decode_steps(n_q, n_kv, hd):
     lens = [int(x) for x in rng.integers(0, 200, size=70)]
     c = _attention_case(rng, lens, [1] * len(lens), n_q, n_kv, hd, "bfloat16")
     assert rel_err(as64(_run_stream(c, n_q, n_kv, hd)), c["ref"]) < 8e-3
+    if whole and n_kv == 8:
+        # many long sequences: every SM streams a hundred pages or more, its warps far apart in the ring
+        lens = [int(x) for x in rng.integers(2500, 3000, size=48)]
+        c = _attention_case(rng, lens, [1] * len(lens), n_q, n_kv, hd, "bfloat16")
+        for _ in range(3):
+            assert rel_err(as64(_run_stream(c, n_q, n_kv, hd)), c["ref"]) < 8e-3
 
 
-def test_attention_stream_far_key_and_window_edge():
+@pytest.mark.parametrize("whole", [False, True])
+def test_attention_stream_far_key_and_window_edge(whole):
+    from functools import partial
+    _run_stream = partial(globals()["_run_stream"], whole_pages=whole)
     rng = np.random.default_rng(43)
     n_q, n_kv, hd = 4, 2, 64
     far = {0: 3, 1: 517}
@@ -659,6 +673,10 @@ def test_attention_stream_refuses_what_it_cannot_do():
     with pytest.raises(K.KernelError, match="shape"):                       # 16 heads per kv head
         K.attention_stream(z(1, 18 * 64), z(1, 1, 64, 64), z(1, 1, 64, 64), z(1, dt=torch.int32),
                            z(1, dt=torch.int32), z(1, 1, dt=torch.int32), z(1, 16 * 64), 16, 1, 64, 64, 0, 1.0)
+    with pytest.raises(K.KernelError, match="shape"):                       # whole pages per warp: heads of 64 only
+        K.attention_stream(z(1, 3 * 128), z(1, 1, 64, 128), z(1, 1, 64, 128), z(1, dt=torch.int32),
+                           z(1, dt=torch.int32), z(1, 1, dt=torch.int32), z(1, 128), 1, 1, 128, 64, 0, 1.0,
+                           whole_pages=True)
 
 
 def test_attention_mma_refuses_head_sizes_it_cannot_do():
