@@ -1507,12 +1507,13 @@ static int clusterk_resident(int cs) {
 // k-block, and all clusters must be resident together.  (What the ranks exchange always fits a ring: at most
 // BN / CWS + 7 chunks of CWS x 128 float32, 60 KB.)
 // A rank's stretch must be CLUSTERK_MIN_KB k-blocks or more, and a "cluster" of one CTA (a whole tile's k per CTA,
-// on fewer SMs than stream-K uses) is not taken.  Measured in whole decode steps: a cluster launch does not start
-// as early behind its predecessor as a plain one, which a second pass saved pays for only where the product is
-// long enough.  Llama-3.2-1B shape (QKV 5 k-blocks a rank, gate|up one CTA a tile): with both 0.965 / 1.158 ms
-// at 8 / 16 rows, with neither 0.927 / 1.071; Llama-3.1-8B and Llama-2-7B shapes (16 to 56 k-blocks a rank) are
-// ahead with the cluster form up to about 40 rows (8B: 5.35 against 5.53 ms at 24 rows, 6.10 against 6.24 at 32,
-// level from 48 on; at 3.93 ms for 8 rows against 4.02 without).
+// on fewer SMs than stream-K uses) is not taken.  Both rules are measured in whole decode steps, not derived.
+// Llama-3.2-1B shape (QKV 24 clusters of 5 with 6 k-blocks a rank; gate|up 128 tiles, one CTA each): QKV in the
+// cluster form costs 5 us a layer at 64 rows, gate|up 4 us at 64 rows and 2.4 us at 8 rows (with an ordinary
+// launch instead of a cluster launch of one CTA just the same), against stream-K on all 148 SMs with its second
+// pass; with neither, the step takes 0.927 instead of 0.965 ms at 8 rows and 1.071 instead of 1.158 at 16.
+// Llama-3.1-8B and Llama-2-7B shapes (16 to 56 k-blocks a rank) are ahead with the cluster form up to about 40
+// rows (8B: 5.35 against 5.53 ms at 24 rows, 6.10 against 6.24 at 32, level from 48 on; 3.93 against 4.02 at 8).
 #ifndef CLUSTERK_MIN_KB
 #define CLUSTERK_MIN_KB 16
 #define CLUSTERK_MIN_CS 2
