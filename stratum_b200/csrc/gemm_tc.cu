@@ -31,7 +31,8 @@
 
 static int g_last_launches = 0;       // kernels the last stratum_gemm_tc call launched (for launch counting)
 static int g_last_form = 0;           // and the form it took: 1 tiles, 2 tiles on pairs of CTAs, 3 stream-K,
-                                      // 4 + 16 * cluster size: k shared inside clusters (for tests)
+                                      // 4 + 16 * cluster size: k shared inside clusters, 5 pairs that share
+                                      // their left-over tiles along k (for tests)
 
 // Work an epilogue may do beyond its basic form.  Every part is off while its pointer is null.
 //
@@ -547,6 +548,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const int n_tiles = tiles_m * tiles_n;
   const int n_kb = (P.K + TC_BK - 1) / TC_BK;
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  // the pairs' work is scheduled like the CTAs' of the tile kernel: whole tiles, then (P.split) the k-blocks of the
+  // tiles of a partly filled last wave spread evenly over all pairs, their pieces going to scratch
+  TcSchedule sched;
+  sched.init(n_tiles, n_kb, P.split, n_pairs, pair);
   volatile int* abort_flag = &S.abort_flag;
 
   if (threadIdx.x == 0) {
@@ -573,9 +578,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
+      int tile, kb0, kb1, slot;
+      for (int i = 0; ok && sched.item(i, tile, kb0, kb1, slot); i++) {
         const int tm = tile % tiles_m, tn = tile / tiles_m;
-        for (int kb = 0; kb < n_kb; kb++, it++) {
+        for (int kb = kb0; kb < kb1; kb++, it++) {
           const int s = it % STAGES;
           if (!mbar_wait(&S.empty[s], ((it / STAGES) & 1) ^ 1, abort_flag)) {
             atomicCAS(P.status, 0, 111); S.abort_flag = 1; ok = false; break;
@@ -596,7 +602,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const uint32_t idesc = instr_desc_bf16_m256(BN);
       uint32_t it = 0, t = 0;
       bool ok = true;
-      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, t++) {
+      int tile, kb0, kb1, slot;
+      for (; ok && sched.item((int)t, tile, kb0, kb1, slot); t++) {
         const int buf = t & 1;
         if (!__all_sync(0xffffffffu, mbar_wait(&S.acc_empty[buf], ((t >> 1) & 1) ^ 1, abort_flag))) {
           if (lane == 0) { atomicCAS(P.status, 0, 112); S.abort_flag = 1; }
@@ -604,7 +611,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * 256;
-        for (int kb = 0; kb < n_kb; kb++, it++) {
+        for (int kb = kb0; kb < kb1; kb++, it++) {
           const int s = it % STAGES;
           if (!__all_sync(0xffffffffu, mbar_wait(&S.full[s], (it / STAGES) & 1, abort_flag))) {
             if (lane == 0) { atomicCAS(P.status, 0, 113); S.abort_flag = 1; }
@@ -616,7 +623,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
             for (int k = 0; k < TC_BK / 16; k++)
               umma_bf16_2cta(d_tmem, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
-                             (kb > 0 || k > 0) ? 1u : 0u);
+                             (kb > kb0 || k > 0) ? 1u : 0u);
             umma_commit_2cta(&S.empty[s], 3);             // the stage is free again, in both CTAs
           }
           __syncwarp();
@@ -632,7 +639,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t acc_empty_leader[2] = {cluster_map(&S.acc_empty[0], 0), cluster_map(&S.acc_empty[1], 0)};
     uint32_t t = 0;
     bool ok = true;
-    for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, t++) {
+    int tile, kb0, kb1, slot;
+    for (; ok && sched.item((int)t, tile, kb0, kb1, slot); t++) {
       const int tm = tile % tiles_m, tn = tile / tiles_m;
       const int buf = t & 1;
       if (!__all_sync(0xffffffffu, mbar_wait(&S.acc_full[buf], (t >> 1) & 1, abort_flag))) {
@@ -643,6 +651,23 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       tc_fence_after();
       const int m = tm * 2 * TC_BM + (int)rank * TC_BM + row;
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * 256;
+      if (slot >= 0) {
+        // a piece of a shared tile: this CTA's 128 rows of partial sums, [column][row] so that the lanes of a warp
+        // write neighbours; the second kernel adds the pieces (only tiles of 256 columns are shared)
+        float* part = P.scratch + ((((size_t)pair * 2 + slot) * 2 + rank) * BN) * TC_BM + row;
+#pragma unroll 1
+        for (int c0 = 0; c0 + 32 <= BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j++) part[(size_t)(c0 + j) * TC_BM] = __uint_as_float(r[j]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(acc_empty_leader[buf]);
+        continue;
+      }
       EpiRow R = epi_row_begin<EPI>(P.X, m, P.M);
 #pragma unroll 1
       for (int c0 = 0; c0 + 32 <= BN; c0 += 32) {
@@ -1188,9 +1213,11 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld,
 // the r-th shared tile.  The pieces lie [column][row]: a warp reads 32 rows of one column at a time and adds the
 // pieces in the order of k (eight columns per thread, two pieces in flight); the sums go through shared memory so
 // that the epilogue writes rows, four neighbouring columns per thread.
+// halves = 2: the pieces of the pair kernel, whose tiles are two CTAs' 128 rows each (G pairs; a pair's slot holds
+// rank 0's rows, then rank 1's).
 template <int BN, int EPI>
 __global__ void __launch_bounds__(256)
-gemm_tc_pieces_kernel(const TcParams P, int G, int n_tiles, int n_kb, int tiles_a) {
+gemm_tc_pieces_kernel(const TcParams P, int G, int n_tiles, int n_kb, int tiles_a, int halves) {
   __shared__ float tile_s[32][65];
   pdl_trigger();
   const int R = n_tiles % G, U = R * n_kb;
@@ -1199,8 +1226,10 @@ gemm_tc_pieces_kernel(const TcParams P, int G, int n_tiles, int n_kb, int tiles_
   if (first_c == last_c) return;                   // one CTA had the whole tile
   const int tile = n_tiles - R + r;
   const int ta = tile % tiles_a, tb = tile / tiles_a;
-  const int row0 = (blockIdx.y % 4) * 32, col0 = (blockIdx.y / 4) * 64;
-  if (ta * TC_BM + row0 >= P.M || tb * BN + col0 >= P.N) return;
+  const int half = blockIdx.y % halves, part_y = blockIdx.y / halves;
+  const int row0 = (part_y % 4) * 32, col0 = (part_y / 4) * 64;
+  const int m0 = (ta * halves + half) * TC_BM + row0;
+  if (m0 >= P.M || tb * BN + col0 >= P.N) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   pdl_wait();
   float acc[8];
@@ -1212,7 +1241,7 @@ gemm_tc_pieces_kernel(const TcParams P, int G, int n_tiles, int n_kb, int tiles_
     for (int e = 0; e < 2; e++) {
       const int cc = c0 + e;
       const int slot = (tc_begin(cc < G ? cc : 0, G, U) / n_kb == r) ? 0 : 1;
-      const float* src = P.scratch + (((size_t)cc * 2 + slot) * BN + col0 + warp * 8) * TC_BM + row0 + lane;
+      const float* src = P.scratch + ((((size_t)cc * 2 + slot) * halves + half) * BN + col0 + warp * 8) * TC_BM + row0 + lane;
 #pragma unroll
       for (int j = 0; j < 8; j++) a[e][j] = (cc <= last_c) ? __ldcg(src + (size_t)j * TC_BM) : 0.f;
     }
@@ -1227,7 +1256,7 @@ gemm_tc_pieces_kernel(const TcParams P, int G, int n_tiles, int n_kb, int tiles_
 #pragma unroll
   for (int pass = 0; pass < 2; pass++) {
     const int rr = pass * 16 + (threadIdx.x >> 4), cc4 = (threadIdx.x & 15) * 4;
-    const int m = ta * TC_BM + row0 + rr;
+    const int m = m0 + rr;
     if (m < P.M)
       fixup_store<EPI>(P, m, tb * BN + col0 + cc4,
                        make_float4(tile_s[rr][cc4], tile_s[rr][cc4 + 1], tile_s[rr][cc4 + 2], tile_s[rr][cc4 + 3]));
@@ -1238,7 +1267,7 @@ gemm_tc_pieces_kernel(const TcParams P, int G, int n_tiles, int n_kb, int tiles_
 // a microsecond).  Plain: waves * n_kb.  Shared: the k-blocks spread over all SMs, plus writing and reading the
 // pieces (a piece of 128 x 256 float32 per SM costs about as much as 16 k-blocks, measured), plus the second
 // launch (6).  STRATUM_GEMM_SPLIT=0 turns sharing off, =1 forces it where it is possible (measurements).
-static bool split_pays(int n_tiles, int n_kb, int sms, int bn) {
+static bool split_pays(int n_tiles, int n_kb, int sms, int bn, float margin = 0.9f) {
   static int mode = -1;
   if (mode < 0) {
     const char* e = getenv("STRATUM_GEMM_SPLIT");
@@ -1250,7 +1279,7 @@ static bool split_pays(int n_tiles, int n_kb, int sms, int bn) {
   const float plain = (float)waves * n_kb;
   const float pieces = (float)(sms + left) / sms;                        // per SM
   const float shared = (float)n_tiles * n_kb / sms + pieces * 16.0f * bn / 256.0f + 6.0f;
-  return shared < 0.9f * plain;
+  return shared < margin * plain;
 }
 
 // The pair kernel: clusters of two CTAs, as many pairs as can be resident (at most one per two SMs).
@@ -1269,13 +1298,17 @@ static int resident_pairs() {
   return pairs;
 }
 
+// split: the tiles of a partly filled last wave are shared along k by all pairs, a second kernel adds their pieces
+// (tiles of 256 columns and the four basic epilogues only; scratch as for the tile kernel).
 template <int BN>
 static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, TcParams P, int epilogue, int n_tiles,
-                      cudaStream_t stream) {
+                      cudaStream_t stream, bool split = false, float* scratch = nullptr) {
   const size_t smem = sizeof(Tc2Smem<TC2_STAGES>) + 1024;
-  P.split = 0; P.scratch = nullptr;
   const int max_pairs = resident_pairs();
   if (max_pairs < 1) return STRATUM_ERR_LIMIT;
+  if (split && (BN != 256 || epilogue >= 4 || !scratch)) return STRATUM_ERR_SHAPE;
+  P.split = split ? 1 : 0; P.scratch = split ? scratch : nullptr;
+  const int tiles_m = (P.M + 2 * TC_BM - 1) / (2 * TC_BM), n_kb = (P.K + TC_BK - 1) / TC_BK;
 #define TC2_LAUNCH(E)                                                                                       \
   {                                                                                                         \
     auto kern = gemm_tc2_kernel<E, BN>;                                                                     \
@@ -1285,10 +1318,17 @@ static int launch_tc2(const CUtensorMap& ma, const CUtensorMap& mb, TcParams P, 
       if (e != cudaSuccess) return (int)e;                                                                  \
       configured = true;                                                                                    \
     }                                                                                                       \
-    const int pairs = n_tiles < max_pairs ? n_tiles : max_pairs;                                            \
-    const int st = launch_pdl(kern, 2 * pairs, TC_THREADS, smem, stream, ma, mb, P);                        \
+    const int pairs = (split || n_tiles >= max_pairs) ? max_pairs : n_tiles;                                \
+    int st = launch_pdl(kern, 2 * pairs, TC_THREADS, smem, stream, ma, mb, P);                              \
     if (st != 0) return st;                                                                                 \
-    g_last_launches = 1; g_last_form = 2;                                                                   \
+    g_last_launches = split ? 2 : 1; g_last_form = split ? 5 : 2;                                                    \
+    if constexpr (BN == 256 && E < 4) {                                                                     \
+      if (split) {                                                                                          \
+        st = launch_pdl(gemm_tc_pieces_kernel<BN, E>, dim3(n_tiles % pairs, 4 * (BN / 64) * 2), 256, 0,     \
+                        stream, P, pairs, n_tiles, n_kb, tiles_m, 2);                                       \
+        if (st != 0) return st;                                                                             \
+      }                                                                                                     \
+    }                                                                                                       \
   }
   switch (epilogue) {
     case 0: TC2_LAUNCH(0) break;
@@ -1331,6 +1371,12 @@ static int pair_kernel_min_rows() {
   return rows;
 }
 
+static bool pair_split_enabled() {                 // STRATUM_GEMM_PAIR_SPLIT=0 turns the sharing among pairs off (measurements)
+  static int on = -1;
+  if (on < 0) { const char* e = getenv("STRATUM_GEMM_PAIR_SPLIT"); on = (e && e[0] == '0') ? 0 : 1; }
+  return on == 1;
+}
+
 // Pairs of CTAs that can be resident at once (for reports).
 STRATUM_EXPORT int stratum_gemm_tc_resident_pairs(void) { return resident_pairs(); }
 
@@ -1360,8 +1406,8 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, TcParams P, i
     if (st != 0) return st;                                                                                 \
     g_last_launches = P.split ? 2 : 1; g_last_form = 1;                                                     \
     if (P.split) {                                                                                          \
-      st = launch_pdl(gemm_tc_pieces_kernel<BN, E>, dim3(left, 4 * (BN / 64)), 256, 0, stream, P, grid,              \
-                      n_tiles, n_kb, tiles_a);                                                              \
+      st = launch_pdl(gemm_tc_pieces_kernel<BN, E>, dim3(left, 4 * (BN / 64)), 256, 0, stream, P, grid,     \
+                      n_tiles, n_kb, tiles_a, 1);                                                           \
       if (st != 0) return st;                                                                               \
     }                                                                                                       \
   }
@@ -1683,6 +1729,21 @@ STRATUM_EXPORT int stratum_gemm_tc_ex(const void* x, const void* w, const float*
     // ahead from a few hundred rows on, except where N is small and the tile kernel can share its tiles along k)
     const int n_tiles2 = ((M + 2 * TC_BM - 1) / (2 * TC_BM)) * ((N + 255) / 256);
     const int rows1 = ((M + TC_BM - 1) / TC_BM) * TC_BM, rows2 = ((M + 2 * TC_BM - 1) / (2 * TC_BM)) * 2 * TC_BM;
+    // Few tiles of 256 x 256 (a few hundred rows, N of a few thousand): their k-blocks are shared by all pairs,
+    // as the tile kernel shares its left-over tiles, but with the pairs' smaller draw on L2 per flop.
+    if (wide && M >= pair_kernel_min_rows() && rows2 * 100 <= rows1 * 115 && scratch && epilogue < 4 && !X.norm_ss &&
+        pair_split_enabled()) {
+      const int pairs = resident_pairs();
+      // (measured on the Llama-8B shapes: K = 14336 at 256 and 512 rows 40 and 59 us against 53 and 83 with the tile
+      // kernel; at 768 rows, where the model says 0.79 of the unshared time, 82 against 79 us: the pairs that stay
+      // idle without sharing leave the busy ones a higher clock)
+      if (pairs >= 1 && split_pays(n_tiles2, (K + TC_BK - 1) / TC_BK, pairs, 256, 0.75f)) {
+        if ((st = make_map(&ma, x, M, K, ldx, TC_BM)) != 0) return st;
+        if ((st = make_map(&mb, w, N, K, K, 128)) != 0) return st;
+        g_last_parts = (N + 255) / 256;
+        return launch_tc2<256>(ma, mb, P, epilogue, n_tiles2, stream, true, scratch);
+      }
+    }
     if (wide && M >= pair_kernel_min_rows() && n_tiles2 * 10 >= (sm_count() / 2) * 6 &&
         rows2 * 100 <= rows1 * 115) {               // (not where half of a pair would work on rows beyond M)
       const int pairs = resident_pairs();

@@ -428,9 +428,10 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
 
 
 def gemm_tc_last_form() -> Tuple[str, int]:
-    """The form the last gemm_tc call took, for tests: ("tiles" | "pairs" | "stream-k" | "cluster-k", cluster size)."""
+    """The form the last gemm_tc call took, for tests:
+    ("tiles" | "pairs" | "pairs-shared" | "stream-k" | "cluster-k", cluster size)."""
     code = int(build.load("gemm_tc").stratum_gemm_tc_last_form())
-    return {1: "tiles", 2: "pairs", 3: "stream-k", 4: "cluster-k"}.get(code % 16, "none"), code // 16
+    return {1: "tiles", 2: "pairs", 3: "stream-k", 4: "cluster-k", 5: "pairs-shared"}.get(code % 16, "none"), code // 16
 
 
 # ------------------------------------------------------------------ attention (any sizes, CUDA cores)

@@ -27,12 +27,25 @@ STORE, ADD_TO_F32, STORE_F32, SWIGLU = K.EPI_STORE, K.EPI_ADD_F32, K.EPI_STORE_F
 # difference (4.00 against 3.99); on the Llama-3.2-1B shapes, where all but gate|up are that small, the step is
 # 8 to 11 % shorter with three to eight rows (1.20 against 1.29 ms at eight) and the same with sixteen.  Both can
 # be set in the environment for measurements.
-# Rows of x from which a product that adds into the residual stream honours the next norm's Handover (writes the
-# bfloat16 rows and the sums of squares the norm needs, so that the norm runs no kernel).  Measured on the Llama-8B
-# layer sizes: at 2,048 rows the two norm kernels of a layer (14 us each) go and the products' epilogues grow by
+# Where a product that adds into the residual stream honours the next norm's Handover (writes the bfloat16 rows
+# and the sums of squares the norm needs, so that the norm runs no kernel): where its tiles of 256 x 256 fill most
+# pairs of SMs, HANDOVER_MIN_TILES of them, and from HANDOVER_MIN_ROWS rows on.  Measured on the Llama-8B layer
+# sizes: at 2,048 rows the two norm kernels of a layer (14 us each) go and the products' epilogues grow by
 # 12 + 5 + 5 us; in decode steps the norm kernels cost nothing to begin with (they run while the next product's
-# weights stream in) and the longer epilogues make a step 4 % slower.  STRATUM_HANDOVER_MIN_ROWS for measurements.
+# weights stream in) and the longer epilogues make a step 4 % slower.  Between: a product that hands over cannot
+# share its left-over tiles along k (the second kernel of that sharing knows the plain epilogues only), and with a
+# few hundred rows the output and down projections are all left-over tiles: at 256 rows the down projection took
+# 109 us handing over against 40 us shared (a prompt of 256 tokens 9.2 against 6.0 ms); the Llama-3.2-1B shape's
+# projections (2,048 wide) fill the SMs only from 2,048 rows on.  Both can be set in the environment.
 HANDOVER_MIN_ROWS = int(os.environ.get("STRATUM_HANDOVER_MIN_ROWS", 256))
+HANDOVER_MIN_TILES = int(os.environ.get("STRATUM_HANDOVER_MIN_TILES", 60))
+
+
+def hands_over(rows: int, out_features: int) -> bool:
+    return (rows >= HANDOVER_MIN_ROWS
+            and ((rows + 255) // 256) * ((out_features + 255) // 256) >= HANDOVER_MIN_TILES)
+
+
 SKINNY_MAX_ROWS = int(os.environ.get("STRATUM_SKINNY_MAX_ROWS", 8))
 STREAMK_MIN_WEIGHTS = int(os.environ.get("STRATUM_STREAMK_MIN_WEIGHTS", 20_000_000))
 

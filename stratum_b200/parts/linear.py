@@ -47,7 +47,7 @@ class Linear:
             out = self.runtime.empty(M, width, dtype=torch.float32 if mode == STORE_F32 else x.dtype)
         if M == 0:
             return out
-        if (emit is not None and mode == ADD_TO_F32 and M >= gemm_dispatch.HANDOVER_MIN_ROWS
+        if (emit is not None and mode == ADD_TO_F32 and gemm_dispatch.hands_over(M, self.out_features)
                 and self.out_features % 128 == 0 and out.stride(0) % 4 == 0
                 and gemm_dispatch.takes_tensor_cores(x, self.weight, extras=False)):
             xb = self.runtime.empty(M, self.out_features, dtype=torch.bfloat16)

@@ -84,8 +84,8 @@ def test_attention_rules(recorded):
 
 def test_extra_epilogue_rules(recorded, monkeypatch):
     """Where a product carries more than its basic epilogue: rows of a handed-over norm and the query/key/value
-    epilogue go to the tensor-core kernel or are refused; a Handover is honoured from HANDOVER_MIN_ROWS rows on,
-    where the tensor-core kernel takes the product anyway; prompt attention gets query tiles of 256 rows."""
+    epilogue go to the tensor-core kernel or are refused; a Handover is honoured where the product's tiles fill the SMs
+    (hands_over); prompt attention gets query tiles of 256 rows."""
     from stratum_b200 import kernels as K
     from stratum_b200.parts import gemm_dispatch as G
     from stratum_b200.parts.base import Handover, NormedRows, Runtime
@@ -104,6 +104,9 @@ def test_extra_epilogue_rules(recorded, monkeypatch):
                                empty=lambda *shape, dtype=torch.bfloat16: torch.zeros(shape, dtype=dtype))
     lin = Linear(rt, torch.zeros(4096, 4096, dtype=torch.bfloat16))
     gain = torch.ones(4096)
+    assert not G.hands_over(768, 4096) and G.hands_over(769, 4096)          # 48 and 64 tiles of 256 x 256
+    assert not G.hands_over(1024, 2048) and G.hands_over(2048, 2048)
+    monkeypatch.setattr(G, "HANDOVER_MIN_TILES", 1)
     for rows, honoured in ((G.HANDOVER_MIN_ROWS - 1, False), (G.HANDOVER_MIN_ROWS, True)):
         recorded.clear()
         ask = Handover(gain, 4096, 1e-5)

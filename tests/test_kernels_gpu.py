@@ -164,6 +164,9 @@ CLUSTER_FORMS = {(8, 4096, 4096), (40, 4096, 4096 + 72), (30, 5000, 3080), (24, 
                  (64, 8192 + 8, 2048 + 16), (17, 4096, 14336), (64, 4096 + 64, 14336)}
 
 
+PAIRS_SHARED = {(512, 4096, 14336), (256, 4096 + 64, 4096), (200, 4096, 4096)}
+
+
 @pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (33, 48, 64), (64, 1000, 200), (100, 256, 4096), (300, 4096 + 16, 512),
                                      (2048, 2 * 177, 96), (129, 6144, 1024), (1, 128, 128), (17, 130, 72),
                                      (8, 4096, 4096), (5, 28672, 1024), (64, 4096 + 64, 14336), (16, 6144, 4096),
@@ -177,6 +180,8 @@ CLUSTER_FORMS = {(8, 4096, 4096), (40, 4096, 4096 + 72), (30, 5000, 3080), (24, 
                                      # pairs of CTAs on 256 x 256 tiles: rows and columns that end inside a tile, more
                                      # tiles than pairs of SMs, one row of tiles
                                      (1000, 2100, 264), (256, 28672, 128), (2304, 9000, 72),
+                                     # a few hundred rows, few tiles of 256 x 256: all pairs of CTAs share them along k
+                                     (512, 4096, 14336), (256, 4096 + 64, 4096), (520, 4100, 14344), (130, 2048 + 8, 1096), (700, 4100, 2048),
                                      # few rows, no more tiles than SMs: too little k for clusters to share
                                      (40, 4096, 2048), (30, 5120, 1000), (3, 2304, 1032), (8, 16000, 520),
                                      # k shared inside clusters, rows dealt out to the ranks
@@ -199,6 +204,8 @@ def test_gemm_tc(M, N, K_):
         assert form == "cluster-k" and 2 <= size <= 8
     elif M <= 64:
         assert K.gemm_tc_last_form()[0] == "stream-k"
+    elif (M, N, K_) in PAIRS_SHARED:
+        assert K.gemm_tc_last_form()[0] == "pairs-shared"
     out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
     K.gemm_tc(x, w, b, out, K.EPI_STORE)
     assert rel_err(as64(out), ref) < 6e-3

@@ -89,7 +89,7 @@ def test_real_layer_sizes_in_every_cut(model, dtype):
 def test_fused_epilogues_at_model_level(model, forced, monkeypatch):
     """The matrix products' extra epilogue work inside a model (bfloat16): rotation and cache write on the
     projection's epilogue, and norms handed over to the product in front of them.  By default the first serves
-    decode steps and the second prompts of 256 rows or more; `forced` turns both on for every step, so that
+    decode steps and the second prompts whose tiles fill the SMs (from 769 rows on at these widths); `forced` turns both on for every step, so that
     every form of the kernel meets them (prompts of 300 and 40 tokens, batches of 3 and 20 single tokens)."""
     from stratum_b200 import kernels as K
     from stratum_b200.engine import Engine, StepEntry, load_model
@@ -98,6 +98,7 @@ def test_fused_epilogues_at_model_level(model, forced, monkeypatch):
     if forced:
         monkeypatch.setenv("STRATUM_FUSE_ROPE", "2")
         monkeypatch.setattr(gemm_dispatch, "HANDOVER_MIN_ROWS", 1)
+        monkeypatch.setattr(gemm_dispatch, "HANDOVER_MIN_TILES", 1)
         monkeypatch.setattr(gemm_dispatch, "SKINNY_MAX_ROWS", 0)        # every product on the tensor-core kernel
     m, _ = load_model(path, torch.bfloat16, "cuda")
     engine = Engine(m, max_tokens=4096)
@@ -116,7 +117,8 @@ def test_fused_epilogues_at_model_level(model, forced, monkeypatch):
     n_layers = cfg["num_hidden_layers"]
     if forced:
         assert calls["rope_store"] == 0                       # rotation rode on the projection
-    assert calls["rmsnorm"] == 2                              # the first layer's first norm, and the final one
+    # handed over: only the first layer's first norm and the final one run a kernel of their own
+    assert calls["rmsnorm"] == (2 if forced else 2 * n_layers + 1)
     got = engine.step([StepEntry(s, q[:n], [n - 1]) for s, q, n in zip(slots[1:], seqs[1:], lens[1:])]).cpu().numpy()
     assert_close(got[:2], np.stack([refs[1][39], refs[2][6]]), "bfloat16", "prompts of 40 and 7 among others")
     before = dict(calls)
