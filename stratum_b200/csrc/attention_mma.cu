@@ -286,7 +286,10 @@ attention_tile_kernel(const AttnParams P) {
   const int qb = blockIdx.x;
   const int kvh = blockIdx.y / P.head_groups, hg = blockIdx.y % P.head_groups;
   const int seq = P.qb_seq[qb];
-  if (seq < 0) return;
+  if (seq < 0) {                       // an entry beyond the step's blocks
+    pdl_wait();                        // no CTA leaves before the kernel before this one is done
+    return;
+  }
   const int tok0 = P.qb_tok0[qb], ntok = P.qb_ntok[qb];
   const int gs = P.n_q / P.n_kv;
   const int Hd = P.head_dim;

@@ -116,6 +116,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const int kvh = blockIdx.x % P.n_kv;
   const int seq = P.qb_seq[qb];
   const int tok0 = P.qb_tok0[qb], ntok = P.qb_ntok[qb];
+  if (seq < 0 || ntok <= 0) {          // an entry beyond the step's blocks (lists of a fixed length: replayed steps)
+    pdl_wait();                        // no CTA leaves before the kernel before this one is done
+    return;
+  }
   volatile int* abort_flag = &S.abort_flag;
 
   if (threadIdx.x == 0) {

@@ -286,7 +286,10 @@ rope_store_prompt_kernel(bf16* __restrict__ qkv, const int* __restrict__ token_p
   pdl_trigger();
   const int t = blockIdx.x;
   const int seq = token_seq[t];
-  if (seq < 0) return;
+  if (seq < 0) {                       // a padding token
+    pdl_wait();                        // no block leaves before the kernel before this one is done
+    return;
+  }
   const int pos = token_pos[t];
   for (int k = threadIdx.x; k < n_pairs; k += blockDim.x) {
     float sn, c;

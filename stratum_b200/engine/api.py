@@ -9,6 +9,7 @@ CONTRIBUTING.md:52); the names follow its command line and environment switches.
 """
 from __future__ import annotations
 
+import os
 from typing import Callable, List, Optional, Sequence, Tuple
 
 import torch
@@ -16,7 +17,7 @@ import torch
 from ..config.base import ModelConfig
 from ..sampling import Pcg32, Sampler, SamplingParams
 from .generate import Backend, GenerationResult, generate
-from .graphs import DecodeGraphs
+from .graphs import DecodeGraphs, PromptGraphs
 from .model import load_model, random_model_on_device
 from .step import Engine, StepEntry
 
@@ -24,8 +25,8 @@ _DTYPES = {"float32": torch.float32, "fp32": torch.float32, "bfloat16": torch.bf
 
 
 class _EngineBackend(Backend):
-    def __init__(self, engine: Engine, sampler: Sampler, graphs=None):
-        self.engine, self.sampler, self.graphs = engine, sampler, graphs
+    def __init__(self, engine: Engine, sampler: Sampler, graphs=None, prompt_graphs=None):
+        self.engine, self.sampler, self.graphs, self.prompt_graphs = engine, sampler, graphs, prompt_graphs
         self.n_pages, self.max_seqs = engine.cache.n_pages, engine.cache.max_seqs
         self.on_logits = None          # optional hook(logits [n, vocab] on the device, picked ids list)
 
@@ -59,7 +60,9 @@ class _EngineBackend(Backend):
             if self.on_logits is not None:
                 self.on_logits(captured.logits[:len(work)], picked)
             return picked, values
-        logits = self.engine.step([StepEntry(s, toks, [len(toks) - 1]) for s, toks in work])
+        entries = [StepEntry(s, toks, [len(toks) - 1]) for s, toks in work]
+        shape = self.prompt_graphs.shape_of(entries) if self.prompt_graphs is not None else None
+        logits = self.prompt_graphs.step(entries, shape) if shape is not None else self.engine.step(entries)
         ids, values = self.sampler.pick(logits, params, streams, want_values=True)
         both = torch.stack([ids.to(torch.float64), values.to(torch.float64)]).cpu()     # one device-to-host copy
         picked = [int(v) for v in both[0].tolist()]
@@ -85,7 +88,10 @@ class Stratum:
         self.engine = Engine(self.model, max_tokens=max_tokens, max_seqs=max_seqs)
         self.sampler = Sampler(self.model.runtime.device)
         self.graphs = DecodeGraphs(self.engine) if use_graphs else None
-        self._backend = _EngineBackend(self.engine, self.sampler, self.graphs)
+        # short prompt steps are replayed too (STRATUM_PROMPT_GRAPHS=0: launch by launch, for measurements)
+        self.prompt_graphs = (PromptGraphs(self.engine)
+                              if use_graphs and os.environ.get("STRATUM_PROMPT_GRAPHS", "1") != "0" else None)
+        self._backend = _EngineBackend(self.engine, self.sampler, self.graphs, self.prompt_graphs)
 
     @classmethod
     def from_random(cls, config: ModelConfig, seed: int = 0, dtype: str = "bfloat16", max_tokens: int = 4096,
@@ -103,7 +109,11 @@ class Stratum:
         self.engine.release(slot)
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """Run the entries' tokens; float32 logits [wanted places, vocab] on the device."""
+        """Run the entries' tokens; float32 logits [wanted places, vocab] on the device.  (A short prompt step is
+        replayed as a captured graph, like decode steps; the logits are then copied out of the graph's output.)"""
+        shape = self.prompt_graphs.shape_of(entries) if self.prompt_graphs is not None else None
+        if shape is not None:
+            return self.prompt_graphs.step(entries, shape).clone()
         return self.engine.step(entries)
 
     def decode_step(self, slots: Sequence[int], tokens: Sequence[int],

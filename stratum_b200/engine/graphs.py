@@ -34,7 +34,7 @@ import torch
 
 from .. import kernels as K
 from ..cache.pages import PAGE_TOKENS, pages_for
-from .step import Engine, StepDescription, StepError
+from .step import Engine, StepDescription, StepEntry, StepError
 
 
 def padded_rows(n: int) -> int:
@@ -236,3 +236,150 @@ class _InFlight:
 
 
 _ONES = [1] * 1024
+
+
+# ---------------------------------------------------------------------------------------------- prompt steps
+def padded_tokens(n: int, limit: int) -> Optional[int]:
+    """Tokens a prompt graph is captured for: multiples of 64 up to 512, of 128 above; None beyond `limit`."""
+    p = ((n + 63) // 64) * 64 if n <= 512 else ((n + 127) // 128) * 128
+    return p if p <= limit else None
+
+
+def padded_seqs(n: int) -> int:
+    w = 1
+    while w < n:
+        w *= 2
+    return w
+
+
+class _CapturedPrompt:
+    def __init__(self):
+        self.desc: Optional[StepDescription] = None
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.kernels = 0
+        self.scratch_epoch = -1
+
+
+class PromptGraphs:
+    """Runs short prompt steps of an Engine (a batch's first step: prompts of unequal lengths) as replayed graphs.
+
+    Issued launch by launch from Python a prompt step costs some ten microseconds of host time a launch, a dozen
+    launches a layer; below a few hundred tokens (a few thousand for a small model) that is more than the GPU
+    needs.  So a prompt step is captured once per shape (tokens padded up to a multiple of 64 or 128, sequences
+    to a power of two, page tables to a power of two of pages) and replayed: the host writes the description
+    (StepDescription.write_prompts) and replays.  Tokens beyond the step's have sequence index -1, sequences
+    beyond the step's bring no token, and the query blocks of the attention are lists of a fixed length whose
+    surplus entries are empty; rows never mix, so padding changes no result.  Only models whose parts all say
+    `replays_prompts` are taken; a step that is too long, or that wants more rows than it has sequences (trace
+    replay asks for every position), runs launch by launch as before.
+
+    Capturing a shape takes three passes (which query-block sizes are asked for; once launch by launch on
+    padding only, so that every kernel has run and every scratch buffer exists; the capture), so a shape pays off
+    from its second or third use on.
+    """
+
+    def __init__(self, engine: Engine, max_graphs: int = 12, max_tokens: int = 2048):
+        self.engine = engine
+        self.max_graphs, self.max_tokens = max_graphs, max_tokens
+        self.graphs: "OrderedDict[Tuple[int, int, int], _CapturedPrompt]" = OrderedDict()
+        self.pool = None
+        self.captures = 0
+        self.replays = 0
+        self.enabled = engine.model.replays_prompts()
+
+    def shape_of(self, entries: Sequence[StepEntry]) -> Optional[Tuple[int, int, int]]:
+        """(padded tokens, padded sequences, page-table width) if this step is one that is replayed, else None."""
+        if not self.enabled or not entries:
+            return None
+        T = sum(len(e.tokens) for e in entries)
+        S = padded_seqs(len(entries))
+        if sum(len(e.want) for e in entries) > S or all(len(e.tokens) == 1 for e in entries):
+            return None
+        Tp = padded_tokens(T, self.max_tokens)
+        if Tp is None:
+            return None
+        cache = self.engine.cache
+        try:
+            longest = max(cache.length(e.slot) + len(e.tokens) for e in entries)
+        except Exception:
+            return None                               # (a bad slot: the step function says so)
+        return Tp, S, width_bucket(max(1, pages_for(longest)))
+
+    def _all_padding(self, d: StepDescription) -> None:
+        d.write_prompts([], [], [])
+        d.write_tokens([], [])
+        d.upload()
+
+    def _capture(self, key: Tuple[int, int, int]) -> _CapturedPrompt:
+        eng = self.engine
+        Tp, S, width = key
+        c = _CapturedPrompt()
+        max_len = width * PAGE_TOKENS
+        # 1. which query-block sizes the model asks for (with no tokens, nothing is launched for them)
+        probe = StepDescription(eng, Tp, S, S, width)
+        self._all_padding(probe)
+        batch = probe.batch(max_len)
+        batch.sizes_seen = set()
+        eng.model.forward(batch, eng.cache)
+        # 2. the description that stays; once launch by launch, on padding only
+        c.desc = StepDescription(eng, Tp, S, S, width, pinned=True, qblock_sizes=sorted(batch.sizes_seen))
+        self._all_padding(c.desc)
+        eng.model.forward(c.desc.batch(max_len), eng.cache)
+        torch.cuda.synchronize()
+        K.check_status()
+        # 3. the capture
+        if self.pool is None:
+            self.pool = torch.cuda.graph_pool_handle()
+        g = torch.cuda.CUDAGraph()
+        before = K.launch_count()
+        with torch.cuda.graph(g, pool=self.pool):
+            c.logits = eng.model.forward(c.desc.batch(max_len), eng.cache)
+        c.kernels = K.launch_count() - before
+        K.count_launches(-c.kernels)                  # captured, not run
+        c.graph = g
+        c.scratch_epoch = K.scratch_epoch()
+        self.captures += 1
+        return c
+
+    def _get(self, key: Tuple[int, int, int]) -> _CapturedPrompt:
+        c = self.graphs.get(key)
+        if c is not None and c.scratch_epoch != K.scratch_epoch():
+            del self.graphs[key]                      # a scratch buffer it recorded the address of was regrown
+            c = None
+        if c is None:
+            while len(self.graphs) >= self.max_graphs:
+                self.graphs.popitem(last=False)
+            c = self._capture(key)
+            if c.scratch_epoch != K.scratch_epoch():  # (the capture itself regrew one: its addresses are the new ones)
+                c.scratch_epoch = K.scratch_epoch()
+            self.graphs[key] = c
+        else:
+            self.graphs.move_to_end(key)
+        return c
+
+    def step(self, entries: Sequence[StepEntry], key: Optional[Tuple[int, int, int]] = None) -> torch.Tensor:
+        """As Engine.step: float32 logits [wanted places, vocab] on the device (a view of the graph's own output,
+        valid until this shape is stepped again).  On error nothing has changed."""
+        eng = self.engine
+        cache = eng.cache
+        slots = [e.slot for e in entries]
+        token_lists = [e.tokens for e in entries]
+        wants = [e.want for e in entries]
+        eng.validate(slots, token_lists, wants)
+        key = key or self.shape_of(entries)
+        if key is None:
+            raise StepError("this step is not one that is replayed")
+        n_new = [len(t) for t in token_lists]
+        cache.reserve(slots, n_new)                   # raises CacheFull before anything is launched
+        before = [cache.length(s) for s in slots]
+        c = self._get(key)
+        c.desc.write_prompts(slots, n_new, wants)
+        c.desc.write_tokens(token_lists, before)
+        c.desc.upload()
+        c.graph.replay()
+        K.count_launches(c.kernels)
+        self.replays += 1
+        eng.check_kernels()                           # synchronises; raises if a kernel gave up a wait
+        cache.advance(slots, n_new)
+        return c.logits[:sum(len(w) for w in wants)]

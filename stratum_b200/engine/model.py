@@ -117,6 +117,13 @@ class Model:
         self.final_norm.bind(weights)
         self.head.bind_with_embedding(weights, self.embedding.table())
 
+    def replays_prompts(self) -> bool:
+        """Whether every part and arrangement serves captured prompt steps (Part.replays_prompts)."""
+        parts = [self.embedding, self.final_norm, self.head] + ([self.position] if self.position is not None else [])
+        for layer in self.layers:
+            parts += list(layer.parts()) + [layer.arrangement]
+        return all(getattr(p, "replays_prompts", False) for p in parts)
+
     # ------------------------------------------------------------------ forward
     def forward(self, step, cache) -> torch.Tensor:
         """Run the tokens of one step through every stop of the schedule; float32 logits at the wanted rows."""

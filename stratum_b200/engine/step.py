@@ -52,6 +52,8 @@ class StepBatch:
     max_len: int = 1                  # longest sequence after this step
     all_single: bool = True           # every sequence brings exactly one token
     host: Optional[dict] = None       # the same numbers on the host, for parts that plan launches
+    fixed_qblocks: Optional[Dict[int, tuple]] = None   # a captured prompt step: its query blocks, padded lists
+    sizes_seen: Optional[set] = None  # when set: the block sizes `query_blocks` was asked for are noted here
     _qblocks: Dict[int, tuple] = field(default_factory=dict)
     _rotation: Dict[object, torch.Tensor] = field(default_factory=dict)
 
@@ -67,7 +69,14 @@ class StepBatch:
 
     def query_blocks(self, tokens_per_block: int):
         """Cut every sequence's new tokens into runs of at most `tokens_per_block`: int32 tensors
-        (sequence, first packed row, tokens) on the device, made once per step and block size."""
+        (sequence, first packed row, tokens) on the device, made once per step and block size.  In a captured
+        prompt step the lists have a fixed length; entries beyond the step's blocks have sequence -1 and no tokens."""
+        if self.fixed_qblocks is not None:
+            if tokens_per_block not in self.fixed_qblocks:
+                raise StepError(f"this captured step was described without query blocks of {tokens_per_block} tokens")
+            return self.fixed_qblocks[tokens_per_block]
+        if self.sizes_seen is not None:
+            self.sizes_seen.add(tokens_per_block)
         if tokens_per_block not in self._qblocks:
             seqs, rows, counts = [], [], []
             r = 0
@@ -94,11 +103,15 @@ class StepDescription:
     """
 
     def __init__(self, engine: "Engine", n_tokens: int, n_seqs: int, n_want: int, width: int,
-                 extras: Sequence = (), pinned: bool = False):
+                 extras: Sequence = (), pinned: bool = False, qblock_sizes: Sequence[int] = ()):
         self.engine = engine
         self.n_tokens, self.n_seqs, self.n_want, self.width = n_tokens, n_seqs, n_want, width
         self.groups = engine.kv_groups
         self.off: Dict[str, tuple] = {}
+        # query blocks of each size a captured prompt step asks for: at most tokens / size + sequences of them
+        self.qblock_sizes = tuple(sorted(qblock_sizes))
+        self.qblock_max = {n: n_tokens // n + n_seqs for n in self.qblock_sizes}
+        extras = tuple(extras) + tuple((f"qb{n}", 3 * self.qblock_max[n]) for n in self.qblock_sizes)
         o = 0
         for name, n in (("ids", n_tokens), ("pos", n_tokens), ("seq", n_tokens), ("want", n_want),
                         ("slot", n_seqs), ("start", n_seqs + 1), ("len", n_seqs),
@@ -158,6 +171,55 @@ class StepDescription:
         self.n_new = list(n_new) + [1] * pad
         self.single = all(n == 1 for n in n_new)
 
+    def write_prompts(self, slots: Sequence[int], n_new: Sequence[int], wants: Sequence[Sequence[int]]) -> None:
+        """Like write_membership, for a description larger than the step in tokens, sequences and wanted rows,
+        each by itself (a captured prompt step): tokens beyond the step's have sequence index -1 and belong to no
+        sequence; sequences beyond the step's bring no token, hold nothing and have the spare state row; wanted
+        rows beyond the step's point at row 0 (their logits are computed and not looked at)."""
+        v = self.views
+        B, T = len(slots), sum(n_new)
+        n_want = sum(len(w) for w in wants)
+        if B > self.n_seqs or T > self.n_tokens or n_want > self.n_want:
+            raise StepError(f"step of {T} tokens, {B} sequences, {n_want} wanted rows in a description for "
+                            f"{self.n_tokens}, {self.n_seqs}, {self.n_want}")
+        cache = self.engine.cache
+        seq, start, slot = v["seq"], v["start"], v["slot"]
+        r = 0
+        for i, n in enumerate(n_new):
+            seq[r:r + n] = i
+            start[i] = r
+            r += n
+        seq[T:] = -1
+        start[B:] = T
+        slot[:B] = slots
+        slot[B:] = cache.max_seqs
+        w = 0
+        for i, ws in enumerate(wants):
+            for p in ws:
+                v["want"][w] = start[i] + int(p)
+                w += 1
+        v["want"][w:] = 0
+        if self.groups:
+            tb = v["tables"].reshape(len(self.groups), self.n_seqs, self.width)
+            tb.fill(-1)
+            for j, gi in enumerate(self.groups):
+                for i, row in enumerate(cache.page_table_rows(slots, gi)):
+                    tb[j, i, :len(row)] = row
+        for size in self.qblock_sizes:
+            m = self.qblock_max[size]
+            qb = v[f"qb{size}"].reshape(3, m)
+            k, r = 0, 0
+            for i, n in enumerate(n_new):
+                for b in range(0, n, size):
+                    qb[0, k], qb[1, k], qb[2, k] = i, r + b, min(size, n - b)
+                    k += 1
+                r += n
+            qb[0, k:] = -1
+            qb[1, k:] = 0
+            qb[2, k:] = 0
+        self.n_new = list(n_new) + [0] * (self.n_seqs - B)
+        self.single = False
+
     def write_tokens(self, token_lists: Sequence[Sequence[int]], before: Sequence[int]) -> None:
         """The tokens themselves, their positions, and each sequence's length once they are appended."""
         v = self.views
@@ -196,11 +258,17 @@ class StepDescription:
         R, W = self.n_seqs, self.width
         a, _ = self.off["tables"]
         tables = {gi: self.dev[a + j * R * W: a + (j + 1) * R * W].view(R, W) for j, gi in enumerate(self.groups)}
+        fixed = None
+        if self.qblock_sizes:
+            fixed = {}
+            for n in self.qblock_sizes:
+                m, f = self.qblock_max[n], self.field(f"qb{n}")
+                fixed[n] = (f[:m], f[m:2 * m], f[2 * m:3 * m])
         return StepBatch(n_tokens=self.n_tokens, n_seqs=R, token_ids=self.field("ids"), token_pos=self.field("pos"),
                          token_seq=self.field("seq"), want_rows=self.field("want"), seq_slot=self.field("slot"),
                          seq_start=self.field("start"), seq_len=self.field("len"), block_tables=tables,
-                         max_new=max(self.n_new), max_len=max_len, all_single=self.single,
-                         host={"n_new": list(self.n_new), "before": self.before})
+                         max_new=max(self.n_new, default=0), max_len=max_len, all_single=self.single,
+                         host={"n_new": list(self.n_new), "before": self.before}, fixed_qblocks=fixed)
 
 
 class Engine:

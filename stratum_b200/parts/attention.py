@@ -41,6 +41,12 @@ class GQAAttention(Mixer):
     takes_normed_rows = True
     hands_on = True
 
+    @property
+    def replays_prompts(self) -> bool:
+        """(as far as the parts inside it do: the position encoding and the norms of the heads)"""
+        inner = [p for p in (self.position, self.q_norm, self.k_norm) if p is not None]
+        return all(getattr(p, "replays_prompts", False) for p in inner)
+
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.hidden = int(spec["hidden"])

@@ -77,6 +77,11 @@ class Part:
     kind = ""
     takes_normed_rows = False    # forward accepts NormedRows in place of the normed tensor
     hands_on = False             # forward takes `emit=Handover` and may honour it
+    # forward also serves a captured prompt step (engine/graphs.py, PromptGraphs): beside the rules for captured
+    # decode steps, tokens with sequence index -1 belong to no sequence (nothing of theirs reaches a cache or a
+    # state row), sequences may bring no token, and query blocks come from step.query_blocks only.  A model whose
+    # parts and arrangements all say so has its short prompt steps replayed; others run them launch by launch.
+    replays_prompts = False
 
     def __init__(self, spec: PartSpec, runtime: Optional[Runtime]):
         self.spec = spec
@@ -179,6 +184,7 @@ class Arrangement:
     optional: tuple = ()
     cache_owner: Optional[str] = "mixer"
     carries = False     # forward takes carry= / hand_to= and returns a carry (see accepts_carry)
+    replays_prompts = False    # as Part.replays_prompts
 
     def forward(self, layer, x: torch.Tensor, step, cache: LayerCache) -> None:
         raise NotImplementedError

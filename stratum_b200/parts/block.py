@@ -12,6 +12,7 @@ from .registry import register_part
 class PreNormResidual(Arrangement):
     """x += mixer(norm_a(x)); x += feed_forward(norm_b(x)): each norm stands before its part, on the
     residual stream (stratum/native/stratum_arch_llama.inc.c:392-396, :524-532, :555)."""
+    replays_prompts = True
 
     slots = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
     carries = True

@@ -17,6 +17,7 @@ from .spec import TensorSpec
 @register_part("embedding", "token_embedding")
 class TokenEmbedding(Embedding):
     """params: vocab, hidden, prefix (e.g. "model.embed_tokens.")."""
+    replays_prompts = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -41,6 +42,7 @@ class TokenEmbedding(Embedding):
 @register_part("head", "linear_head")
 class LinearHead(Head):
     """params: vocab, hidden, tied (the file may leave the matrix out), prefix (e.g. "lm_head.")."""
+    replays_prompts = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)

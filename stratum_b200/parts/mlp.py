@@ -24,6 +24,7 @@ def interleave_rows(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 @register_part("feed_forward", "swiglu")
 class SwiGLU(FeedForward):
     """params: hidden, intermediate, bias, prefix."""
+    replays_prompts = True
     takes_normed_rows = True
     hands_on = True
 

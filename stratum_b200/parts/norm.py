@@ -14,6 +14,7 @@ from .spec import TensorSpec
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
     """params: size, eps, prefix (e.g. "input_layernorm.")."""
+    replays_prompts = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)

@@ -77,6 +77,7 @@ def inverse_frequencies(rope_dim: int, theta: float, scaling: Optional[dict]) ->
 @register_part("position", "rope")
 class RotaryEmbedding(PositionEncoding):
     """params: rope_dim, theta, interleaved, scaling (dict with 'kind' and its numbers, or None)."""
+    replays_prompts = True
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -101,3 +102,4 @@ class RotaryEmbedding(PositionEncoding):
 @register_part("position", "none")
 class NoPositionEncoding(PositionEncoding):
     """Queries and keys are used as projected."""
+    replays_prompts = True
