@@ -158,6 +158,7 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     with open(os.path.join(path, "config.json")) as f:
         assert json.load(f)["architectures"] == ["ToyStateForCausalLM"]
     llm = Stratum(path, dtype="float32", max_tokens=1024)                                        # chosen by config.json
+    assert not llm.prompt_graphs.enabled        # a part that does not say `replays_prompts`: prompts launch by launch
     groups = llm.engine.cache.groups
     assert len(groups) == 2 and sum(isinstance(g.spec, StateSpec) for g in groups) == 1
     assert [g.state.shape for g in groups if g.state is not None] == [(2, llm.engine.cache.max_seqs + 1, 24)]
