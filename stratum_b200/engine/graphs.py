@@ -276,13 +276,15 @@ class PromptGraphs:
     sequences (trace replay asks for every position), runs launch by launch as before.
 
     Capturing a shape takes three passes (which query-block sizes are asked for; once launch by launch on
-    padding only, so that every kernel has run and every scratch buffer exists; the capture), so a shape pays off
-    from its second or third use on.
+    padding only, so that every kernel has run and every scratch buffer exists; the capture), so a shape is
+    captured when it is met for the second time (`capture_after` sightings run launch by launch first): a shape
+    that never comes back costs nothing extra, one that does pays off from its third use on.
     """
 
-    def __init__(self, engine: Engine, max_graphs: int = 12, max_tokens: int = 1024):
+    def __init__(self, engine: Engine, max_graphs: int = 12, max_tokens: int = 1024, capture_after: int = 1):
         self.engine = engine
-        self.max_graphs, self.max_tokens = max_graphs, max_tokens
+        self.max_graphs, self.max_tokens, self.capture_after = max_graphs, max_tokens, capture_after
+        self.sightings: Dict[Tuple[int, int, int], int] = {}
         self.graphs: "OrderedDict[Tuple[int, int, int], _CapturedPrompt]" = OrderedDict()
         self.pool = None
         self.captures = 0
@@ -290,7 +292,18 @@ class PromptGraphs:
         self.enabled = engine.model.replays_prompts()
 
     def shape_of(self, entries: Sequence[StepEntry]) -> Optional[Tuple[int, int, int]]:
-        """(padded tokens, padded sequences, page-table width) if this step is one that is replayed, else None."""
+        """(padded tokens, padded sequences, page-table width) if this step is one that is replayed now, else
+        None.  (Counts the sighting: call once per step.)"""
+        key = self._shape(entries)
+        if key is None or key in self.graphs:
+            return key
+        if len(self.sightings) > 4096:
+            self.sightings.clear()
+        n = self.sightings.get(key, 0)
+        self.sightings[key] = n + 1
+        return key if n >= self.capture_after else None
+
+    def _shape(self, entries: Sequence[StepEntry]) -> Optional[Tuple[int, int, int]]:
         if not self.enabled or not entries:
             return None
         T = sum(len(e.tokens) for e in entries)
@@ -368,7 +381,7 @@ class PromptGraphs:
         token_lists = [e.tokens for e in entries]
         wants = [e.want for e in entries]
         eng.validate(slots, token_lists, wants)
-        key = key or self.shape_of(entries)
+        key = key or self._shape(entries)
         if key is None:
             raise StepError("this step is not one that is replayed")
         n_new = [len(t) for t in token_lists]

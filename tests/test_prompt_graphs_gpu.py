@@ -20,6 +20,7 @@ def test_replayed_prompt_steps(tmp_path, name, dtype):
     replayed = Stratum(path, dtype=dtype, max_tokens=4096)
     by_hand = Stratum(path, dtype=dtype, max_tokens=4096, use_graphs=False)
     assert replayed.prompt_graphs is not None and replayed.prompt_graphs.enabled and by_hand.prompt_graphs is None
+    replayed.prompt_graphs.capture_after = 0             # (by default a shape is captured at its second sighting)
     rng = np.random.default_rng(7)
     # (5, 70, 130) and (70, 4, 131) share a shape (256 tokens, 4 sequences); 64 tokens fill theirs exactly
     batches = [(5, 70, 130), (64,), (1, 200, 3, 17, 40), (70, 4, 131), (2, 1)]
@@ -67,6 +68,8 @@ def test_what_is_replayed_and_what_is_not(tmp_path):
     pg = llm.prompt_graphs
     a, b = llm.acquire(), llm.acquire()
     toks = list(range(1, 40))
+    # a shape is replayed from its second sighting on: one that never comes back is not captured
+    assert pg.shape_of([StepEntry(a, toks, [38]), StepEntry(b, toks[:3], [2])]) is None
     assert pg.shape_of([StepEntry(a, toks, [38]), StepEntry(b, toks[:3], [2])]) == (64, 2, 1)
     assert pg.shape_of([StepEntry(a, toks, list(range(39)))]) is None          # every position wanted: by hand
     assert pg.shape_of([StepEntry(a, [1], [0]), StepEntry(b, [2], [0])]) is None   # one token each: a decode step
