@@ -47,11 +47,12 @@ def test_residual_add_hands_on_to_the_next_norm(M, N, K):
 
 
 @pytest.mark.parametrize("M", ROWS)
-@pytest.mark.parametrize("mode", ["store", "swiglu"])
-def test_rows_scaled_by_a_handed_over_norm(M, mode):
+@pytest.mark.parametrize("mode,K,N", [("store", 1024, 2048 + 128), ("swiglu", 1024, 2048 + 128),
+                                      ("store", 4096 + 64, 4096)])   # the last: k shared inside clusters up to 64 rows
+def test_rows_scaled_by_a_handed_over_norm(M, mode, K, N):
     from stratum_b200 import kernels as Kn
     rng = np.random.default_rng(M)
-    K, N, H, eps, parts = 1024, 2048 + 128, 1024, 1e-5, 7
+    H, eps, parts = 1024, 1e-5, 7
     x, w = _bf(rng.standard_normal((M, K)) * 0.5), _bf(rng.standard_normal((N, K)) * 0.05)
     bias = dev(rng.standard_normal(N) * 0.1)
     ss = dev(rng.random((parts + 2, M)) * H / parts)                 # two rows more than are used
@@ -62,6 +63,8 @@ def test_rows_scaled_by_a_handed_over_norm(M, mode):
         out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
         Kn.gemm_tc(x, w, bias, out, Kn.EPI_STORE, extra)
         want = y
+        if N == 4096 and M <= 64:
+            assert Kn.gemm_tc_last_form()[0] == "cluster-k"
     else:
         out = torch.empty(M, N // 2, dtype=torch.bfloat16, device="cuda")
         Kn.gemm_tc(x, w, bias, out, Kn.EPI_SWIGLU, extra)
@@ -72,11 +75,12 @@ def test_rows_scaled_by_a_handed_over_norm(M, mode):
 
 
 @pytest.mark.parametrize("M", ROWS)
-@pytest.mark.parametrize("n_q,n_kv,hd,pairs", [(8, 2, 128, 64), (6, 3, 64, 16), (4, 4, 32, 16)])
-def test_query_key_value_epilogue_rotates_and_writes_the_cache(M, n_q, n_kv, hd, pairs):
+@pytest.mark.parametrize("n_q,n_kv,hd,pairs,K", [(8, 2, 128, 64, 512), (6, 3, 64, 16, 512), (4, 4, 32, 16, 512),
+                                                 (24, 4, 128, 64, 4096)])   # the last: clusters up to 64 rows
+def test_query_key_value_epilogue_rotates_and_writes_the_cache(M, n_q, n_kv, hd, pairs, K):
     from stratum_b200 import kernels as Kn
     rng = np.random.default_rng(M * hd)
-    K, N = 512, (n_q + 2 * n_kv) * hd
+    N = (n_q + 2 * n_kv) * hd
     x, w = _bf(rng.standard_normal((M, K)) * 0.5), _bf(rng.standard_normal((N, K)) * 0.05)
     bias = dev(rng.standard_normal(N) * 0.1)
     # rows are tokens of sequences of unequal lengths with pages in an order of their own; some rows are padding
@@ -106,6 +110,8 @@ def test_query_key_value_epilogue_rotates_and_writes_the_cache(M, n_q, n_kv, hd,
     Kn.gemm_tc(x, w, bias, out, Kn.EPI_QKV_ROPE, extra)
     torch.cuda.synchronize()
     Kn.check_status()
+    if K == 4096 and M <= 64:
+        assert Kn.gemm_tc_last_form()[0] == "cluster-k"
     y = P.linear(as64(x), as64(w), as64(bias))
     q = y[:, :n_q * hd].reshape(M, n_q, hd)
     k = y[:, n_q * hd:(n_q + n_kv) * hd].reshape(M, n_kv, hd)
