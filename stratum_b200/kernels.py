@@ -598,12 +598,44 @@ def feed_ids(ids: torch.Tensor, feed: torch.Tensor, prev: torch.Tensor) -> None:
     _check(f(_ptr(ids), _ptr(feed), _ptr(prev), ids.numel(), _stream()), "feed_ids")
 
 
+SAMPLE_SPLITS, SAMPLE_KEEP = 32, 64
+_sample_scratch = None
+
+
+def _sample_scratch_for(rows: int, device):
+    """What the many-blocks-per-row sampling kernel leaves between its two stages (per row: the stretches' best
+    logits, ids, sums and last kept keys, their lists of candidates, a counter that starts at zero and is left
+    at zero, a mark for the one-block kernel)."""
+    global _sample_scratch
+    if _sample_scratch is None or _sample_scratch[6].numel() < rows:
+        n = max(rows, 64)
+        f32, i32 = torch.float32, torch.int32
+        _sample_scratch = (torch.empty(n * SAMPLE_SPLITS, dtype=f32, device=device),
+                           torch.empty(n * SAMPLE_SPLITS, dtype=i32, device=device),
+                           torch.empty(n * SAMPLE_SPLITS * 8, dtype=f32, device=device),
+                           torch.empty(n * SAMPLE_SPLITS, dtype=i32, device=device),
+                           torch.empty(n * SAMPLE_SPLITS * SAMPLE_KEEP, dtype=f32, device=device),
+                           torch.empty(n * SAMPLE_SPLITS * SAMPLE_KEEP, dtype=i32, device=device),
+                           torch.zeros(n, dtype=i32, device=device),
+                           torch.zeros(n, dtype=i32, device=device))
+        scratch_regrown()
+    return _sample_scratch
+
+
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
-           uniform: torch.Tensor, ids: torch.Tensor, values: Optional[torch.Tensor] = None) -> None:
+           uniform: torch.Tensor, ids: torch.Tensor, values: Optional[torch.Tensor] = None,
+           one_block_per_row: bool = False) -> None:
+    """Per row: temperature <= 0 greedy, else a draw by `uniform` from exp((l - max) / T), optionally among the
+    top_k largest (0: off, at most 512) cut after the prefix that reaches top_p (1: off).  Rows of 8,192 logits
+    or more are cut over 32 blocks each (one_block_per_row: the single-block kernel, for comparison)."""
     _need(logits, "logits", torch.float32, contiguous=False); _need(ids, "ids", torch.int32)
     _need(temperature, "temperature", torch.float32); _need(top_k, "top_k", torch.int32)
     _need(top_p, "top_p", torch.float32); _need(uniform, "uniform", torch.float32)
+    scratch = (None,) * 8 if one_block_per_row else _sample_scratch_for(logits.shape[0], logits.device)
     f = _fn("sampling", "stratum_sample",
-            [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+            [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(f(_ptr(logits), logits.stride(0), logits.shape[0], logits.shape[1], _ptr(temperature), _ptr(top_k),
-             _ptr(top_p), _ptr(uniform), _ptr(ids), _ptr(values), _stream()), "sample")
+             _ptr(top_p), _ptr(uniform), _ptr(ids), _ptr(values), *[_ptr(t) for t in scratch], _stream()), "sample")
+    if not one_block_per_row and 8192 <= logits.shape[1] <= 262144:
+        count_launches(1)                      # the one-block kernel behind, for marked rows

@@ -42,22 +42,27 @@ def _lands_in(cum, ids, got, u):
     assert below - CDF_NOISE <= u and (last or u < cum[i] + CDF_NOISE), (u, got, below, cum[i])
 
 
-def _pick(logits, temp, top_k, top_p, us):
+def _pick(logits, temp, top_k, top_p, us, one_block_per_row=False):
     from stratum_b200 import kernels as K
     n = len(us)
     L = _dev(np.repeat(logits[None], n, 0), torch.float32)
     ids = torch.empty(n, dtype=torch.int32, device="cuda")
+    vals = torch.empty(n, dtype=torch.float32, device="cuda")
     K.sample(L, _dev([temp] * n, torch.float32), _dev([top_k] * n, torch.int32), _dev([top_p] * n, torch.float32),
-             _dev(us, torch.float32), ids)
-    return ids.tolist()
+             _dev(us, torch.float32), ids, vals, one_block_per_row=one_block_per_row)
+    got = ids.tolist()
+    assert vals.tolist() == [float(logits[g]) for g in got]
+    return got
 
 
-@pytest.mark.parametrize("vocab", [320, 5000, 128256])
-def test_temperature_draws_follow_the_inverse_cdf(vocab):
+@pytest.mark.parametrize("one_block", [False, True])
+@pytest.mark.parametrize("vocab", [320, 5000, 8192, 50001, 128256])
+def test_temperature_draws_follow_the_inverse_cdf(vocab, one_block):
+    """(From 8,192 logits on a row is cut over 32 blocks; one_block: the kernel with one block a row.)"""
     rng = np.random.default_rng(vocab)
     logits = (rng.standard_normal(vocab) * 2.0).astype(np.float32)
     us = np.concatenate([rng.random(2000), [0.0, 0.999999]]).astype(np.float32)
-    got = _pick(logits, 0.8, 0, 1.0, us)
+    got = _pick(logits, 0.8, 0, 1.0, us, one_block)
     ids, probs = P.filtered_distribution(logits, np.float32(0.8), 0, 1.0)
     cum = np.cumsum(probs)
     for u, g in zip(us, got):
@@ -75,6 +80,8 @@ def test_top_k_top_p_candidates(top_k, top_p):
     logits[[10, 20, 30]] = logits.max() + 0.5             # a tie at the very top: lower ids come first
     us = rng.random(600).astype(np.float32)
     got = _pick(logits, 1.3, top_k, top_p, us)
+    # the row cut over 32 blocks and the row in one block keep the same candidates in the same order: the same picks
+    assert got == _pick(logits, 1.3, top_k, top_p, us, one_block_per_row=True)
     k = top_k if 0 < top_k <= 512 else 512                # a filtered draw keeps at most 512 candidates
     ids, probs = P.filtered_distribution(logits, np.float32(1.3), k, top_p)
     cum = np.cumsum(probs)
@@ -96,3 +103,45 @@ def test_greedy_rows_and_sampled_rows_in_one_launch():
     assert got[0] == int(logits[0].argmax()) and got[2] == int(logits[2].argmax())
     i, p = P.filtered_distribution(logits[1], 1.0, 0, 1.0)
     assert got[1] == P.sample_inverse_cdf(i, p, 0.5)
+
+
+@pytest.mark.parametrize("vocab", [8192, 20011, 128256])
+def test_rows_cut_over_blocks_ties_and_odd_rows(vocab):
+    """Ties that straddle the cut inside a stretch and across stretches, a row of equal logits, logits of -inf,
+    more candidates asked for than a stretch holds: the 32-block kernel against the plain oracle and the one-block
+    kernel."""
+    rng = np.random.default_rng(vocab + 1)
+    us = rng.random(300).astype(np.float32)
+    chunk = (vocab + 31) // 32
+    cases = []
+    a = (rng.standard_normal(vocab) * 2.0).astype(np.float32)
+    top = float(a.max()) + 1.0
+    a[[3, chunk - 1, chunk, 5 * chunk + 7, vocab - 1]] = top       # five equal at the top, in three stretches
+    cases.append(("tie across stretches", a, 3))                    # only the three lowest ids survive
+    b = np.full(vocab, -1.25, dtype=np.float32)
+    cases.append(("all equal", b, 7))                               # ids 0..6
+    c = (rng.standard_normal(vocab) * 2.0).astype(np.float32)
+    c[rng.random(vocab) < 0.5] = -np.inf
+    cases.append(("half of them -inf", c, 40))
+    d = (rng.standard_normal(vocab) * 0.01).astype(np.float32)
+    d[: chunk // 2] += 10.0                                         # the first stretch alone holds the best 512
+    cases.append(("one stretch holds all candidates", d, 512))
+    for name, logits, k in cases:
+        for top_p in (1.0, 0.8):
+            got = _pick(logits, 0.9, k, top_p, us)
+            assert got == _pick(logits, 0.9, k, top_p, us, one_block_per_row=True), name
+            ids, probs = P.filtered_distribution(logits, np.float32(0.9), k, top_p)
+            cum = np.cumsum(probs)
+            assert set(got) <= set(ids.tolist()), name
+            for u, g in zip(us, got):
+                _lands_in(cum, ids, g, u)
+    assert set(_pick(cases[0][1], 0.9, 3, 1.0, us)) <= {3, chunk - 1, chunk}
+    assert set(_pick(cases[1][1], 0.9, 7, 1.0, us)) == set(range(7))
+    # without filters, and greedy rows, on the same odd rows
+    for name, logits, _ in cases[:3]:
+        got = _pick(logits, 0.9, 0, 1.0, us)
+        ids, probs = P.filtered_distribution(logits, np.float32(0.9), 0, 1.0)
+        cum = np.cumsum(probs)
+        for u, g in zip(us, got):
+            _lands_in(cum, ids, g, u)
+        assert _pick(logits, 0.0, 0, 1.0, us[:3]) == [P.argmax_lowest(logits)] * 3
