@@ -385,16 +385,20 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab, const float* 
       }
     });
     __syncthreads();
-    if (tid == 0) {
-      unsigned remaining = sh_remaining;
-      int b = 255;
-      for (; b > 0; b--) {
-        if (hist[b] >= remaining) break;
-        remaining -= hist[b];
+    {
+      // thread t < 256 looks at bucket 255 - t: the bucket that holds the k-th largest is the one whose count, added
+      // to the counts of the buckets above it, first reaches what is still wanted (one thread walking the 256
+      // buckets cost 4 us a pass)
+      const int b = 255 - tid;
+      const unsigned cnt = tid < 256 ? hist[b] : 0u;
+      const unsigned remaining = sh_remaining;
+      unsigned all;
+      const unsigned above = block_excl_scan(cnt, u_scratch, &all);
+      if (tid < 256 && above < remaining && remaining <= above + cnt) {
+        sh_prefix = prefix | ((unsigned)b << shift);
+        sh_remaining = remaining - above;   // how many of the k lie in the chosen bucket
+        sh_equal_total = cnt;               // after the last pass: how many logits equal the k-th largest
       }
-      sh_prefix = prefix | ((unsigned)b << shift);
-      sh_remaining = remaining;       // how many of the k lie in the chosen bucket
-      sh_equal_total = hist[b];       // after the last pass: how many logits equal the k-th largest
     }
     __syncthreads();
   }

@@ -14,7 +14,7 @@ forward launches on the current stream only, reads nothing back to the host, tak
 StepBatch's host numbers (never from device tensors), allocates only through torch or Runtime.scratch, and
 leaves the cache of rows with sequence index -1 alone (their state row is the spare one, `max_seqs`).
 
-A graph is specific to (rows, page-table width, greedy or sampling): rows is the batch padded up a little (padding
+A graph is specific to (rows, page-table width, how tokens are picked): rows is the batch padded up a little (padding
 rows carry sequence index -1, which every kernel that touches the cache skips; rows never mix, so
 padding changes no result), and the width is the next power of two of the pages the longest
 sequence holds, which also fixes how the keys are split across warps.
@@ -37,6 +37,20 @@ from ..cache.pages import PAGE_TOKENS, pages_for
 from .step import Engine, StepDescription, StepEntry, StepError
 
 
+# How a graph picks its tokens: greedy, by a draw, or (many rows with top-k / top-p) by a draw with the sampling kernel
+# that gives a row one block: with filters and more than SAMPLE_SPLIT_MAX_ROWS rows the kernel that cuts a row over
+# 32 blocks queues thousands of blocks for the SMs and loses (110 against 83 us at 64 rows with top-k 50).
+PICK_GREEDY, PICK_DRAW, PICK_FILTERED_MANY_ROWS = 0, 1, 2
+SAMPLE_SPLIT_MAX_ROWS = 32
+
+
+def pick_kind(rows: int, temperature: float, top_k: int, top_p: float) -> int:
+    if not (temperature > 0.0):
+        return PICK_GREEDY
+    filtered = top_k > 0 or top_p < 1.0
+    return PICK_FILTERED_MANY_ROWS if filtered and rows > SAMPLE_SPLIT_MAX_ROWS else PICK_DRAW
+
+
 def padded_rows(n: int) -> int:
     """Rows a graph is captured for: exact up to 8, then the next multiple of 8."""
     return n if n <= 8 else ((n + 7) // 8) * 8
@@ -50,8 +64,9 @@ def width_bucket(n_pages: int) -> int:
 
 
 class _Captured:
-    def __init__(self, engine: Engine, rows: int, width: int, greedy: bool):
-        self.rows, self.width, self.greedy = rows, width, greedy
+    def __init__(self, engine: Engine, rows: int, width: int, pick: int):
+        self.rows, self.width, self.pick = rows, width, pick
+        self.greedy = pick == PICK_GREEDY
         B = rows
         self.desc = StepDescription(engine, B, B, B, width, pinned=True,
                                     extras=(("temperature", B), ("top_k", B), ("top_p", B), ("uniform", B),
@@ -99,7 +114,7 @@ class DecodeGraphs:
             K.argmax(logits, c.out_ids, c.out_vals)
         else:
             K.sample(logits, f32("temperature"), d.field("top_k"), f32("top_p"), f32("uniform"), c.out_ids,
-                     c.out_vals)
+                     c.out_vals, one_block_per_row=c.pick == PICK_FILTERED_MANY_ROWS)
         c.out[2 * c.rows:].copy_(K.status_word())
         c.logits = logits
 
@@ -125,8 +140,8 @@ class DecodeGraphs:
         c.signature = None
         self.captures += 1
 
-    def _get(self, rows: int, width: int, greedy: bool) -> _Captured:
-        key = (rows, width, greedy)
+    def _get(self, rows: int, width: int, pick: int) -> _Captured:
+        key = (rows, width, pick)
         c = self.graphs.get(key)
         if c is not None and c.graph is not None and c.scratch_epoch != K.scratch_epoch():
             # a scratch buffer was regrown (and the old one freed) since this graph recorded its address
@@ -135,7 +150,7 @@ class DecodeGraphs:
         if c is None:
             while len(self.graphs) >= self.max_graphs:
                 self.graphs.popitem(last=False)
-            c = _Captured(self.engine, rows, width, greedy)
+            c = _Captured(self.engine, rows, width, pick)
             self.graphs[key] = c
         else:
             self.graphs.move_to_end(key)
@@ -173,7 +188,8 @@ class DecodeGraphs:
         ones = _ONES[:B] if B <= len(_ONES) else [1] * B
         cache.reserve(slots, ones)
         before = [cache.length(s) for s in slots]
-        c = self._get(padded_rows(B), width_bucket(pages_for(max(before) + 1)), not (temperature > 0.0))
+        c = self._get(padded_rows(B), width_bucket(pages_for(max(before) + 1)),
+                      pick_kind(padded_rows(B), temperature, top_k, top_p))
         if c.graph is None:
             self._capture(c)
         if c.upload_pending:                          # the pinned description is about to be rewritten

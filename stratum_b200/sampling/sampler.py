@@ -41,5 +41,8 @@ class Sampler:
         host[2, :] = params.top_p
         host[3, :] = [s.uniform() for s in streams]
         dev = torch.from_numpy(host).to(self.device)
-        K.sample(logits, dev[0], dev[1].view(torch.int32), dev[2], dev[3], ids, values)
+        # (with filters and many rows the kernel that gives a row one block is ahead: engine/graphs.py, pick_kind)
+        many_filtered = n > 32 and (params.top_k > 0 or params.top_p < 1.0)
+        K.sample(logits, dev[0], dev[1].view(torch.int32), dev[2], dev[3], ids, values,
+                 one_block_per_row=many_filtered)
         return ids, values
