@@ -13,6 +13,8 @@
 //               query heads of the group along N, as in attention_decode_kernel: S^T = K Q^T, online softmax
 //               in float32 per head, O^T += V^T P^T with V transposed in registers by movmatrix.  Fragments are
 //               16-byte reads of shared memory at the swizzled address of (key, 8 dims).
+//               (Heads of 64 with many pages: eight warps, each taking every eighth page whole; see the entry
+//               point's note.)
 //
 // When a (sequence, kv head) ends, the four warps' maxima, sums and outputs are merged through shared memory.
 // If the CTA saw all of its keys the normalised output is written; otherwise the unnormalised output, maximum
@@ -224,8 +226,8 @@ attention_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
     while (u < u1 && cur.b == b && cur.kvh == kvh) {
       const int s = it % STAGES;
       if constexpr (WP) {
-        // a warp takes every fourth page whole: the scores of its 64 keys first, one maximum and one rescaling of
-        // the sums per page, then the products with V; the four warps work on four pages at a time
+        // the pages go round the warps, and a warp takes a page whole: the scores of its 64 keys first, one maximum
+        // and one rescaling of the sums per page, then the products with V; NW warps work on NW pages at a time
         to_end = cur.page == sq.first + sq.n - 1;
         if ((int)(it % NW) == w) {
           // A wait can tell a barrier's current phase from the one before only, and the filling of this stage
