@@ -238,7 +238,9 @@ def run_workload(llm, cfg, n_layers, workload, shape, peaks, rng):
         if index == 0 and req == len(lens) - 1:
             marks["first"] = time.perf_counter()
 
-    llm.generate([p[:8] for p in prompts[:2]], max_new_tokens=2, stop_ids=())     # compile and warm up
+    # compile, load and warm up what this very workload uses (which kernels a step takes depends on its rows: a
+    # kernel's first launch loads its code, and a shape's first decode step captures its graph)
+    llm.generate(prompts, max_new_tokens=4, stop_ids=())
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     out = llm.generate(prompts, max_new_tokens=new, stop_ids=(), on_token=on_token)
