@@ -592,6 +592,26 @@ def test_attention_tc_far_key(halves):
     assert rel_err(as64(_run_tc(c, [100, 700], n_q, n_kv, hd, halves=halves)), c["ref"]) < 8e-3
 
 
+@pytest.mark.parametrize("halves", [1, 2])
+@pytest.mark.parametrize("n_q,n_kv,hd", [(8, 2, 128), (4, 2, 64)])
+def test_attention_tc_long_walk(n_q, n_kv, hd, halves):
+    """Three hundred new tokens behind 5,900 cached ones: every query tile walks some ninety key tiles (the K and V
+    rings go round forty times), one key near the beginning stands out for the last query, and with a window of
+    1,000 the walk begins in the middle of the cache."""
+    rng = np.random.default_rng(hd + halves)
+
+    def spike(s, q, k, v):
+        if s == 0:
+            d = rng.standard_normal(hd); d /= np.linalg.norm(d)
+            k[3, :, :] = d * 12.0
+            q[-1, :, :] = d * 12.0
+
+    c = _attention_case(rng, [5900, 0], [300, 64], n_q, n_kv, hd, "bfloat16", spike=spike)
+    assert rel_err(as64(_run_tc(c, [300, 64], n_q, n_kv, hd, halves=halves)), c["ref"]) < 8e-3
+    c = _attention_case(rng, [5900], [300], n_q, n_kv, hd, "bfloat16", window=1000, spike=spike)
+    assert rel_err(as64(_run_tc(c, [300], n_q, n_kv, hd, window=1000, halves=halves)), c["ref"]) < 8e-3
+
+
 def _run_stream(c, n_q, n_kv, hd, window=0, pad_rows=0, whole_pages=False):
     """attention_stream on the case's new tokens (one per sequence), optionally with padding rows appended."""
     from stratum_b200 import kernels as K
