@@ -1062,7 +1062,11 @@ gemm_tc_clusterk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   tc_fence_after();
   const uint32_t tmem_base = S.tmem_base;
   constexpr int CW = (BN >= 32) ? 32 : 16;
-  float v[BN];                                     // epilogue warps: this thread's weight row, all rows of x
+  // Up to 64 rows of x an epilogue thread holds its weight row's sums for all rows of x in registers; with 256
+  // rows (prompts of up to 256 tokens) it reads tensor memory chunk by chunk when it deals the chunks out.
+  constexpr bool WIDE = BN > 64;
+  static_assert(!WIDE || !XT, "the wide cluster forms know the plain epilogues only");
+  float v[WIDE ? 1 : BN];                          // epilogue warps: this thread's weight row, all rows of x
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -1122,17 +1126,19 @@ gemm_tc_clusterk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
         if (lane == 0) { atomicCAS(P.status, 0, 124); S.abort_flag = 1; }
       }
       tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+      if constexpr (!WIDE) {
+        const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
 #pragma unroll
-      for (int c0 = 0; c0 < BN; c0 += CW) {
-        uint32_t r[CW];
-        if constexpr (CW == 32) tmem_ld32(taddr + c0, r); else tmem_ld16(taddr + c0, r);
-        tmem_ld_wait();
+        for (int c0 = 0; c0 < BN; c0 += CW) {
+          uint32_t r[CW];
+          if constexpr (CW == 32) tmem_ld32(taddr + c0, r); else tmem_ld16(taddr + c0, r);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < CW; j++) v[c0 + j] = __uint_as_float(r[j]);
+          for (int j = 0; j < CW; j++) v[c0 + j] = __uint_as_float(r[j]);
+        }
+        tc_fence_before();
       }
-      tc_fence_before();
-    } else {
+    } else if constexpr (!WIDE) {
 #pragma unroll
       for (int j = 0; j < BN; j++) v[j] = 0.0f;
     }
@@ -1143,26 +1149,55 @@ gemm_tc_clusterk_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
   // to the ranks (chunk c to rank c % CS) and every CTA writes its partial sums of a chunk into the ring of the
   // chunk's rank; after the second, every rank adds what it was given in the order of the ranks, which is the order
   // of k, and runs the epilogue for its rows: the adding and storing is spread over the cluster.
-  constexpr int CWS = BN >= 32 ? 8 : 4;
+  constexpr int CWS = BN > 64 ? 16 : (BN >= 32 ? 8 : 4);
   constexpr int NCH = BN / CWS;
+  // (what a rank is given fits its ring, a and b together: at most NCH + 7 chunks of CWS x 128 float32)
+  static_assert((size_t)(NCH + 7) * CWS * TC_BM * sizeof(float) <= (size_t)STAGES * (TC_BM + BN) * TC_BK * sizeof(bf16),
+                "the exchange does not fit the ring");
   const int live = (P.M + CWS - 1) / CWS < NCH ? (P.M + CWS - 1) / CWS : NCH;   // chunks that hold rows of x
   const int row = (warp & 3) * 32 + lane;
   __syncwarp();
   cluster_sync_all();
   float* part = reinterpret_cast<float*>(S.a);      // this CTA's ring: [its chunks][source rank][CWS][128] float32
   if (warp >= 2) {
+    if constexpr (WIDE) {
+      // (every rank's MMAs are complete: each rank's epilogue warps came to the meeting after their wait for them)
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < live; c++) {
+        uint32_t r[CWS];
+        if (kb1 > kb0) { tmem_ld16(taddr + c * CWS, r); tmem_ld_wait(); }
+        else {
 #pragma unroll
-    for (int c = 0; c < NCH; c++) {
-      if (c < live) {
+          for (int j = 0; j < CWS; j++) r[j] = 0u;
+        }
         const int owner = c % CS, slot = c / CS;
         float* mine = part + (size_t)(slot * CS + rank) * CWS * TC_BM + row;
         if (owner == rank) {
 #pragma unroll
-          for (int j = 0; j < CWS; j++) mine[j * TC_BM] = v[c * CWS + j];
+          for (int j = 0; j < CWS; j++) mine[j * TC_BM] = __uint_as_float(r[j]);
         } else {
           const uint32_t dst = cluster_map(mine, (uint32_t)owner);
 #pragma unroll
-          for (int j = 0; j < CWS; j++) st_cluster_f32(dst + (uint32_t)(j * TC_BM * sizeof(float)), v[c * CWS + j]);
+          for (int j = 0; j < CWS; j++) st_cluster_f32(dst + (uint32_t)(j * TC_BM * sizeof(float)), __uint_as_float(r[j]));
+        }
+      }
+      tc_fence_before();
+    } else {
+#pragma unroll
+      for (int c = 0; c < NCH; c++) {
+        if (c < live) {
+          const int owner = c % CS, slot = c / CS;
+          float* mine = part + (size_t)(slot * CS + rank) * CWS * TC_BM + row;
+          if (owner == rank) {
+#pragma unroll
+            for (int j = 0; j < CWS; j++) mine[j * TC_BM] = v[c * CWS + j];
+          } else {
+            const uint32_t dst = cluster_map(mine, (uint32_t)owner);
+#pragma unroll
+            for (int j = 0; j < CWS; j++) st_cluster_f32(dst + (uint32_t)(j * TC_BM * sizeof(float)), v[c * CWS + j]);
+          }
         }
       }
     }
@@ -1607,7 +1642,7 @@ static int launch_clusterk(const CUtensorMap& mw, const CUtensorMap& mx, const S
 
 // The cluster form up to this many (padded) rows of x (STRATUM_GEMM_CLUSTERK_ROWS overrides, for measurements).
 #ifndef CLUSTERK_MAX_BN
-#define CLUSTERK_MAX_BN 64
+#define CLUSTERK_MAX_BN 256
 #endif
 static int clusterk_max_rows() {
   static int rows = -1;
@@ -1623,7 +1658,31 @@ static int clusterk_max_rows() {
 #define SK_RING_32 9
 #define SK_RING_64 8
 #define SK_RING_128 6
+#define SK_RING_256 4
 #endif
+
+// The cluster form for 129 to 256 rows of x (prompts of up to 256 tokens): x as one block of 256 rows along N of
+// the MMA, the plain epilogues only.  0: not taken (launch another form); 1: launched (*st holds the status).
+template <int BN, int STAGES>
+static int try_clusterk_wide(const CUtensorMap& mw, const CUtensorMap& mx, const SkParams& P, int epilogue,
+                             cudaStream_t stream, int* st) {
+  if (!clusterk_enabled() || BN > clusterk_max_rows() || epilogue > 3 || P.X.norm_ss) return 0;
+#define CKW(E)                                                                       \
+  {                                                                                  \
+    const int cs = clusterk_size<BN, STAGES, E, false>(P.tiles, P.n_kb);             \
+    if (cs <= 0) return 0;                                                           \
+    *st = launch_clusterk<BN, STAGES, E, false>(mw, mx, P, cs, stream);              \
+    return 1;                                                                        \
+  }
+  switch (epilogue) {
+    case 0: CKW(0)
+    case 1: CKW(1)
+    case 2: CKW(2)
+    case 3: CKW(3)
+    default: return 0;
+  }
+#undef CKW
+}
 
 template <int BN, int STAGES>
 static int launch_streamk(const CUtensorMap& mw, const CUtensorMap& mx, const SkParams& P, int epilogue,
@@ -1722,6 +1781,27 @@ STRATUM_EXPORT int stratum_gemm_tc_ex(const void* x, const void* w, const float*
   const long long tiles_plain = (long long)((M + TC_BM - 1) / TC_BM) * ((N + (N >= 2048 ? 255 : 127)) / (N >= 2048 ? 256 : 128));
   const bool swap = M <= 64 || (M <= 128 && scratch && tiles_plain * 10 < (long long)sm_count() * 7);
   int st;
+  if (M > 128 && M <= 256) {
+    // 129 to 256 rows and few tiles of W (the output and down projections of a short prompt): k cut inside clusters,
+    // the sums exchanged through distributed shared memory, instead of sharing tiles along k with a second kernel
+    // that adds the pieces.  Measured on the Llama-8B shapes (K = 4096 / 14336, N = 4096): 17.4 / 36.2 us at 192
+    // rows and 20.0 / 39.2 at 256 against 22.3 / 40.1 and 22.5 / 40.5 for pairs of CTAs sharing tiles; with 65 to
+    // 128 rows (x as one block of 128) it was level with stream-K and its second pass (14.4 / 29.5 against
+    // 13.8 / 28.8), so those stay as they were.
+    const int bn = 256;
+    SkParams Q;
+    Q.bias = bias; Q.out = out; Q.status = status; Q.scratch = scratch;
+    Q.M = M; Q.N = N; Q.K = K; Q.ldo = ldo; Q.X = X;
+    Q.tiles = (N + TC_BM - 1) / TC_BM;
+    Q.n_kb = (K + TC_BK - 1) / TC_BK;
+    Q.total_kb = Q.tiles * Q.n_kb;
+    if (Q.tiles * 2 <= sm_count() && Q.n_kb / 2 >= CLUSTERK_MIN_KB) {     // (a cluster of two at least: cheap pre-check)
+      if ((st = make_map(&ma, w, N, K, K, TC_BM)) != 0) return st;
+      if ((st = make_map(&mb, x, M, K, ldx, bn)) != 0) return st;
+      g_last_parts = Q.tiles;
+      if (try_clusterk_wide<256, SK_RING_256>(ma, mb, Q, epilogue, stream, &st)) return st;
+    }
+  }
   if (!swap) {
     // prompts: 128 rows of x by 256 (or 128) rows of W per tile
     const bool wide = N >= 2048;

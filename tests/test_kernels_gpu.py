@@ -164,7 +164,9 @@ CLUSTER_FORMS = {(8, 4096, 4096), (40, 4096, 4096 + 72), (30, 5000, 3080), (24, 
                  (64, 8192 + 8, 2048 + 16), (17, 4096, 14336), (64, 4096 + 64, 14336)}
 
 
-PAIRS_SHARED = {(512, 4096, 14336), (256, 4096 + 64, 4096), (200, 4096, 4096)}
+PAIRS_SHARED = {(512, 4096, 14336), (256, 6144, 4096 + 64), (200, 2048, 8192)}
+# 129 to 256 rows, few tiles of W, long k: clusters again, x as one block of 256 rows
+WIDE_CLUSTERS = {(200, 4096, 4096), (256, 4096 + 64, 4096), (250, 4100, 14344), (129, 4096, 4096 + 8)}
 
 
 @pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (33, 48, 64), (64, 1000, 200), (100, 256, 4096), (300, 4096 + 16, 512),
@@ -182,6 +184,7 @@ PAIRS_SHARED = {(512, 4096, 14336), (256, 4096 + 64, 4096), (200, 4096, 4096)}
                                      (1000, 2100, 264), (256, 28672, 128), (2304, 9000, 72),
                                      # a few hundred rows, few tiles of 256 x 256: all pairs of CTAs share them along k
                                      (512, 4096, 14336), (256, 4096 + 64, 4096), (520, 4100, 14344), (130, 2048 + 8, 1096), (700, 4100, 2048),
+                                     (256, 6144, 4096 + 64), (200, 2048, 8192), (250, 4100, 14344), (129, 4096, 4096 + 8),
                                      # few rows, no more tiles than SMs: too little k for clusters to share
                                      (40, 4096, 2048), (30, 5120, 1000), (3, 2304, 1032), (8, 16000, 520),
                                      # k shared inside clusters, rows dealt out to the ranks
@@ -206,6 +209,8 @@ def test_gemm_tc(M, N, K_):
         assert K.gemm_tc_last_form()[0] == "stream-k"
     elif (M, N, K_) in PAIRS_SHARED:
         assert K.gemm_tc_last_form()[0] == "pairs-shared"
+    elif (M, N, K_) in WIDE_CLUSTERS:
+        assert K.gemm_tc_last_form()[0] == "cluster-k"
     out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
     K.gemm_tc(x, w, b, out, K.EPI_STORE)
     assert rel_err(as64(out), ref) < 6e-3
