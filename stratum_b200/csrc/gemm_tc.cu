@@ -1811,13 +1811,16 @@ STRATUM_EXPORT int stratum_gemm_tc_ex(const void* x, const void* w, const float*
     const int rows1 = ((M + TC_BM - 1) / TC_BM) * TC_BM, rows2 = ((M + 2 * TC_BM - 1) / (2 * TC_BM)) * 2 * TC_BM;
     // Few tiles of 256 x 256 (a few hundred rows, N of a few thousand): their k-blocks are shared by all pairs,
     // as the tile kernel shares its left-over tiles, but with the pairs' smaller draw on L2 per flop.
-    if (wide && M >= pair_kernel_min_rows() && rows2 * 100 <= rows1 * 115 && scratch && epilogue < 4 && !X.norm_ss &&
+    if (wide && M >= pair_kernel_min_rows() && rows2 * 100 <= rows1 * 125 && scratch && epilogue < 4 && !X.norm_ss &&
         pair_split_enabled()) {
       const int pairs = resident_pairs();
       // (measured on the Llama-8B shapes: K = 14336 at 256 and 512 rows 40 and 59 us against 53 and 83 with the tile
       // kernel; at 768 rows, where the model says 0.79 of the unshared time, 82 against 79 us: the pairs that stay
       // idle without sharing leave the busy ones a higher clock)
-      if (pairs >= 1 && split_pays(n_tiles2, (K + TC_BK - 1) / TC_BK, pairs, 256, 0.75f)) {
+      // (where the tiles are too few for the pairs to run unshared, the other way is the tile kernel sharing its
+      // tiles, which the pairs beat more easily: K = 4096 at 512 rows 27.9 against 30.3 us at 0.88 of the model)
+      const bool pairs_unshared_possible = n_tiles2 * 10 >= (sm_count() / 2) * 6;
+      if (pairs >= 1 && split_pays(n_tiles2, (K + TC_BK - 1) / TC_BK, pairs, 256, pairs_unshared_possible ? 0.75f : 0.9f)) {
         if ((st = make_map(&ma, x, M, K, ldx, TC_BM)) != 0) return st;
         if ((st = make_map(&mb, w, N, K, K, 128)) != 0) return st;
         g_last_parts = (N + 255) / 256;
@@ -1825,7 +1828,9 @@ STRATUM_EXPORT int stratum_gemm_tc_ex(const void* x, const void* w, const float*
       }
     }
     if (wide && M >= pair_kernel_min_rows() && n_tiles2 * 10 >= (sm_count() / 2) * 6 &&
-        rows2 * 100 <= rows1 * 115) {               // (not where half of a pair would work on rows beyond M)
+        rows2 * 100 <= rows1 * 125) {               // (not where half of a pair would work on rows beyond M: up to a
+                                                    // quarter more rows the pairs still win, 10.1 against 11.0 ms for a
+                                                    // prompt of 640 tokens on the Llama-8B shape; a third more, they lose)
       const int pairs = resident_pairs();
       if (pairs >= 1) {
         // (epilogue 5 walks whole heads: tiles of 256 columns begin where a head begins)
