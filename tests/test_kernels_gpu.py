@@ -164,7 +164,7 @@ CLUSTER_FORMS = {(8, 4096, 4096), (40, 4096, 4096 + 72), (30, 5000, 3080), (24, 
                  (64, 8192 + 8, 2048 + 16), (17, 4096, 14336), (64, 4096 + 64, 14336)}
 
 
-PAIRS_SHARED = {(512, 4096, 14336), (256, 6144, 4096 + 64), (200, 2048, 8192)}
+PAIRS_SHARED = {(512, 4096, 14336), (256, 6144, 4096 + 64), (400, 4096, 14336 + 8)}
 # 129 to 256 rows, few tiles of W, long k: clusters again, x as one block of 256 rows
 WIDE_CLUSTERS = {(200, 4096, 4096), (256, 4096 + 64, 4096), (250, 4100, 14344), (129, 4096, 4096 + 8)}
 
@@ -184,7 +184,7 @@ WIDE_CLUSTERS = {(200, 4096, 4096), (256, 4096 + 64, 4096), (250, 4100, 14344), 
                                      (1000, 2100, 264), (256, 28672, 128), (2304, 9000, 72),
                                      # a few hundred rows, few tiles of 256 x 256: all pairs of CTAs share them along k
                                      (512, 4096, 14336), (256, 4096 + 64, 4096), (520, 4100, 14344), (130, 2048 + 8, 1096), (700, 4100, 2048),
-                                     (256, 6144, 4096 + 64), (200, 2048, 8192), (250, 4100, 14344), (129, 4096, 4096 + 8),
+                                     (256, 6144, 4096 + 64), (200, 2048, 8192), (400, 4096, 14336 + 8), (250, 4100, 14344), (129, 4096, 4096 + 8),
                                      # few rows, no more tiles than SMs: too little k for clusters to share
                                      (40, 4096, 2048), (30, 5120, 1000), (3, 2304, 1032), (8, 16000, 520),
                                      # k shared inside clusters, rows dealt out to the ranks
