@@ -1,5 +1,7 @@
 // Picking the next token from float32 logits: greedy argmax and temperature sampling with
-// optional top-k / top-p filtering, one thread block per row.
+// optional top-k / top-p filtering.  Rows of 8,192 logits or more are cut over 32 thread blocks each
+// (argmax_split_kernel, sample_split_kernel); shorter rows, and rows the split sampling kernel marks,
+// get one block (argmax_kernel, sample_kernel).
 //
 // Greedy: the largest logit, the lowest index among equals (stratum/native/stratum_engine.h:429-463).
 // Sampling (stratum/native/stratum_arch_qwen35.inc.c:14023-14109): probabilities
